@@ -1,0 +1,159 @@
+"""TEST INFRASTRUCTURE ONLY -- drives the compiled, unmodified reference CPU code (oracle/_ref).
+
+The reference's Python package cannot be imported on this image (it imports `onmt`, which is absent),
+so this file talks to the reference's pybind module directly and repeats the weight packing its
+`from_torch` constructors do (python/turbo_transformers/layers/modeling_bert.py:58-65,88-95,124-131,
+179-204,530-560; modeling_smart_pad.py:434-486).  Nothing in the product package may import this file.
+"""
+import importlib.util
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.utils.dlpack as dlpack
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+_cxx = None
+
+
+def available():
+    from . import build_ref
+    return os.path.exists(build_ref.module_path())
+
+
+def load():
+    """Import oracle/_ref/turbo_transformers_cxx (building it first if the reference tree is present)."""
+    global _cxx
+    if _cxx is not None:
+        return _cxx
+    from . import build_ref
+    path = build_ref.build(verbose=False)
+    if path is None or not os.path.exists(path):
+        raise RuntimeError("oracle/_ref is not built and the reference tree is not available")
+    spec = importlib.util.spec_from_file_location("turbo_transformers_cxx", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    _cxx = mod
+    return mod
+
+
+def set_num_threads(n):
+    load().set_num_threads(int(n))
+
+
+def T(t):
+    """torch CPU tensor (or numpy array) -> reference core::Tensor owning a private copy."""
+    if isinstance(t, np.ndarray):
+        t = torch.from_numpy(np.ascontiguousarray(t))
+    return load().Tensor.from_dlpack(dlpack.to_dlpack(t.detach().contiguous().clone()))
+
+
+def back(t):
+    return dlpack.from_dlpack(t.to_dlpack())
+
+
+def E():
+    return load().Tensor.create_empty()
+
+
+def pack_bert_weights(hf_model):
+    """HF BertModel -> the dict-of-numpy layout both oracles use (weights [in,out], fused QKV [H,3H])."""
+    def n(p):
+        return p.detach().float().cpu().numpy().copy()
+    e = hf_model.embeddings
+    W = {"embedding": {"word": n(e.word_embeddings.weight), "position": n(e.position_embeddings.weight),
+                       "token_type": n(e.token_type_embeddings.weight), "ln_gamma": n(e.LayerNorm.weight),
+                       "ln_beta": n(e.LayerNorm.bias)}, "layers": []}
+    for l in hf_model.encoder.layer:
+        a = l.attention
+        qkv_w = torch.t(torch.cat((a.self.query.weight, a.self.key.weight, a.self.value.weight), 0)).contiguous()
+        qkv_b = torch.cat((a.self.query.bias, a.self.key.bias, a.self.value.bias), 0)
+        W["layers"].append({
+            "attention": {"qkv_weight": n(qkv_w), "qkv_bias": n(qkv_b),
+                          "dense_weight": n(torch.t(a.output.dense.weight).contiguous()),
+                          "dense_bias": n(a.output.dense.bias), "ln_gamma": n(a.output.LayerNorm.weight),
+                          "ln_beta": n(a.output.LayerNorm.bias)},
+            "inter_weight": n(torch.t(l.intermediate.dense.weight).contiguous()),
+            "inter_bias": n(l.intermediate.dense.bias),
+            "out_weight": n(torch.t(l.output.dense.weight).contiguous()), "out_bias": n(l.output.dense.bias),
+            "out_ln_gamma": n(l.output.LayerNorm.weight), "out_ln_beta": n(l.output.LayerNorm.bias)})
+    if getattr(hf_model, "pooler", None) is not None:
+        W["pooler_weight"] = n(torch.t(hf_model.pooler.dense.weight).contiguous())
+        W["pooler_bias"] = n(hf_model.pooler.dense.bias)
+    return W
+
+
+class RefBert:
+    """The reference's BERT, fixed-length and smart-batch, assembled from its compiled layer classes."""
+
+    def __init__(self, W, num_heads):
+        cxx = load()
+        self.cxx, self.h = cxx, num_heads
+        e = W["embedding"]
+        self.emb = cxx.BERTEmbedding(T(e["word"]), T(e["position"]), T(e["token_type"]), T(e["ln_gamma"]),
+                                     T(e["ln_beta"]))
+        self.layers, self.sb_layers = [], []
+        for lw in W["layers"]:
+            a = lw["attention"]
+            att = cxx.BertAttention(T(a["qkv_weight"]), T(a["qkv_bias"]), T(a["dense_weight"]), T(a["dense_bias"]),
+                                    T(a["ln_gamma"]), T(a["ln_beta"]), num_heads)
+            H = a["dense_weight"].shape[0]
+            qw, kw, vw = (np.ascontiguousarray(a["qkv_weight"][:, i * H:(i + 1) * H]) for i in range(3))
+            qb, kb, vb = (np.ascontiguousarray(a["qkv_bias"][i * H:(i + 1) * H]) for i in range(3))
+            sb = cxx.MultiHeadedAttentionSmartBatch(T(kw), T(kb), T(vw), T(vb), T(qw), T(qb), T(a["dense_weight"]),
+                                                    T(a["dense_bias"]), T(a["qkv_weight"]), T(a["qkv_bias"]),
+                                                    T(a["ln_gamma"]), T(a["ln_beta"]), num_heads)
+            inter = cxx.BertIntermediate(T(lw["inter_weight"]), T(lw["inter_bias"]))
+            out = cxx.BertOutput(T(lw["out_weight"]), T(lw["out_bias"]), T(lw["out_ln_gamma"]),
+                                 T(lw["out_ln_beta"]))
+            self.layers.append((att, inter, out))
+            self.sb_layers.append((sb, inter, out))
+        self.pooler = cxx.BertPooler(T(W["pooler_weight"]), T(W["pooler_bias"])) if "pooler_weight" in W else None
+        self.prep, self.seqpool = cxx.PrepareBertMasks(), cxx.SequencePool("First")
+
+    def embed(self, ids, att_mask=None):
+        am = T(att_mask) if att_mask is not None else E()
+        tt, pos, ext = E(), E(), E()
+        x = T(ids)
+        self.prep(x, am, tt, pos, ext)
+        h = E()
+        self.emb(x, pos, tt, h)
+        return h, ext
+
+    def forward(self, ids, att_mask=None, n_layers=None):
+        """ids int64 [B,L] -> (sequence_output [B,L,H], pooled [B,H]) as torch fp32."""
+        h, ext = self.embed(torch.as_tensor(ids, dtype=torch.int64), att_mask)
+        for att, inter, out in self.layers[:n_layers]:
+            ao, ap, io, ho = E(), E(), E(), E()
+            att(h, ext, ao, ap, False)
+            inter(ao, io)
+            out(io, ao, ho)
+            h = ho
+        pooled = None
+        if self.pooler is not None:
+            sp, po = E(), E()
+            self.seqpool(h, sp)
+            self.pooler(sp, po)
+            pooled = back(po)
+        return back(h), pooled
+
+    def forward_smart_batch(self, id_list, n_layers=None):
+        """list of int64 id sequences -> packed [1,sumL,H] (modeling_smart_pad.py:434-486)."""
+        lens = [int(len(i)) for i in id_list]
+        xs = []
+        for ids in id_list:
+            h, _ = self.embed(torch.as_tensor(ids, dtype=torch.int64).reshape(1, -1))
+            xs.append(back(h))
+        x = torch.cat(xs, 1)
+        mask = torch.zeros(len(lens), 1, max(lens))
+        for b, n in enumerate(lens):
+            mask[b, 0, n:] = -1e9
+        h = T(x)
+        for sb, inter, out in self.sb_layers[:n_layers]:
+            ao, ap, io, ho = E(), E(), E(), E()
+            sb(h, h, h, T(mask), "self", ao, ap, {}, lens, [], False, True, False, False)
+            inter(ao, io)
+            out(io, ao, ho)
+            h = ho
+        return back(h)
