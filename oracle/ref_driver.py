@@ -31,6 +31,18 @@ def load():
     path = build_ref.build(verbose=False)
     if path is None or not os.path.exists(path):
         raise RuntimeError("oracle/_ref is not built and the reference tree is not available")
+    # The OpenBLAS object was linked against a libgfortran that sits beside it but is not on the loader
+    # path: load those dependencies first.
+    import ctypes
+    import glob
+    blas = build_ref.find_openblas()
+    if blas:
+        for pat in ("libquadmath*", "libgfortran*"):
+            for dep in sorted(glob.glob(os.path.join(os.path.dirname(blas), pat))):
+                try:
+                    ctypes.CDLL(dep, mode=ctypes.RTLD_GLOBAL)
+                except OSError:
+                    pass
     spec = importlib.util.spec_from_file_location("turbo_transformers_cxx", path)
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
@@ -157,3 +169,19 @@ class RefBert:
             out(io, ao, ho)
             h = ho
         return back(h)
+
+
+def pack_gpt2_weights(hf_model):
+    """HF GPT2Model -> the dict layout oracle/restate.py:gpt2_model takes (Conv1D weights are already [in,out])."""
+    def n(p):
+        return p.detach().float().cpu().numpy().copy()
+    W = {"wte": n(hf_model.wte.weight), "wpe": n(hf_model.wpe.weight), "lnf_gamma": n(hf_model.ln_f.weight),
+         "lnf_beta": n(hf_model.ln_f.bias), "layers": []}
+    for b in hf_model.h:
+        W["layers"].append({
+            "attention": {"qkv_weight": n(b.attn.c_attn.weight), "qkv_bias": n(b.attn.c_attn.bias),
+                          "dense_weight": n(b.attn.c_proj.weight), "dense_bias": n(b.attn.c_proj.bias),
+                          "ln_gamma": n(b.ln_1.weight), "ln_beta": n(b.ln_1.bias)},
+            "ln2_gamma": n(b.ln_2.weight), "ln2_beta": n(b.ln_2.bias), "fc_weight": n(b.mlp.c_fc.weight),
+            "fc_bias": n(b.mlp.c_fc.bias), "proj_weight": n(b.mlp.c_proj.weight), "proj_bias": n(b.mlp.c_proj.bias)})
+    return W

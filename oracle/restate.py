@@ -348,6 +348,35 @@ def q_linear(x, wq, w_scale, bias):
     return (acc.astype(F32) * xs * F32(w_scale) + bias.astype(F32)).astype(F32)
 
 
+def q_bert_model(ids, W, num_heads, quantize_attention=True, att_mask=None):
+    """BERT forward with the benchmark's int8 scheme on the Linears (all six, or only the two feed-forward
+    ones as the reference's qmodeling_bert.py:13-45 did); attention, softmax and layer norms in fp32."""
+    def qlin(x, w, b):
+        wq, ws = q_quantize_weight(w)
+        return q_linear(x, wq, ws, b)
+
+    def flin(x, w, b):
+        return mat_mul(x, False, w, False) + b
+
+    _, tt, pos, ext = prepare_bert_masks(ids, att_mask)
+    x = bert_embedding(ids, pos, tt, W["embedding"])
+    B, L, H = x.shape
+    d = H // num_heads
+    alin = qlin if quantize_attention else flin
+    for lw in W["layers"]:
+        a = lw["attention"]
+        qkv = alin(x, a["qkv_weight"], a["qkv_bias"]).reshape(B, L, 3, H)
+        q, k, v = split_add_bias_transpose_for_score(qkv, np.zeros(3 * H, F32), num_heads)
+        p = apply_mask_and_softmax(batch_mat_mul(q, False, k, True, 1.0 / math.sqrt(float(d))), ext, 1.0)
+        ctx = transpose_for_score(batch_mat_mul(p, False, v, False))
+        o = alin(ctx, a["dense_weight"], a["dense_bias"]).reshape(B, L, H)
+        att = layer_norm(o + x, a["ln_gamma"], a["ln_beta"], 1e-12)
+        inter = gelu_tanh(qlin(att, lw["inter_weight"], lw["inter_bias"]))
+        out = qlin(inter, lw["out_weight"], lw["out_bias"]).reshape(B, L, H)
+        x = layer_norm(out + att, lw["out_ln_gamma"], lw["out_ln_beta"], 1e-12)
+    return x
+
+
 # --------------------------------------------------------------------------------------------------
 # G: GPT-2 block composed from the reference's pre-LN flags
 # --------------------------------------------------------------------------------------------------

@@ -1,0 +1,510 @@
+#include "layers.h"
+
+#include <algorithm>
+#include <cmath>
+
+namespace turbo_transformers {
+namespace layers {
+
+using core::Check;
+using core::DeviceContext;
+using core::Tensor;
+
+namespace {
+
+// dtype of a floating tensor as ttb_dtype; throws for anything else or for host memory.
+int FloatType(const Tensor& t, const char* what) {
+  TT_ENFORCE(!t.is_null(), "%s is null", what);
+  if (!t.on_gpu()) TT_THROW("%s is not on a CUDA device: this runtime has no CPU path", what);
+  int dt = core::ToTTBDtype(t.dtype());
+  TT_ENFORCE(dt == TTB_F32 || dt == TTB_F16 || dt == TTB_BF16, "%s must be fp32, fp16 or bf16", what);
+  return dt;
+}
+
+void SameTypeDevice(const Tensor& a, const Tensor& b, const char* what) {
+  TT_ENFORCE(core::SameType(a.dtype(), b.dtype()), "%s: tensors differ in dtype", what);
+  TT_ENFORCE(a.device_type() == b.device_type() && a.device_id() == b.device_id(), "%s: tensors are on different devices", what);
+}
+
+std::vector<int64_t> ShapeOf(const Tensor& t) {
+  std::vector<int64_t> s(t.n_dim());
+  for (size_t i = 0; i < s.size(); ++i) s[i] = t.shape((int)i);
+  return s;
+}
+
+std::vector<int64_t> WithLast(const Tensor& t, int64_t last) {
+  auto s = ShapeOf(t);
+  s.back() = last;
+  return s;
+}
+
+// Which of the reference's two mask forms a tensor is (softmax.cpp:93-102): one row per batch or per query.
+bool MaskIs2D(const Tensor& m) {
+  return m.n_dim() == 2 || (m.n_dim() == 3 && m.shape(1) == 1) || (m.n_dim() == 4 && m.shape(2) == 1);
+}
+
+}  // namespace
+
+// ===================================================================================================
+// PackedLinear
+// ===================================================================================================
+const void* PackedLinear::Packed(bool is_trans) const {
+  std::lock_guard<std::mutex> g(cache_->mu);
+  Tensor& p = cache_->packed[is_trans ? 1 : 0];
+  if (p.is_null()) {
+    const int dt = FloatType(weight_, "linear weight");
+    const int64_t K = in_dim(is_trans), N = out_dim(is_trans);
+    ttb_ctx* c = DeviceContext(weight_.device_id());
+    p.Reshape(weight_.dtype(), {N, K}, kDLCUDA, weight_.device_id(), "linear/packed_weight");
+    Check(ttb_prepack_weight(c, dt, weight_.raw(), is_trans ? 1 : 0, K, N, dt, p.raw_mut()), c, "prepack_weight");
+  }
+  return p.raw();
+}
+
+void PackedLinear::Int8(bool is_trans, const int8_t** wq, const float** scale) const {
+  std::lock_guard<std::mutex> g(cache_->mu);
+  const int i = is_trans ? 1 : 0;
+  if (cache_->q[i].is_null()) {
+    const int dt = FloatType(weight_, "linear weight");
+    const int64_t K = in_dim(is_trans), N = out_dim(is_trans);
+    ttb_ctx* c = DeviceContext(weight_.device_id());
+    cache_->q[i].Reshape(core::kInt8, {N, K}, kDLCUDA, weight_.device_id(), "linear/int8_weight");
+    cache_->qscale[i].Reshape(core::kFloat32, {1}, kDLCUDA, weight_.device_id(), "linear/int8_scale");
+    Check(ttb_prepack_weight_int8(c, dt, weight_.raw(), i, K, N, cache_->q[i].mutableData<int8_t>(),
+                                  cache_->qscale[i].mutableData<float>()),
+          c, "prepack_weight_int8");
+  }
+  *wq = cache_->q[i].data<int8_t>();
+  *scale = cache_->qscale[i].data<float>();
+}
+
+void PackedLinear::Forward(const Tensor& x, int64_t M, int epilogue, const void* residual, void* out, bool is_trans,
+                           const char* name) const {
+  const int dt = FloatType(x, name);
+  SameTypeDevice(x, weight_, name);
+  const int64_t K = in_dim(is_trans), N = out_dim(is_trans);
+  TT_ENFORCE_EQ(x.shape(-1), K, "%s: input width %lld does not match the weight's %lld", name, (long long)x.shape(-1), (long long)K);
+  ttb_ctx* c = DeviceContext(x.device_id());
+  const void* bias = bias_.is_null() ? nullptr : bias_.raw();
+  if (!bias && epilogue == TTB_EPI_BIAS) epilogue = TTB_EPI_NONE;
+  if (dt == TTB_F32) {
+    // exact path: the reference's sequence MatMul -> elementwise kernel
+    Check(ttb_matmul(c, dt, x.raw(), 0, weight_.raw(), is_trans ? 1 : 0, M, N, K, 1.0f, 0.0f, out), c, name);
+    switch (epilogue) {
+      case TTB_EPI_NONE: break;
+      case TTB_EPI_BIAS: Check(ttb_add_bias(c, dt, out, bias, M, N), c, name); break;
+      case TTB_EPI_BIAS_GELU: Check(ttb_add_bias_act(c, dt, out, bias, M, N, TTB_ACT_GELU), c, name); break;
+      case TTB_EPI_BIAS_TANH: Check(ttb_add_bias_act(c, dt, out, bias, M, N, TTB_ACT_TANH), c, name); break;
+      case TTB_EPI_BIAS_RESIDUAL: Check(ttb_add_input_bias(c, dt, out, residual, bias, M, N, out), c, name); break;
+      default: TT_THROW("%s: unknown epilogue %d", name, epilogue);
+    }
+    return;
+  }
+  if (use_int8_) {
+    const int8_t* wq;
+    const float* ws;
+    Int8(is_trans, &wq, &ws);
+    Tensor xq(nullptr), xs(nullptr);
+    xq.Reshape(core::kInt8, {M, K}, kDLCUDA, x.device_id(), "linear/int8_activations");
+    xs.Reshape(core::kFloat32, {M}, kDLCUDA, x.device_id(), "linear/int8_row_scales");
+    Check(ttb_quantize_rows_int8(c, dt, x.raw(), M, K, xq.mutableData<int8_t>(), xs.mutableData<float>()), c, name);
+    Check(ttb_linear_int8(c, dt, xq.data<int8_t>(), xs.data<float>(), wq, ws, bias, residual, N, M, N, K, epilogue, out, N), c, name);
+    return;
+  }
+  Check(ttb_linear(c, dt, x.raw(), K, Packed(is_trans), bias, residual, N, M, N, K, epilogue, out, N), c, name);
+}
+
+// ===================================================================================================
+// BERTEmbedding
+// ===================================================================================================
+void BERTEmbedding::EnforceShapeAndType() const {
+  TT_ENFORCE_EQ(word_embedings_.n_dim(), 2, "word embeddings must be a matrix");
+  TT_ENFORCE_EQ(position_embeddings_.n_dim(), 2, "position embeddings must be a matrix");
+  TT_ENFORCE_EQ(token_type_embeddings_.n_dim(), 2, "token type embeddings must be a matrix");
+  TT_ENFORCE_EQ(word_embedings_.shape(1), position_embeddings_.shape(1), "embedding widths differ");
+  TT_ENFORCE_EQ(word_embedings_.shape(1), layer_norm_weights_.shape(0), "layer norm width differs from the embedding width");
+}
+
+void BERTEmbedding::operator()(const Tensor& input_ids, const Tensor& position_ids, const Tensor& token_type_ids,
+                               Tensor* output_tensor) const {
+  TT_ENFORCE_EQ(input_ids.n_dim(), 2, "The input ids should be a matrix with shape [BatchSize, SeqLen].");
+  TT_ENFORCE(output_tensor, "The output tensor should not be nullptr.");
+  const int dt = FloatType(word_embedings_, "word embeddings");
+  TT_ENFORCE(input_ids.on_gpu(), "input ids must be on the GPU");
+  const int64_t B = input_ids.shape(0), L = input_ids.shape(1), H = word_embedings_.shape(1);
+  const int dev = input_ids.device_id();
+  ttb_ctx* c = DeviceContext(dev);
+  output_tensor->Reshape(word_embedings_.dtype(), {B, L, H}, kDLCUDA, dev, "BERTEmbedding/Reshape");
+  Check(ttb_embedding_ln(c, dt, input_ids.data<int64_t>(), position_ids.is_null() ? nullptr : position_ids.data<int64_t>(),
+                         token_type_ids.is_null() ? nullptr : token_type_ids.data<int64_t>(), nullptr, B, L, B * L,
+                         word_embedings_.raw(), position_embeddings_.raw(), token_type_embeddings_.raw(),
+                         layer_norm_weights_.raw(), layer_norm_bias_.raw(), H, word_embedings_.shape(0),
+                         position_embeddings_.shape(0), token_type_embeddings_.shape(0), 1e-12f, output_tensor->raw_mut()),
+        c, "BERTEmbedding");
+}
+
+void BERTEmbedding::Packed(const Tensor& input_ids, const std::vector<int64_t>& seq_lens, Tensor* output_tensor) const {
+  const int dt = FloatType(word_embedings_, "word embeddings");
+  TT_ENFORCE(input_ids.on_gpu(), "input ids must be on the GPU");
+  const int64_t T = input_ids.numel(), H = word_embedings_.shape(1);
+  TT_ENFORCE_EQ(T, std::accumulate(seq_lens.begin(), seq_lens.end(), (int64_t)0), "ids do not match the sequence lengths");
+  const int dev = input_ids.device_id();
+  ttb_ctx* c = DeviceContext(dev);
+  output_tensor->Reshape(word_embedings_.dtype(), {1, T, H}, kDLCUDA, dev, "BERTEmbedding/Reshape");
+  Check(ttb_embedding_ln(c, dt, input_ids.data<int64_t>(), nullptr, nullptr, core::CuSeqlens(dev, seq_lens),
+                         (int64_t)seq_lens.size(), 0, T, word_embedings_.raw(), position_embeddings_.raw(),
+                         token_type_embeddings_.raw(), layer_norm_weights_.raw(), layer_norm_bias_.raw(), H,
+                         word_embedings_.shape(0), position_embeddings_.shape(0), token_type_embeddings_.shape(0), 1e-12f,
+                         output_tensor->raw_mut()),
+        c, "BERTEmbedding/packed");
+}
+
+// ===================================================================================================
+// MultiHeadedAttention
+// ===================================================================================================
+MultiHeadedAttention::MultiHeadedAttention(Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor dense_weight, Tensor dense_bias,
+                                           Tensor qkv_weight, Tensor qkv_bias, int64_t num_attention_heads)
+    : qkv_(std::move(qkv_weight), std::move(qkv_bias)), dense_(std::move(dense_weight), std::move(dense_bias)),
+      layernorm_gamma_(nullptr), layernorm_beta_(nullptr), num_attention_heads_(num_attention_heads) {
+  EnforceShapeAndType();
+}
+
+MultiHeadedAttention::MultiHeadedAttention(Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor dense_weight, Tensor dense_bias,
+                                           Tensor qkv_weight, Tensor qkv_bias, Tensor layernorm_gamma, Tensor layernorm_beta,
+                                           int64_t num_attention_heads)
+    : qkv_(std::move(qkv_weight), std::move(qkv_bias)), dense_(std::move(dense_weight), std::move(dense_bias)),
+      layernorm_gamma_(std::move(layernorm_gamma)), layernorm_beta_(std::move(layernorm_beta)),
+      num_attention_heads_(num_attention_heads) {
+  EnforceShapeAndType();
+}
+
+void MultiHeadedAttention::EnforceShapeAndType() const {
+  TT_ENFORCE(!qkv_.weight().is_null() && !qkv_.bias().is_null(), "self attention needs the fused qkv weight and bias");
+  TT_ENFORCE_EQ(qkv_.weight().n_dim(), 2, "qkv weight must be a matrix");
+  TT_ENFORCE_EQ(dense_.weight().n_dim(), 2, "dense weight must be a matrix");
+  TT_ENFORCE(num_attention_heads_ > 0, "number of heads must be positive");
+}
+
+void MultiHeadedAttention::operator()(const Tensor& key_tensor, const Tensor& value_tensor, const Tensor& query_tensor,
+                                      const Tensor& attention_mask, const std::string& attn_type, Tensor* output,
+                                      Tensor* att_score, std::unordered_map<std::string, Tensor*> layer_cache,
+                                      bool pre_layernorm, bool post_layernorm, bool post_add_input, bool is_trans_weight) const {
+  TT_ENFORCE_EQ(key_tensor.n_dim(), 3, "The key_tensor should be a matrix with shape [batch_size, key_seq_len, hidden_size].");
+  TT_ENFORCE_EQ(value_tensor.n_dim(), 3, "The value_tensor should be a matrix with shape [batch_size, key_seq_len, hidden_size].");
+  TT_ENFORCE_EQ(query_tensor.n_dim(), 3, "The query_tensors should be a matrix with shape [batch_size, query_seq_len, hidden_size].");
+  if (attn_type != "self") {
+    if (attn_type == "context") TT_THROW("context (encoder-decoder) attention is outside the scope of this runtime");
+    TT_THROW("attn_type should be context or self.");
+  }
+  for (auto& kv : layer_cache)
+    if (kv.second && !kv.second->is_null()) TT_THROW("incremental decoding caches (layer_cache) are outside the scope of this runtime");
+  Run(query_tensor, attention_mask, nullptr, output, att_score, pre_layernorm, post_layernorm, post_add_input, is_trans_weight);
+}
+
+void MultiHeadedAttentionSmartBatch::operator()(const Tensor& key_tensor, const Tensor& value_tensor, const Tensor& query_tensor,
+                                                const Tensor& attention_mask, const std::string& attn_type, Tensor* output,
+                                                Tensor* att_score, std::unordered_map<std::string, Tensor*> layer_cache,
+                                                const std::vector<int64_t>& query_seq_len_list,
+                                                const std::vector<int64_t>& key_seq_len_list, bool pre_layernorm,
+                                                bool post_layernorm, bool post_add_input, bool is_trans_weight) const {
+  TT_ENFORCE_EQ(query_tensor.n_dim(), 3, "The query_tensors should be a matrix with shape [1, sum_query_seq_len, hidden_size].");
+  TT_ENFORCE_EQ(query_tensor.shape(0), 1, "The packed query tensor's first dimension must be 1.");
+  if (attn_type != "self") {
+    if (attn_type == "context") TT_THROW("context (encoder-decoder) attention is outside the scope of this runtime");
+    TT_THROW("attn_type should be context or self.");
+  }
+  for (auto& kv : layer_cache)
+    if (kv.second && !kv.second->is_null()) TT_THROW("incremental decoding caches (layer_cache) are outside the scope of this runtime");
+  TT_ENFORCE(!query_seq_len_list.empty(), "query_seq_len_list is empty");
+  const int64_t total = std::accumulate(query_seq_len_list.begin(), query_seq_len_list.end(), (int64_t)0);
+  TT_ENFORCE_EQ(query_tensor.shape(1), total, "The query_tensor shape 1 should be the sum of seq_len_list.");
+  Run(query_tensor, attention_mask, &query_seq_len_list, output, att_score, pre_layernorm, post_layernorm, post_add_input,
+      is_trans_weight);
+}
+
+void BertAttention::operator()(const Tensor& input_tensor, const Tensor& attention_mask, Tensor* output, Tensor* attn,
+                               bool is_trans_weight) const {
+  // bert_attention.cpp:29-47 of the reference: self attention with post layer norm
+  TT_ENFORCE_EQ(input_tensor.n_dim(), 3, "The input should be [batch_size, seq_len, hidden_size].");
+  Run(input_tensor, attention_mask, nullptr, output, attn, false, true, false, is_trans_weight);
+}
+
+void MultiHeadedAttention::Run(const Tensor& x, const Tensor& attention_mask, const std::vector<int64_t>* seq_lens, Tensor* output,
+                               Tensor* att_score, bool pre_layernorm, bool post_layernorm, bool post_add_input,
+                               bool is_trans_weight) const {
+  TT_ENFORCE(output, "The output tensor should not be nullptr.");
+  const int dt = FloatType(x, "attention input");
+  SameTypeDevice(x, qkv_.weight(), "attention");
+  const int dev = x.device_id();
+  ttb_ctx* c = DeviceContext(dev);
+  const int64_t H = x.shape(2), heads = num_attention_heads_, d = H / heads;
+  TT_ENFORCE_EQ(d * heads, H, "hidden size %lld is not divisible by %lld heads", (long long)H, (long long)heads);
+  TT_ENFORCE_EQ(qkv_.out_dim(is_trans_weight), 3 * H, "qkv weight does not map hidden -> 3*hidden");
+  const int64_t B = seq_lens ? (int64_t)seq_lens->size() : x.shape(0);
+  const int64_t T = seq_lens ? x.shape(1) : x.shape(0) * x.shape(1);
+  const int64_t maxL = seq_lens ? *std::max_element(seq_lens->begin(), seq_lens->end()) : x.shape(1);
+  if (pre_layernorm || post_layernorm) TT_ENFORCE(!layernorm_gamma_.is_null(), "this attention layer was built without layer norm weights");
+  const float scale = 1.0f / std::sqrt((float)d);
+  const auto out_shape = ShapeOf(x);
+
+  // 1) optional pre layer norm into a temporary (the input itself is the residual)
+  Tensor normed(nullptr);
+  const Tensor* gemm_in = &x;
+  if (pre_layernorm) {
+    normed.Reshape(x.dtype(), out_shape, kDLCUDA, dev, "self/layernorm/Reshape");
+    Check(ttb_layernorm(c, dt, x.raw(), normed.raw_mut(), layernorm_gamma_.raw(), layernorm_beta_.raw(), T, H, pre_ln_eps_), c,
+          "self/layernorm");
+    gemm_in = &normed;
+  }
+
+  const bool fused = dt != TTB_F32 && !materialize_scores_ && d == 64;
+  Tensor context(nullptr);  // [T, H] token-major attention output
+  context.Reshape(x.dtype(), {T, H}, kDLCUDA, dev, "batch_gemm4/Reshape");
+
+  if (fused) {
+    // 2) QKV projection with the bias in the GEMM epilogue, left token-major [T, 3H]
+    Tensor qkv(nullptr);
+    qkv.Reshape(x.dtype(), {T, 3 * H}, kDLCUDA, dev, "self/qkv_out1/Reshape");
+    qkv_.Forward(*gemm_in, T, TTB_EPI_BIAS, nullptr, qkv.raw_mut(), is_trans_weight, "self/gemm012_fused");
+    // 3) attention over packed tokens; the mask tensor (if any) is applied as the reference does
+    const int32_t* cu = seq_lens ? core::CuSeqlens(dev, *seq_lens) : core::UniformCuSeqlens(dev, B, maxL);
+    const float* mask = nullptr;
+    int64_t mbs = 0, mrs = 0;
+    if (!attention_mask.is_null()) {
+      TT_ENFORCE(attention_mask.on_gpu() && core::SameType(attention_mask.dtype(), core::kFloat32),
+                 "the attention mask must be an fp32 tensor on the GPU");
+      mask = attention_mask.data<float>();
+      const int64_t Lk = attention_mask.shape(-1);
+      TT_ENFORCE_GE(Lk, maxL, "attention mask is shorter than the longest sequence");
+      if (MaskIs2D(attention_mask)) { mbs = Lk; mrs = 0; }
+      else { mrs = Lk; mbs = attention_mask.shape(-2) * Lk; }
+    }
+    Check(ttb_attention_fwd(c, dt, qkv.raw(), cu, B, maxL, heads, d, mask, mbs, mrs, causal_ ? 1 : 0, scale, context.raw_mut()), c,
+          "attention_fwd");
+    if (att_score) *att_score = Tensor(nullptr);
+  } else {
+    // The reference's own sequence (multi_headed_attention.cpp:168-232,320-354), scores materialised.
+    TT_ENFORCE(!causal_ || !attention_mask.is_null(), "the unfused path needs an explicit mask tensor for causal attention");
+    Tensor qkv(nullptr), q(nullptr), k(nullptr), v(nullptr), ctx_heads(nullptr), scores_local(nullptr);
+    qkv.Reshape(x.dtype(), {T, 3 * H}, kDLCUDA, dev, "self/qkv_out1/Reshape");
+    qkv_.Forward(*gemm_in, T, TTB_EPI_NONE, nullptr, qkv.raw_mut(), is_trans_weight, "self/gemm012_fused");
+    const std::vector<int64_t> head_shape{B, heads, maxL, d};
+    q.Reshape(x.dtype(), head_shape, kDLCUDA, dev, "self/q/Reshape");
+    k.Reshape(x.dtype(), head_shape, kDLCUDA, dev, "self/k/Reshape");
+    v.Reshape(x.dtype(), head_shape, kDLCUDA, dev, "self/v/Reshape");
+    const int32_t* cu = seq_lens ? core::CuSeqlens(dev, *seq_lens) : nullptr;
+    Check(ttb_split_add_bias_transpose_pad(c, dt, qkv.raw(), qkv_.bias().raw(), cu, B, maxL, heads, d, q.raw_mut(), k.raw_mut(),
+                                           v.raw_mut()),
+          c, "self/SplitAddBiasTransposeForScore");
+    Tensor* scores = att_score ? att_score : &scores_local;
+    scores->Reshape(x.dtype(), {B, heads, maxL, maxL}, kDLCUDA, dev, "batch_gemm3/Reshape");
+    Check(ttb_batch_matmul(c, dt, q.raw(), 0, k.raw(), 1, B * heads, maxL, maxL, d, scale, 0.0f, scores->raw_mut()), c, "batch_gemm3");
+    const float* mask = nullptr;
+    int is2d = 1;
+    if (!attention_mask.is_null()) {
+      TT_ENFORCE(attention_mask.on_gpu() && core::SameType(attention_mask.dtype(), core::kFloat32),
+                 "the attention mask must be an fp32 tensor on the GPU");
+      TT_ENFORCE_EQ(attention_mask.shape(-1), maxL, "attention mask width must equal the (padded) key length");
+      mask = attention_mask.data<float>();
+      is2d = MaskIs2D(attention_mask) ? 1 : 0;
+    }
+    Check(ttb_mask_softmax(c, dt, scores->raw_mut(), mask, B, heads, maxL, maxL, 1.0f, is2d), c, "ApplyMaskAndSoftmax");
+    ctx_heads.Reshape(x.dtype(), head_shape, kDLCUDA, dev, "ApplyMaskAndSoftmax/Reshape");
+    Check(ttb_batch_matmul(c, dt, scores->raw(), 0, v.raw(), 0, B * heads, maxL, d, maxL, 1.0f, 0.0f, ctx_heads.raw_mut()), c,
+          "batch_gemm4");
+    Check(ttb_transpose_for_score_pad(c, dt, ctx_heads.raw(), cu, B, maxL, heads, d, context.raw_mut()), c, "TransposeForScore");
+  }
+
+  // 4) output projection and what follows it
+  output->Reshape(x.dtype(), out_shape, kDLCUDA, dev, "gemm5/Reshape");
+  if (post_add_input) {
+    dense_.Forward(context, T, TTB_EPI_BIAS_RESIDUAL, x.raw(), output->raw_mut(), is_trans_weight, "gemm5");
+  } else if (!post_layernorm) {
+    dense_.Forward(context, T, TTB_EPI_BIAS, nullptr, output->raw_mut(), is_trans_weight, "gemm5");
+  } else if (dt == TTB_F32) {
+    dense_.Forward(context, T, TTB_EPI_NONE, nullptr, output->raw_mut(), is_trans_weight, "gemm5");
+    Check(ttb_add_bias_layernorm(c, dt, output->raw_mut(), x.raw(), dense_.bias().raw(), layernorm_gamma_.raw(),
+                                 layernorm_beta_.raw(), T, H, 1e-12f),
+          c, "AddBiasLayerNorm");
+  } else {
+    dense_.Forward(context, T, TTB_EPI_BIAS_RESIDUAL, x.raw(), output->raw_mut(), is_trans_weight, "gemm5");
+    Check(ttb_layernorm(c, dt, output->raw(), output->raw_mut(), layernorm_gamma_.raw(), layernorm_beta_.raw(), T, H, 1e-12f), c,
+          "AddBiasLayerNorm");
+  }
+}
+
+// ===================================================================================================
+// feed-forward, pooler, pooling, masks
+// ===================================================================================================
+void BertIntermediate::EnforceShapeAndType() const {
+  TT_ENFORCE_EQ(dense_.weight().n_dim(), 2, "dense weight must be matrix");
+  TT_ENFORCE_EQ(dense_.bias().n_dim(), 1, "dense bias must be vector");
+  TT_ENFORCE_EQ(dense_.weight().shape(1), dense_.bias().shape(0), "weight and bias shape mismatch");
+}
+
+void BertIntermediate::operator()(const Tensor& input_tensor, Tensor* output_tensor) const {
+  TT_ENFORCE(output_tensor, "The output tensor should not be nullptr.");
+  FloatType(input_tensor, "BertIntermediate input");
+  output_tensor->Reshape(input_tensor.dtype(), WithLast(input_tensor, dense_.out_dim(false)), kDLCUDA, input_tensor.device_id(),
+                         "BertIntermediate/Reshape");
+  dense_.Forward(input_tensor, input_tensor.rows(), TTB_EPI_BIAS_GELU, nullptr, output_tensor->raw_mut(), false, "BertIntermediate");
+}
+
+void BertOutput::EnforceShapeAndType() const {
+  TT_ENFORCE_EQ(dense_.weight().n_dim(), 2, "dense weight must be matrix");
+  TT_ENFORCE_EQ(dense_.bias().n_dim(), 1, "dense bias must be vector");
+  TT_ENFORCE_EQ(dense_.weight().shape(1), dense_.bias().shape(0), "weight and bias shape mismatch");
+  TT_ENFORCE_EQ(layer_norm_weight_.shape(0), dense_.weight().shape(1), "layer norm width mismatch");
+}
+
+void BertOutput::operator()(const Tensor& hidden_states, const Tensor& input_tensor, Tensor* output_tensor) const {
+  TT_ENFORCE(output_tensor, "The output tensor should not be nullptr.");
+  const int dt = FloatType(hidden_states, "BertOutput input");
+  SameTypeDevice(hidden_states, input_tensor, "BertOutput");
+  const int64_t M = hidden_states.rows(), N = dense_.out_dim(false);
+  TT_ENFORCE_EQ(input_tensor.numel(), M * N, "BertOutput: residual shape mismatch");
+  ttb_ctx* c = DeviceContext(hidden_states.device_id());
+  output_tensor->Reshape(hidden_states.dtype(), WithLast(hidden_states, N), kDLCUDA, hidden_states.device_id(), "BertOutput/Reshape");
+  if (dt == TTB_F32) {
+    dense_.Forward(hidden_states, M, TTB_EPI_NONE, nullptr, output_tensor->raw_mut(), false, "BertOutput/MatMul");
+    Check(ttb_add_bias_layernorm(c, dt, output_tensor->raw_mut(), input_tensor.raw(), dense_.bias().raw(), layer_norm_weight_.raw(),
+                                 layer_norm_bias_.raw(), M, N, 1e-12f),
+          c, "BertOutput/AddBiasLayerNorm");
+  } else {
+    dense_.Forward(hidden_states, M, TTB_EPI_BIAS_RESIDUAL, input_tensor.raw(), output_tensor->raw_mut(), false, "BertOutput/MatMul");
+    Check(ttb_layernorm(c, dt, output_tensor->raw(), output_tensor->raw_mut(), layer_norm_weight_.raw(), layer_norm_bias_.raw(), M, N,
+                        1e-12f),
+          c, "BertOutput/AddBiasLayerNorm");
+  }
+}
+
+void BertPooler::EnforceShapeAndType() const {
+  TT_ENFORCE_EQ(dense_.weight().n_dim(), 2, "dense weight must be matrix");
+  TT_ENFORCE_EQ(dense_.bias().n_dim(), 1, "dense bias must be vector");
+  TT_ENFORCE_EQ(dense_.weight().shape(1), dense_.bias().shape(0), "weight and bias shape mismatch %lld, %lld",
+                (long long)dense_.weight().shape(1), (long long)dense_.bias().shape(0));
+}
+
+void BertPooler::operator()(const Tensor& input_tensor, Tensor* output_tensor) const {
+  TT_ENFORCE_EQ(input_tensor.n_dim(), 2, "input's dim should be 2, not %zu", input_tensor.n_dim());
+  FloatType(input_tensor, "BertPooler input");
+  output_tensor->Reshape(input_tensor.dtype(), {input_tensor.shape(0), dense_.out_dim(false)}, kDLCUDA, input_tensor.device_id(),
+                         "BertPooler");
+  dense_.Forward(input_tensor, input_tensor.shape(0), TTB_EPI_BIAS_TANH, nullptr, output_tensor->raw_mut(), false, "BertPooler");
+}
+
+SequencePool::SequencePool(const std::string& pool_type) {
+  if (pool_type == "First") pool_type_ = TTB_POOL_FIRST;
+  else if (pool_type == "Last") pool_type_ = TTB_POOL_LAST;
+  else if (pool_type == "Mean") pool_type_ = TTB_POOL_MEAN;
+  else if (pool_type == "Max") pool_type_ = TTB_POOL_MAX;
+  else TT_THROW("The input pool type (%s) is not supported.", pool_type.c_str());
+}
+
+void SequencePool::operator()(const Tensor& input, Tensor* output) const {
+  TT_ENFORCE_EQ(input.n_dim(), 3, "The input's dim should be 3, but the input's dim is %zu", input.n_dim());
+  const int dt = FloatType(input, "SequencePool input");
+  ttb_ctx* c = DeviceContext(input.device_id());
+  output->Reshape(input.dtype(), {input.shape(0), input.shape(2)}, kDLCUDA, input.device_id(), "SequencePool/Reshape");
+  Check(ttb_seq_pool(c, dt, input.raw(), input.shape(0), input.shape(1), input.shape(2), pool_type_, output->raw_mut()), c, "SeqPool");
+}
+
+void SequencePool::Packed(const Tensor& input, const std::vector<int64_t>& seq_lens, Tensor* output) const {
+  const int dt = FloatType(input, "SequencePool input");
+  const int dev = input.device_id();
+  ttb_ctx* c = DeviceContext(dev);
+  const int64_t B = (int64_t)seq_lens.size(), H = input.shape(-1);
+  output->Reshape(input.dtype(), {B, H}, kDLCUDA, dev, "SequencePool/Reshape");
+  Check(ttb_seq_pool_varlen(c, dt, input.raw(), core::CuSeqlens(dev, seq_lens), B, H, pool_type_, output->raw_mut()), c, "SeqPool/packed");
+}
+
+void PrepareBertMasks::operator()(const Tensor& inputs, Tensor* att_mask, Tensor* seq_type, Tensor* position_ids,
+                                  Tensor* extended_attention_mask) const {
+  TT_ENFORCE_EQ(inputs.n_dim(), 2, "inputs must be [batch, seq_len]");
+  TT_ENFORCE(inputs.on_gpu(), "inputs must be on the GPU: this runtime has no CPU path");
+  const int64_t B = inputs.shape(0), L = inputs.shape(1);
+  const int dev = inputs.device_id();
+  ttb_ctx* c = DeviceContext(dev);
+  int64_t *pos_out = nullptr, *type_out = nullptr, *mask_out = nullptr;
+  const int64_t* mask_in = nullptr;
+  if (position_ids->is_null()) pos_out = position_ids->Reshape<int64_t>({B, L}, kDLCUDA, dev, "PrepareBertMasks/possitionids/Reshape");
+  if (seq_type->is_null()) type_out = seq_type->Reshape<int64_t>({B, L}, kDLCUDA, dev, "PrepareBertMasks/seqids/Reshape");
+  if (att_mask->is_null()) mask_out = att_mask->Reshape<int64_t>({B, L}, kDLCUDA, dev, "PrepareBertMasks/attmask/Reshape");
+  else mask_in = att_mask->data<int64_t>();
+  float* ext = extended_attention_mask->Reshape<float>({B, 1, 1, L}, kDLCUDA, dev, "PrepareBertMasks/extendedattnmask/Reshape");
+  Check(ttb_prepare_bert_masks(c, B, L, mask_in, mask_out, type_out, pos_out, ext), c, "PrepareBertMasks");
+}
+
+void PositionwiseFeedForward::set_activation(const std::string& act) {
+  if (act == "relu") act_ = TTB_ACT_RELU;
+  else if (act == "gelu") act_ = TTB_ACT_GELU;
+  else TT_THROW("activation must be relu or gelu");
+}
+
+void PositionwiseFeedForward::operator()(const Tensor& x, Tensor* output, bool is_trans_weight) const {
+  const int dt = FloatType(x, "FFN input");
+  const int dev = x.device_id();
+  ttb_ctx* c = DeviceContext(dev);
+  const int64_t M = x.rows(), H = x.shape(-1), F = dense1_.out_dim(is_trans_weight);
+  TT_ENFORCE_EQ(dense1_.in_dim(is_trans_weight), H, "dense weight and input tensor should have the same model_dim.");
+  Tensor normed(nullptr), inter(nullptr);
+  normed.Reshape(x.dtype(), ShapeOf(x), kDLCUDA, dev, "FFN/LayerNorm/Reshape");
+  Check(ttb_layernorm(c, dt, x.raw(), normed.raw_mut(), layer_norm_weight_.raw(), layer_norm_bias_.raw(), M, H, eps_), c, "FFN/LayerNorm");
+  inter.Reshape(x.dtype(), {M, F}, kDLCUDA, dev, "FFN/inter/Reshape");
+  if (act_ == TTB_ACT_GELU) {
+    dense1_.Forward(normed, M, TTB_EPI_BIAS_GELU, nullptr, inter.raw_mut(), is_trans_weight, "FFN/gemm0");
+  } else {
+    dense1_.Forward(normed, M, TTB_EPI_NONE, nullptr, inter.raw_mut(), is_trans_weight, "FFN/gemm0");
+    Check(ttb_add_bias_act(c, dt, inter.raw_mut(), dense1_.bias().raw(), M, F, TTB_ACT_RELU), c, "FFN/AddBiasAct");
+  }
+  output->Reshape(x.dtype(), ShapeOf(x), kDLCUDA, dev, "FFN/Reshape");
+  dense2_.Forward(inter, M, TTB_EPI_BIAS_RESIDUAL, x.raw(), output->raw_mut(), is_trans_weight, "FFN/gemm1");
+}
+
+void FusedAddBiasGELU::operator()(Tensor* t) const {
+  const int dt = FloatType(*t, "FusedAddBiasGELU input");
+  ttb_ctx* c = DeviceContext(t->device_id());
+  Check(ttb_add_bias_act(c, dt, t->raw_mut(), bias_.raw(), t->rows(), t->shape(-1), TTB_ACT_GELU), c, "FusedAddBiasGELU");
+}
+
+void FusedAddBiasLayerNorm::operator()(const Tensor& input_tensor, Tensor* output_tensor) const {
+  const int dt = FloatType(*output_tensor, "FusedAddBiasLayerNorm output");
+  SameTypeDevice(input_tensor, *output_tensor, "FusedAddBiasLayerNorm");
+  ttb_ctx* c = DeviceContext(output_tensor->device_id());
+  Check(ttb_add_bias_layernorm(c, dt, output_tensor->raw_mut(), input_tensor.raw(), bias_.raw(), norm_weight_.raw(), norm_bias_.raw(),
+                               output_tensor->rows(), output_tensor->shape(-1), 1e-12f),
+        c, "FusedAddBiasLayerNorm");
+}
+
+void LayerNorm::operator()(const Tensor& input, Tensor* output) const {
+  const int dt = FloatType(input, "LayerNorm input");
+  ttb_ctx* c = DeviceContext(input.device_id());
+  output->Reshape(input.dtype(), ShapeOf(input), kDLCUDA, input.device_id(), "LayerNorm/Reshape");
+  Check(ttb_layernorm(c, dt, input.raw(), output->raw_mut(), gamma_.raw(), beta_.raw(), input.rows(), input.shape(-1), eps_), c, "LayerNorm");
+}
+
+void TokenPositionEmbedding::operator()(const Tensor& input_ids, Tensor* output) const {
+  TT_ENFORCE_EQ(input_ids.n_dim(), 2, "The input ids should be a matrix with shape [BatchSize, SeqLen].");
+  const int dt = FloatType(token_, "token embeddings");
+  TT_ENFORCE(input_ids.on_gpu(), "input ids must be on the GPU");
+  const int64_t B = input_ids.shape(0), L = input_ids.shape(1), H = token_.shape(1);
+  const int dev = input_ids.device_id();
+  ttb_ctx* c = DeviceContext(dev);
+  Tensor pos(nullptr);
+  int64_t* pos_ids = pos.Reshape<int64_t>({B, L}, kDLCUDA, dev, "TokenPositionEmbedding/positions");
+  Check(ttb_prepare_bert_masks(c, B, L, nullptr, nullptr, nullptr, pos_ids, nullptr), c, "TokenPositionEmbedding/positions");
+  output->Reshape(token_.dtype(), {B, L, H}, kDLCUDA, dev, "TokenPositionEmbedding/Reshape");
+  Check(ttb_lookup_embedding(c, dt, output->raw_mut(), token_.raw(), input_ids.data<int64_t>(), B * L, H, token_.shape(0), 0), c,
+        "TokenPositionEmbedding/token");
+  Check(ttb_lookup_embedding(c, dt, output->raw_mut(), position_.raw(), pos_ids, B * L, H, position_.shape(0), 1), c,
+        "TokenPositionEmbedding/position");
+}
+
+void Linear::operator()(const Tensor& input, Tensor* output) const {
+  FloatType(input, "Linear input");
+  output->Reshape(input.dtype(), WithLast(input, dense_.out_dim(is_trans_)), kDLCUDA, input.device_id(), "Linear/Reshape");
+  dense_.Forward(input, input.rows(), TTB_EPI_BIAS, nullptr, output->raw_mut(), is_trans_, "Linear");
+}
+
+}  // namespace layers
+}  // namespace turbo_transformers

@@ -1,0 +1,271 @@
+// Layer classes with the names, constructor argument order and operator() signatures of the reference's
+// turbo_transformers/layers/*.h, re-implemented over the C ABI in include/ttb.h.
+//
+//   fp32 tensors  -> the reference's own op sequence on exact-precision kernels (MatMul, SplitAddBias...,
+//                    BatchMatMul, ApplyMaskAndSoftmax, ..., AddBiasLayerNorm), scores materialised
+//   fp16 / bf16   -> tcgen05 GEMMs with fused epilogues + one attention kernel over packed tokens
+//   int8          -> (after QuantizeInt8()) int8 tcgen05 GEMMs with dequantising epilogues
+// The dtype is taken from the weights handed to the constructor; activations must match it.
+// No layer keeps per-call state in members, so one object may be called from several host threads
+// (the reference serialised MultiHeadedAttention behind a global mutex).
+#pragma once
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "core.h"
+
+namespace turbo_transformers {
+namespace layers {
+
+// A Linear weight plus its lazily-built tensor-core re-layouts. The source tensor may alias memory owned
+// by the caller's framework and is never written.
+class PackedLinear {
+ public:
+  PackedLinear() : weight_(nullptr), bias_(nullptr) {}
+  PackedLinear(core::Tensor weight, core::Tensor bias) : weight_(std::move(weight)), bias_(std::move(bias)) {}
+  PackedLinear(PackedLinear&&) = default;
+  const core::Tensor& weight() const { return weight_; }
+  const core::Tensor& bias() const { return bias_; }
+  int64_t in_dim(bool is_trans) const { return weight_.shape(is_trans ? 1 : 0); }
+  int64_t out_dim(bool is_trans) const { return weight_.shape(is_trans ? 0 : 1); }
+  // K-major [N,K] copy in the weight's own 16-bit dtype (built on first use).
+  const void* Packed(bool is_trans) const;
+  // int8 [N,K] copy + device scale (built on first use).
+  void Int8(bool is_trans, const int8_t** wq, const float** scale) const;
+  void set_int8(bool on) { use_int8_ = on; }
+  bool use_int8() const { return use_int8_; }
+
+  // out[M,N] = epilogue(x[M,K] . W + bias); picks the kernel by dtype / int8 flag.
+  void Forward(const core::Tensor& x, int64_t M, int epilogue, const void* residual, void* out, bool is_trans,
+               const char* name) const;
+
+ private:
+  core::Tensor weight_, bias_;
+  bool use_int8_ = false;
+  struct Cache {
+    std::mutex mu;
+    core::Tensor packed[2]{core::Tensor(nullptr), core::Tensor(nullptr)};
+    core::Tensor q[2]{core::Tensor(nullptr), core::Tensor(nullptr)};
+    core::Tensor qscale[2]{core::Tensor(nullptr), core::Tensor(nullptr)};
+  };
+  std::unique_ptr<Cache> cache_{new Cache()};
+};
+
+class BERTEmbedding {
+ public:
+  BERTEmbedding(core::Tensor word_embeddings, core::Tensor position_embeddings, core::Tensor token_type_embeddings,
+                core::Tensor layer_norm_weights, core::Tensor layer_norm_bias, float dropout_rate = 0.f)
+      : word_embedings_(std::move(word_embeddings)), position_embeddings_(std::move(position_embeddings)),
+        token_type_embeddings_(std::move(token_type_embeddings)), layer_norm_weights_(std::move(layer_norm_weights)),
+        layer_norm_bias_(std::move(layer_norm_bias)) {
+    EnforceShapeAndType();
+  }
+  void EnforceShapeAndType() const;
+  void operator()(const core::Tensor& input_ids, const core::Tensor& position_ids, const core::Tensor& token_type_ids,
+                  core::Tensor* output_tensor) const;
+  // Packed variable-length form: ids [sumL], positions restart at 0 per sequence, types 0.
+  void Packed(const core::Tensor& input_ids, const std::vector<int64_t>& seq_lens, core::Tensor* output_tensor) const;
+
+ private:
+  core::Tensor word_embedings_, position_embeddings_, token_type_embeddings_, layer_norm_weights_, layer_norm_bias_;
+};
+
+class MultiHeadedAttention {
+ public:
+  MultiHeadedAttention(core::Tensor k_weight, core::Tensor k_bias, core::Tensor v_weight, core::Tensor v_bias,
+                       core::Tensor q_weight, core::Tensor q_bias, core::Tensor dense_weight, core::Tensor dense_bias,
+                       core::Tensor qkv_weight, core::Tensor qkv_bias, int64_t num_attention_heads);
+  MultiHeadedAttention(core::Tensor k_weight, core::Tensor k_bias, core::Tensor v_weight, core::Tensor v_bias,
+                       core::Tensor q_weight, core::Tensor q_bias, core::Tensor dense_weight, core::Tensor dense_bias,
+                       core::Tensor qkv_weight, core::Tensor qkv_bias, core::Tensor layernorm_gamma,
+                       core::Tensor layernorm_beta, int64_t num_attention_heads);
+  void EnforceShapeAndType() const;
+
+  void operator()(const core::Tensor& key_tensor, const core::Tensor& value_tensor, const core::Tensor& query_tensor,
+                  const core::Tensor& attention_mask, const std::string& attn_type, core::Tensor* output,
+                  core::Tensor* att_score, std::unordered_map<std::string, core::Tensor*> layer_cache,
+                  bool pre_layernorm = false, bool post_layernorm = false, bool post_add_input = false,
+                  bool is_trans_weight = false) const;
+
+  // Shared implementation: seq_lens == nullptr means a [B,L,H] batch of equal lengths, otherwise
+  // query_tensor is packed [1,sumL,H].
+  void Run(const core::Tensor& query_tensor, const core::Tensor& attention_mask, const std::vector<int64_t>* seq_lens,
+           core::Tensor* output, core::Tensor* att_score, bool pre_layernorm, bool post_layernorm, bool post_add_input,
+           bool is_trans_weight) const;
+
+  // 16-bit models skip the [B,heads,L,L] score tensor unless asked: it is the largest HBM round trip of
+  // the reference path. fp32 models always materialise it, as the reference does.
+  void set_materialize_scores(bool on) { materialize_scores_ = on; }
+  void set_pre_layernorm_eps(float eps) { pre_ln_eps_ = eps; }  // the reference hard-codes 1e-6
+  void set_causal(bool on) { causal_ = on; }                    // decoder-style self-attention without a mask tensor
+  void QuantizeInt8() { qkv_.set_int8(true); dense_.set_int8(true); }
+  int64_t num_attention_heads() const { return num_attention_heads_; }
+
+ private:
+  PackedLinear qkv_, dense_;
+  core::Tensor layernorm_gamma_, layernorm_beta_;
+  int64_t num_attention_heads_;
+  bool materialize_scores_ = false, causal_ = false;
+  float pre_ln_eps_ = 1e-6f;
+};
+
+class MultiHeadedAttentionSmartBatch : public MultiHeadedAttention {
+ public:
+  using MultiHeadedAttention::MultiHeadedAttention;
+  void operator()(const core::Tensor& key_tensor, const core::Tensor& value_tensor, const core::Tensor& query_tensor,
+                  const core::Tensor& attention_mask, const std::string& attn_type, core::Tensor* output,
+                  core::Tensor* att_score, std::unordered_map<std::string, core::Tensor*> layer_cache,
+                  const std::vector<int64_t>& query_seq_len_list, const std::vector<int64_t>& key_seq_len_list,
+                  bool pre_layernorm = false, bool post_layernorm = false, bool post_add_input = false,
+                  bool is_trans_weight = false) const;
+};
+
+class BertAttention : public MultiHeadedAttention {
+ public:
+  BertAttention(core::Tensor qkv_weight, core::Tensor qkv_bias, core::Tensor dense_weight, core::Tensor dense_bias,
+                core::Tensor layer_norm_weight, core::Tensor layer_norm_bias, int64_t num_attention_heads)
+      : MultiHeadedAttention(core::Tensor(nullptr), core::Tensor(nullptr), core::Tensor(nullptr), core::Tensor(nullptr),
+                             core::Tensor(nullptr), core::Tensor(nullptr), std::move(dense_weight), std::move(dense_bias),
+                             std::move(qkv_weight), std::move(qkv_bias), std::move(layer_norm_weight),
+                             std::move(layer_norm_bias), num_attention_heads) {}
+  void operator()(const core::Tensor& input_tensor, const core::Tensor& attention_mask, core::Tensor* output,
+                  core::Tensor* attn = nullptr, bool is_trans_weight = false) const;
+};
+
+class BertIntermediate {
+ public:
+  BertIntermediate(core::Tensor dense_weight, core::Tensor dense_bias) : dense_(std::move(dense_weight), std::move(dense_bias)) {
+    EnforceShapeAndType();
+  }
+  void EnforceShapeAndType() const;
+  void operator()(const core::Tensor& input_tensor, core::Tensor* output_tensor) const;
+  void QuantizeInt8() { dense_.set_int8(true); }
+
+ private:
+  PackedLinear dense_;
+};
+
+class BertOutput {
+ public:
+  BertOutput(core::Tensor dense_weight, core::Tensor dense_bias, core::Tensor layer_norm_weight, core::Tensor layer_norm_bias)
+      : dense_(std::move(dense_weight), std::move(dense_bias)), layer_norm_weight_(std::move(layer_norm_weight)),
+        layer_norm_bias_(std::move(layer_norm_bias)) {
+    EnforceShapeAndType();
+  }
+  void EnforceShapeAndType() const;
+  void operator()(const core::Tensor& hidden_states, const core::Tensor& input_tensor, core::Tensor* output_tensor) const;
+  void QuantizeInt8() { dense_.set_int8(true); }
+
+ private:
+  PackedLinear dense_;
+  core::Tensor layer_norm_weight_, layer_norm_bias_;
+};
+
+class BertPooler {
+ public:
+  BertPooler(core::Tensor dense_weight, core::Tensor dense_bias) : dense_(std::move(dense_weight), std::move(dense_bias)) {
+    EnforceShapeAndType();
+  }
+  void EnforceShapeAndType() const;
+  void operator()(const core::Tensor& input_tensor, core::Tensor* output_tensor) const;
+
+ private:
+  PackedLinear dense_;
+};
+
+class SequencePool {
+ public:
+  explicit SequencePool(const std::string& pool_type);
+  void operator()(const core::Tensor& input, core::Tensor* output) const;
+  // First/Last/Mean/Max per sequence of a packed [1,sumL,H] tensor -> [B,H].
+  void Packed(const core::Tensor& input, const std::vector<int64_t>& seq_lens, core::Tensor* output) const;
+
+ private:
+  int pool_type_;
+};
+
+class PrepareBertMasks {
+ public:
+  void operator()(const core::Tensor& inputs, core::Tensor* att_mask, core::Tensor* seq_type, core::Tensor* position_ids,
+                  core::Tensor* extended_attention_mask) const;
+};
+
+// Pre-LN feed-forward block: out = x + W2 act(W1 LN(x) + b1) + b2 (positionwise_ffn.cpp:31-75).
+// The reference's activation is ReLU; "gelu" selects the tanh-form GELU for GPT-2 style blocks.
+class PositionwiseFeedForward {
+ public:
+  PositionwiseFeedForward(core::Tensor dense_weight_1, core::Tensor dense_bias_1, core::Tensor dense_weight_2,
+                          core::Tensor dense_bias_2, core::Tensor layer_norm_weight, core::Tensor layer_norm_bias)
+      : dense1_(std::move(dense_weight_1), std::move(dense_bias_1)), dense2_(std::move(dense_weight_2), std::move(dense_bias_2)),
+        layer_norm_weight_(std::move(layer_norm_weight)), layer_norm_bias_(std::move(layer_norm_bias)) {}
+  void operator()(const core::Tensor& input_tensor, core::Tensor* output, bool is_trans_weight = true) const;
+  void set_activation(const std::string& act);
+  void set_layernorm_eps(float eps) { eps_ = eps; }
+
+ private:
+  PackedLinear dense1_, dense2_;
+  core::Tensor layer_norm_weight_, layer_norm_bias_;
+  int act_ = TTB_ACT_RELU;
+  float eps_ = 1e-12f;
+};
+
+// In-place bias + tanh-GELU on a projection computed elsewhere (layers/addbias_act.cpp:20-23).
+class FusedAddBiasGELU {
+ public:
+  explicit FusedAddBiasGELU(core::Tensor bias) : bias_(std::move(bias)) {}
+  void operator()(core::Tensor* input_tensor) const;
+
+ private:
+  core::Tensor bias_;
+};
+
+// In-place out = LN(out + input + bias) (layers/addbias_layernorm.cpp:20-24).
+class FusedAddBiasLayerNorm {
+ public:
+  FusedAddBiasLayerNorm(core::Tensor bias, core::Tensor norm_weight, core::Tensor norm_bias)
+      : bias_(std::move(bias)), norm_weight_(std::move(norm_weight)), norm_bias_(std::move(norm_bias)) {}
+  void operator()(const core::Tensor& input_tensor, core::Tensor* output_tensor) const;
+
+ private:
+  core::Tensor bias_, norm_weight_, norm_bias_;
+};
+
+// Stand-alone LayerNorm (kernels::LayerNorm, layer_norm.cpp:32-91) for pre-LN models' final norm.
+class LayerNorm {
+ public:
+  LayerNorm(core::Tensor gamma, core::Tensor beta, float eps) : gamma_(std::move(gamma)), beta_(std::move(beta)), eps_(eps) {}
+  void operator()(const core::Tensor& input, core::Tensor* output) const;
+
+ private:
+  core::Tensor gamma_, beta_;
+  float eps_;
+};
+
+// Token + learned position embedding without a layer norm (decoder-only models): two
+// kernels::LookupEmbedding passes (embedding.cpp:28-85), set then accumulate.
+class TokenPositionEmbedding {
+ public:
+  TokenPositionEmbedding(core::Tensor token_table, core::Tensor position_table)
+      : token_(std::move(token_table)), position_(std::move(position_table)) {}
+  void operator()(const core::Tensor& input_ids, core::Tensor* output) const;  // ids [B,L] -> [B,L,H], positions 0..L-1
+
+ private:
+  core::Tensor token_, position_;
+};
+
+// out = x . W (+ bias): kernels::MatMul as a layer, used for the tied-embedding logits of decoder models.
+class Linear {
+ public:
+  Linear(core::Tensor weight, core::Tensor bias, bool is_trans_weight)
+      : dense_(std::move(weight), std::move(bias)), is_trans_(is_trans_weight) {}
+  void operator()(const core::Tensor& input, core::Tensor* output) const;
+
+ private:
+  PackedLinear dense_;
+  bool is_trans_;
+};
+
+}  // namespace layers
+}  // namespace turbo_transformers

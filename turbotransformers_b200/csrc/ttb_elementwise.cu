@@ -1,0 +1,689 @@
+// Bandwidth-bound kernels: layer norm, bias/activation, embedding, pooling, transposes, softmax, quantise.
+// All are warp-per-row or 16-byte-vector grid-stride kernels; reductions use warp shuffles and fp32 math.
+#include <vector>
+
+#include "ttb_common.cuh"
+
+using namespace ttb;
+
+namespace {
+
+constexpr int kRowsPerBlock = 4;  // warps per CTA in warp-per-row kernels
+
+inline int grid_for(int64_t work, int per_block, int sm_count) {
+  int64_t g = (work + per_block - 1) / per_block;
+  int64_t cap = (int64_t)sm_count * 32;
+  return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+// ------------------------------------------------------------------------------------------------
+// LayerNorm: out = LN(x [+ residual + bias]) * gamma + beta. One warp per row, row cached in registers.
+// ITERS vectors of 8 elements per lane: N % 8 == 0 and N <= 256*ITERS.
+// ------------------------------------------------------------------------------------------------
+template <typename T, int ITERS, bool ADD>
+__global__ void __launch_bounds__(kRowsPerBlock * 32)
+layernorm_rows_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ bias,
+                      const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ out, int64_t M, int N,
+                      float eps) {
+  const int lane = threadIdx.x & 31;
+  const int warps_total = gridDim.x * kRowsPerBlock;
+  for (int64_t row = (int64_t)blockIdx.x * kRowsPerBlock + (threadIdx.x >> 5); row < M; row += warps_total) {
+    const T* xr = x + row * N;
+    float v[ITERS][8];
+    float sum = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int col = (it * 32 + lane) * 8;
+      if (col < N) {
+        Vec8<T> a;
+        a.load(xr + col);
+        if (ADD) {
+          Vec8<T> r, b;
+          r.load(residual + row * N + col);
+          b.load(bias + col);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a.v[j] = a.v[j] + r.v[j] + b.v[j];
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { v[it][j] = a.v[j]; sum += a.v[j]; }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[it][j] = 0.f;
+      }
+    }
+    const float mean = warp_sum(sum) / (float)N;
+    float sq = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int col = (it * 32 + lane) * 8;
+      if (col < N) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { float d = v[it][j] - mean; sq += d * d; }
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(sq) / (float)N + eps);
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int col = (it * 32 + lane) * 8;
+      if (col < N) {
+        Vec8<T> g, b, o;
+        g.load(gamma + col);
+        b.load(beta + col);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o.v[j] = b.v[j] + g.v[j] * rstd * (v[it][j] - mean);
+        o.store(out + row * N + col);
+      }
+    }
+  }
+}
+
+// Any N: one warp per row, three passes over the row (the re-reads hit L1/L2).
+template <typename T, bool ADD>
+__global__ void __launch_bounds__(kRowsPerBlock * 32)
+layernorm_rows_generic_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ bias,
+                              const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ out, int64_t M,
+                              int N, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int warps_total = gridDim.x * kRowsPerBlock;
+  for (int64_t row = (int64_t)blockIdx.x * kRowsPerBlock + (threadIdx.x >> 5); row < M; row += warps_total) {
+    auto val = [&](int c) {
+      float a = to_f(x[row * N + c]);
+      if (ADD) a += to_f(residual[row * N + c]) + to_f(bias[c]);
+      return a;
+    };
+    float sum = 0.f;
+    for (int c = lane; c < N; c += 32) sum += val(c);
+    const float mean = warp_sum(sum) / (float)N;
+    float sq = 0.f;
+    for (int c = lane; c < N; c += 32) { float d = val(c) - mean; sq += d * d; }
+    const float rstd = rsqrtf(warp_sum(sq) / (float)N + eps);
+    // x may alias out: every lane reads only the columns it then writes.
+    for (int c = lane; c < N; c += 32) {
+      float a = val(c);
+      out[row * N + c] = from_f<T>(to_f(beta[c]) + to_f(gamma[c]) * rstd * (a - mean));
+    }
+  }
+}
+
+template <typename T, bool ADD>
+int launch_layernorm(ttb_ctx* ctx, const T* x, const T* residual, const T* bias, const T* gamma, const T* beta, T* out,
+                     int64_t M, int64_t N, float eps) {
+  if (M == 0) return TTB_OK;
+  const int grid = grid_for(M, kRowsPerBlock, ctx->sm_count);
+  const int block = kRowsPerBlock * 32;
+#define LN_CASE(IT)                                                                                             \
+  layernorm_rows_kernel<T, IT, ADD><<<grid, block, 0, ctx->stream>>>(x, residual, bias, gamma, beta, out, M, (int)N, eps)
+  const bool aligned = (N % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) |
+                                         reinterpret_cast<uintptr_t>(gamma) | reinterpret_cast<uintptr_t>(beta) |
+                                         (ADD ? (reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(bias)) : 0)) %
+                                            16 == 0);
+  if (aligned && N <= 256) LN_CASE(1);
+  else if (aligned && N <= 512) LN_CASE(2);
+  else if (aligned && N <= 768) LN_CASE(3);
+  else if (aligned && N <= 1024) LN_CASE(4);
+  else if (aligned && N <= 2048) LN_CASE(8);
+  else
+    layernorm_rows_generic_kernel<T, ADD><<<grid, block, 0, ctx->stream>>>(x, residual, bias, gamma, beta, out, M, (int)N, eps);
+#undef LN_CASE
+  return launched(ctx, "layernorm");
+}
+
+// ------------------------------------------------------------------------------------------------
+// out = act(out + bias), in place.
+// ------------------------------------------------------------------------------------------------
+template <int ACT> __device__ __forceinline__ float apply_act(float x) {
+  if (ACT == TTB_ACT_GELU) return gelu_tanh(x);
+  if (ACT == TTB_ACT_TANH) return tanhf(x);
+  return x > 0.f ? x : 0.f;
+}
+
+template <typename T, int ACT, bool VEC>
+__global__ void __launch_bounds__(256)
+add_bias_act_kernel(T* __restrict__ out, const T* __restrict__ bias, int64_t M, int N) {
+  if (VEC) {
+    const int64_t nvec = M * (int64_t)(N / 8);
+    const int per_row = N / 8;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
+      const int col = (int)(i % per_row) * 8;
+      Vec8<T> a, b;
+      a.load(out + i * 8);
+      b.load(bias + col);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a.v[j] = apply_act<ACT>(a.v[j] + b.v[j]);
+      a.store(out + i * 8);
+    }
+  } else {
+    const int64_t n = M * (int64_t)N;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+      out[i] = from_f<T>(apply_act<ACT>(to_f(out[i]) + to_f(bias[i % N])));
+  }
+}
+
+// out = in1 (+ in2) + bias
+template <typename T, bool ADD_INPUT>
+__global__ void __launch_bounds__(256)
+add_bias_kernel(const T* __restrict__ in1, const T* __restrict__ in2, const T* __restrict__ bias, T* __restrict__ out,
+                int64_t M, int N) {
+  const int64_t n = M * (int64_t)N;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    float a = to_f(in1[i]) + to_f(bias[i % N]);
+    if (ADD_INPUT) a += to_f(in2[i]);
+    out[i] = from_f<T>(a);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Embedding gather. Ids outside the table are clamped and flagged (the reference trapped the GPU).
+// ------------------------------------------------------------------------------------------------
+template <typename T, bool ADD>
+__global__ void __launch_bounds__(256)
+lookup_kernel(T* __restrict__ out, const T* __restrict__ table, const int64_t* __restrict__ ids, int64_t n_ids,
+              int hidden, int64_t vocab, int* status) {
+  for (int64_t r = blockIdx.x; r < n_ids; r += gridDim.x) {
+    int64_t id = ids[r];
+    if (id < 0 || id >= vocab) {
+      if (threadIdx.x == 0) atomicExch(status, (int)TTB_ERR_BAD_INDEX);
+      id = id < 0 ? 0 : vocab - 1;
+    }
+    const T* src = table + id * hidden;
+    T* dst = out + r * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+      dst[c] = ADD ? from_f<T>(to_f(dst[c]) + to_f(src[c])) : src[c];
+  }
+}
+
+__device__ __forceinline__ int find_sequence(const int32_t* cu, int B, int token) {
+  int lo = 0, hi = B;  // largest b with cu[b] <= token
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (cu[mid] <= token) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+// word[id] + position[pos] + token_type[tt] -> LayerNorm, one warp per token, any hidden size.
+template <typename T>
+__global__ void __launch_bounds__(kRowsPerBlock * 32)
+embedding_ln_kernel(const int64_t* __restrict__ ids, const int64_t* __restrict__ pos_ids,
+                    const int64_t* __restrict__ type_ids, const int32_t* __restrict__ cu, int B, int seq_len,
+                    int64_t n_tokens, const T* __restrict__ word, const T* __restrict__ position,
+                    const T* __restrict__ token_type, const T* __restrict__ gamma, const T* __restrict__ beta,
+                    int hidden, int64_t vocab, int64_t n_pos, int64_t n_types, float eps, T* __restrict__ out,
+                    int* status) {
+  const int lane = threadIdx.x & 31;
+  const int warps_total = gridDim.x * kRowsPerBlock;
+  for (int64_t t = (int64_t)blockIdx.x * kRowsPerBlock + (threadIdx.x >> 5); t < n_tokens; t += warps_total) {
+    int64_t id = ids[t];
+    int64_t pos = pos_ids ? pos_ids[t] : (cu ? (int64_t)t - cu[find_sequence(cu, B, (int)t)] : (t % seq_len));
+    int64_t tt = type_ids ? type_ids[t] : 0;
+    bool bad = id < 0 || id >= vocab || pos < 0 || pos >= n_pos || tt < 0 || tt >= n_types;
+    if (bad) {
+      if (lane == 0) atomicExch(status, (int)TTB_ERR_BAD_INDEX);
+      id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+      pos = pos < 0 ? 0 : (pos >= n_pos ? n_pos - 1 : pos);
+      tt = tt < 0 ? 0 : (tt >= n_types ? n_types - 1 : tt);
+    }
+    const T* w = word + id * hidden;
+    const T* p = position + pos * hidden;
+    const T* y = token_type + tt * hidden;
+    // same accumulation order as the reference: word, then token type, then position
+    auto val = [&](int c) { return (to_f(w[c]) + to_f(y[c])) + to_f(p[c]); };
+    float sum = 0.f;
+    for (int c = lane; c < hidden; c += 32) sum += val(c);
+    const float mean = warp_sum(sum) / (float)hidden;
+    float sq = 0.f;
+    for (int c = lane; c < hidden; c += 32) { float d = val(c) - mean; sq += d * d; }
+    const float rstd = rsqrtf(warp_sum(sq) / (float)hidden + eps);
+    for (int c = lane; c < hidden; c += 32)
+      out[t * hidden + c] = from_f<T>(to_f(beta[c]) + to_f(gamma[c]) * rstd * (val(c) - mean));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Pooling over the sequence axis.
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void seq_pool_kernel(const T* __restrict__ in, int64_t B, int64_t L, int H, int type, T* __restrict__ out) {
+  for (int64_t b = blockIdx.x; b < B; b += gridDim.x) {
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+      const T* base = in + b * L * H + c;
+      float r;
+      if (type == TTB_POOL_FIRST) r = to_f(base[0]);
+      else if (type == TTB_POOL_LAST) r = to_f(base[(L - 1) * H]);
+      else if (type == TTB_POOL_MEAN) {
+        r = 0.f;
+        for (int64_t l = 0; l < L; ++l) r += to_f(base[l * H]);
+        r /= (float)L;
+      } else {
+        r = to_f(base[0]);
+        for (int64_t l = 1; l < L; ++l) r = fmaxf(r, to_f(base[l * H]));
+      }
+      out[b * H + c] = from_f<T>(r);
+    }
+  }
+}
+
+template <typename T>
+__global__ void seq_pool_varlen_kernel(const T* __restrict__ in, const int32_t* __restrict__ cu, int64_t B, int H,
+                                       int type, T* __restrict__ out) {
+  for (int64_t b = blockIdx.x; b < B; b += gridDim.x) {
+    const int64_t lo = cu[b], hi = cu[b + 1];
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+      float r;
+      if (type == TTB_POOL_FIRST) r = to_f(in[lo * H + c]);
+      else if (type == TTB_POOL_LAST) r = to_f(in[(hi - 1) * H + c]);
+      else if (type == TTB_POOL_MEAN) {
+        r = 0.f;
+        for (int64_t l = lo; l < hi; ++l) r += to_f(in[l * H + c]);
+        r /= (float)(hi - lo);
+      } else {
+        r = to_f(in[lo * H + c]);
+        for (int64_t l = lo + 1; l < hi; ++l) r = fmaxf(r, to_f(in[l * H + c]));
+      }
+      out[b * H + c] = from_f<T>(r);
+    }
+  }
+}
+
+__global__ void prepare_masks_kernel(int64_t B, int64_t L, const int64_t* __restrict__ mask_in,
+                                     int64_t* __restrict__ mask_out, int64_t* __restrict__ type_out,
+                                     int64_t* __restrict__ pos_out, float* __restrict__ ext_out) {
+  const int64_t n = B * L;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = mask_in ? mask_in[i] : 1;
+    if (mask_out) mask_out[i] = m;
+    if (type_out) type_out[i] = 0;
+    if (pos_out) pos_out[i] = i % L;
+    if (ext_out) ext_out[i] = -10000.0f * (1.0f - (float)m);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Transposes between token-major [.., L, heads, d] and head-major [B, heads, L, d]; optional bias,
+// optional packed<->padded mapping through cu_seqlens. One thread moves 1 element; consecutive threads
+// walk d, so both sides are accessed in d-long contiguous runs.
+// ------------------------------------------------------------------------------------------------
+// mode 0: qkv [B,L,3,h,d] + bias -> q,k,v [B,h,L,d]     (cu == nullptr: fixed length; else packed -> padded, zero-filled)
+template <typename T>
+__global__ void __launch_bounds__(256)
+split_add_bias_transpose_kernel(const T* __restrict__ qkv, const T* __restrict__ bias, const int32_t* __restrict__ cu,
+                                int64_t B, int64_t L, int heads, int d, T* __restrict__ q, T* __restrict__ k,
+                                T* __restrict__ v) {
+  const int64_t H = (int64_t)heads * d;
+  const int64_t n = B * L * 3 * H;  // over the padded output index space
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int dd = (int)(i % d);
+    const int hh = (int)((i / d) % heads);
+    const int w = (int)((i / H) % 3);
+    const int64_t l = (i / (3 * H)) % L;
+    const int64_t b = i / (3 * H * L);
+    T* dst = (w == 0 ? q : (w == 1 ? k : v)) + ((b * heads + hh) * L + l) * d + dd;
+    int64_t src_tok;
+    if (cu) {
+      const int64_t len = cu[b + 1] - cu[b];
+      if (l >= len) { *dst = from_f<T>(0.f); continue; }
+      src_tok = cu[b] + l;
+    } else {
+      src_tok = b * L + l;
+    }
+    const int64_t c = (int64_t)w * H + (int64_t)hh * d + dd;
+    *dst = from_f<T>(to_f(qkv[src_tok * 3 * H + c]) + to_f(bias[c]));
+  }
+}
+
+// [B,h,L,d] -> [B,L,h*d] (cu == nullptr) or padded -> packed [sumL, h*d] (cu given; index space = padded)
+template <typename T>
+__global__ void __launch_bounds__(256)
+transpose_for_score_kernel(const T* __restrict__ in, const int32_t* __restrict__ cu, int64_t B, int64_t L, int heads,
+                           int d, T* __restrict__ out) {
+  const int64_t H = (int64_t)heads * d;
+  const int64_t n = B * L * H;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int dd = (int)(i % d);
+    const int hh = (int)((i / d) % heads);
+    const int64_t l = (i / H) % L;
+    const int64_t b = i / (H * L);
+    int64_t dst_tok;
+    if (cu) {
+      if (l >= cu[b + 1] - cu[b]) continue;
+      dst_tok = cu[b] + l;
+    } else {
+      dst_tok = b * L + l;
+    }
+    out[dst_tok * H + (int64_t)hh * d + dd] = in[((b * heads + hh) * L + l) * d + dd];
+  }
+}
+
+// [B,L,h,d] + bias -> [B,h,L,d] (cu == nullptr) or packed [sumL,h,d] + bias -> padded, zero-filled
+template <typename T>
+__global__ void __launch_bounds__(256)
+add_bias_transpose_kernel(const T* __restrict__ in, const T* __restrict__ bias, const int32_t* __restrict__ cu, int64_t B,
+                          int64_t L, int heads, int d, T* __restrict__ out) {
+  const int64_t H = (int64_t)heads * d;
+  const int64_t n = B * L * H;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int dd = (int)(i % d);
+    const int hh = (int)((i / d) % heads);
+    const int64_t l = (i / H) % L;
+    const int64_t b = i / (H * L);
+    T* dst = out + ((b * heads + hh) * L + l) * d + dd;
+    int64_t src_tok;
+    if (cu) {
+      if (l >= cu[b + 1] - cu[b]) { *dst = from_f<T>(0.f); continue; }
+      src_tok = cu[b] + l;
+    } else {
+      src_tok = b * L + l;
+    }
+    const int64_t c = (int64_t)hh * d + dd;
+    *dst = from_f<T>(to_f(in[src_tok * H + c]) + to_f(bias[c]));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// softmax(scores*scale + mask) over the last dim, in place; one warp per row, any row length.
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kRowsPerBlock * 32)
+mask_softmax_kernel(T* __restrict__ scores, const float* __restrict__ mask, int64_t B, int heads, int64_t Lq,
+                    int64_t Lk, float scale, int is_2d) {
+  const int lane = threadIdx.x & 31;
+  const int64_t rows = B * heads * Lq;
+  const int warps_total = gridDim.x * kRowsPerBlock;
+  for (int64_t row = (int64_t)blockIdx.x * kRowsPerBlock + (threadIdx.x >> 5); row < rows; row += warps_total) {
+    T* s = scores + row * Lk;
+    const int64_t b = row / (heads * Lq);
+    const int64_t i = row % Lq;
+    const float* m = mask ? mask + (is_2d ? b * Lk : (b * Lq + i) * Lk) : nullptr;
+    float mx = -INFINITY;
+    for (int64_t j = lane; j < Lk; j += 32) mx = fmaxf(mx, to_f(s[j]) * scale + (m ? m[j] : 0.f));
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int64_t j = lane; j < Lk; j += 32) sum += expf(to_f(s[j]) * scale + (m ? m[j] : 0.f) - mx);
+    const float inv = 1.0f / warp_sum(sum);
+    for (int64_t j = lane; j < Lk; j += 32)
+      s[j] = from_f<T>(expf(to_f(s[j]) * scale + (m ? m[j] : 0.f) - mx) * inv);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Per-row symmetric int8 quantisation; one warp per row.
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kRowsPerBlock * 32)
+quantize_rows_kernel(const T* __restrict__ x, int64_t M, int K, int8_t* __restrict__ xq, float* __restrict__ scale) {
+  const int lane = threadIdx.x & 31;
+  const int warps_total = gridDim.x * kRowsPerBlock;
+  for (int64_t row = (int64_t)blockIdx.x * kRowsPerBlock + (threadIdx.x >> 5); row < M; row += warps_total) {
+    const T* xr = x + row * K;
+    float amax = 0.f;
+    for (int c = lane; c < K; c += 32) amax = fmaxf(amax, fabsf(to_f(xr[c])));
+    amax = warp_max(amax);
+    const float sc = amax > 0.f ? amax / 127.0f : 1.0f;
+    if (lane == 0) scale[row] = sc;
+    for (int c = lane; c < K; c += 32) {
+      float q = rintf(to_f(xr[c]) / sc);
+      q = fminf(fmaxf(q, -127.f), 127.f);
+      xq[row * K + c] = (int8_t)q;
+    }
+  }
+}
+
+}  // namespace
+
+// =================================================================================================
+// C ABI
+// =================================================================================================
+extern "C" int ttb_add_bias_layernorm(ttb_ctx* ctx, int dtype, void* out, const void* input, const void* bias,
+                                      const void* gamma, const void* beta, int64_t M, int64_t N, float eps) {
+  if (!ctx) return TTB_ERR_INVALID;
+  TTB_REQUIRE(ctx, M >= 0 && N > 0, "add_bias_layernorm: bad shape M=%lld N=%lld", (long long)M, (long long)N);
+  TTB_REQUIRE(ctx, M == 0 || (out && input && bias && gamma && beta), "add_bias_layernorm: null pointer");
+  DeviceGuard g(ctx->device);
+  TTB_DISPATCH_FLOAT(ctx, dtype, T,
+                     return (launch_layernorm<T, true>(ctx, (const T*)out, (const T*)input, (const T*)bias, (const T*)gamma,
+                                                       (const T*)beta, (T*)out, M, N, eps)));
+  return TTB_OK;
+}
+
+extern "C" int ttb_layernorm(ttb_ctx* ctx, int dtype, const void* in, void* out, const void* gamma, const void* beta,
+                             int64_t M, int64_t N, float eps) {
+  if (!ctx) return TTB_ERR_INVALID;
+  TTB_REQUIRE(ctx, M >= 0 && N > 0, "layernorm: bad shape");
+  TTB_REQUIRE(ctx, M == 0 || (in && out && gamma && beta), "layernorm: null pointer");
+  DeviceGuard g(ctx->device);
+  TTB_DISPATCH_FLOAT(ctx, dtype, T,
+                     return (launch_layernorm<T, false>(ctx, (const T*)in, nullptr, nullptr, (const T*)gamma,
+                                                        (const T*)beta, (T*)out, M, N, eps)));
+  return TTB_OK;
+}
+
+extern "C" int ttb_add_bias_act(ttb_ctx* ctx, int dtype, void* out, const void* bias, int64_t M, int64_t N, int act) {
+  if (!ctx) return TTB_ERR_INVALID;
+  TTB_REQUIRE(ctx, M >= 0 && N > 0, "add_bias_act: bad shape");
+  TTB_REQUIRE(ctx, act >= 0 && act <= 2, "add_bias_act: unknown activation %d", act);
+  if (M == 0) return TTB_OK;
+  TTB_REQUIRE(ctx, out && bias, "add_bias_act: null pointer");
+  DeviceGuard g(ctx->device);
+  const bool vec = N % 8 == 0 && (reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(bias)) % 16 == 0;
+  const int grid = grid_for(vec ? M * N / 8 : M * N, 256, ctx->sm_count);
+#define ACT_CASE(A)                                                                                    \
+  if (vec) add_bias_act_kernel<T, A, true><<<grid, 256, 0, ctx->stream>>>((T*)out, (const T*)bias, M, (int)N); \
+  else add_bias_act_kernel<T, A, false><<<grid, 256, 0, ctx->stream>>>((T*)out, (const T*)bias, M, (int)N)
+  TTB_DISPATCH_FLOAT(ctx, dtype, T, {
+    if (act == TTB_ACT_GELU) { ACT_CASE(TTB_ACT_GELU); }
+    else if (act == TTB_ACT_TANH) { ACT_CASE(TTB_ACT_TANH); }
+    else { ACT_CASE(TTB_ACT_RELU); }
+  });
+#undef ACT_CASE
+  return launched(ctx, "add_bias_act");
+}
+
+extern "C" int ttb_add_bias(ttb_ctx* ctx, int dtype, void* out, const void* bias, int64_t M, int64_t N) {
+  if (!ctx) return TTB_ERR_INVALID;
+  TTB_REQUIRE(ctx, M >= 0 && N > 0, "add_bias: bad shape");
+  if (M == 0) return TTB_OK;
+  TTB_REQUIRE(ctx, out && bias, "add_bias: null pointer");
+  DeviceGuard g(ctx->device);
+  const int grid = grid_for(M * N, 256, ctx->sm_count);
+  TTB_DISPATCH_FLOAT(ctx, dtype, T,
+                     (add_bias_kernel<T, false><<<grid, 256, 0, ctx->stream>>>((const T*)out, nullptr, (const T*)bias, (T*)out, M, (int)N)));
+  return launched(ctx, "add_bias");
+}
+
+extern "C" int ttb_add_input_bias(ttb_ctx* ctx, int dtype, const void* in1, const void* in2, const void* bias,
+                                  int64_t M, int64_t N, void* out) {
+  if (!ctx) return TTB_ERR_INVALID;
+  TTB_REQUIRE(ctx, M >= 0 && N > 0, "add_input_bias: bad shape");
+  if (M == 0) return TTB_OK;
+  TTB_REQUIRE(ctx, in1 && in2 && bias && out, "add_input_bias: null pointer");
+  DeviceGuard g(ctx->device);
+  const int grid = grid_for(M * N, 256, ctx->sm_count);
+  TTB_DISPATCH_FLOAT(ctx, dtype, T,
+                     (add_bias_kernel<T, true><<<grid, 256, 0, ctx->stream>>>((const T*)in1, (const T*)in2, (const T*)bias, (T*)out, M, (int)N)));
+  return launched(ctx, "add_input_bias");
+}
+
+extern "C" int ttb_lookup_embedding(ttb_ctx* ctx, int dtype, void* out, const void* table, const int64_t* ids,
+                                    int64_t n_ids, int64_t hidden, int64_t vocab, int add) {
+  if (!ctx) return TTB_ERR_INVALID;
+  TTB_REQUIRE(ctx, n_ids >= 0 && hidden > 0 && vocab > 0, "lookup_embedding: bad shape");
+  if (n_ids == 0) return TTB_OK;
+  TTB_REQUIRE(ctx, out && table && ids, "lookup_embedding: null pointer");
+  DeviceGuard g(ctx->device);
+  const int grid = (int)(n_ids < (int64_t)ctx->sm_count * 16 ? n_ids : (int64_t)ctx->sm_count * 16);
+  const int block = hidden >= 256 ? 256 : 128;
+  TTB_DISPATCH_FLOAT(ctx, dtype, T, {
+    if (add) lookup_kernel<T, true><<<grid, block, 0, ctx->stream>>>((T*)out, (const T*)table, ids, n_ids, (int)hidden, vocab, ctx->d_status);
+    else lookup_kernel<T, false><<<grid, block, 0, ctx->stream>>>((T*)out, (const T*)table, ids, n_ids, (int)hidden, vocab, ctx->d_status);
+  });
+  return launched(ctx, "lookup_embedding");
+}
+
+extern "C" int ttb_embedding_ln(ttb_ctx* ctx, int dtype, const int64_t* ids, const int64_t* position_ids,
+                                const int64_t* token_type_ids, const int32_t* cu_seqlens, int64_t B, int64_t seq_len,
+                                int64_t n_tokens, const void* word, const void* position, const void* token_type,
+                                const void* gamma, const void* beta, int64_t hidden, int64_t vocab,
+                                int64_t n_positions, int64_t n_types, float eps, void* out) {
+  if (!ctx) return TTB_ERR_INVALID;
+  TTB_REQUIRE(ctx, n_tokens >= 0 && hidden > 0 && vocab > 0 && n_positions > 0 && n_types > 0, "embedding_ln: bad shape");
+  if (n_tokens == 0) return TTB_OK;
+  TTB_REQUIRE(ctx, ids && word && position && token_type && gamma && beta && out, "embedding_ln: null pointer");
+  TTB_REQUIRE(ctx, position_ids || cu_seqlens || seq_len > 0, "embedding_ln: need position_ids, cu_seqlens or seq_len");
+  TTB_REQUIRE(ctx, !cu_seqlens || B > 0, "embedding_ln: cu_seqlens needs B > 0");
+  DeviceGuard g(ctx->device);
+  const int grid = grid_for(n_tokens, kRowsPerBlock, ctx->sm_count);
+  TTB_DISPATCH_FLOAT(ctx, dtype, T,
+                     (embedding_ln_kernel<T><<<grid, kRowsPerBlock * 32, 0, ctx->stream>>>(
+                         ids, position_ids, token_type_ids, cu_seqlens, (int)B, (int)(seq_len > 0 ? seq_len : 1), n_tokens,
+                         (const T*)word, (const T*)position, (const T*)token_type, (const T*)gamma, (const T*)beta,
+                         (int)hidden, vocab, n_positions, n_types, eps, (T*)out, ctx->d_status)));
+  return launched(ctx, "embedding_ln");
+}
+
+extern "C" int ttb_seq_pool(ttb_ctx* ctx, int dtype, const void* in, int64_t B, int64_t L, int64_t H, int pool_type,
+                            void* out) {
+  if (!ctx) return TTB_ERR_INVALID;
+  TTB_REQUIRE(ctx, B >= 0 && L > 0 && H > 0, "seq_pool: bad shape");
+  TTB_REQUIRE(ctx, pool_type >= 0 && pool_type <= 3, "seq_pool: unknown pool type %d", pool_type);
+  if (B == 0) return TTB_OK;
+  TTB_REQUIRE(ctx, in && out, "seq_pool: null pointer");
+  DeviceGuard g(ctx->device);
+  TTB_DISPATCH_FLOAT(ctx, dtype, T,
+                     (seq_pool_kernel<T><<<(int)(B < 65535 ? B : 65535), 256, 0, ctx->stream>>>((const T*)in, B, L, (int)H, pool_type, (T*)out)));
+  return launched(ctx, "seq_pool");
+}
+
+extern "C" int ttb_seq_pool_varlen(ttb_ctx* ctx, int dtype, const void* in, const int32_t* cu_seqlens, int64_t B,
+                                   int64_t H, int pool_type, void* out) {
+  if (!ctx) return TTB_ERR_INVALID;
+  TTB_REQUIRE(ctx, B >= 0 && H > 0, "seq_pool_varlen: bad shape");
+  TTB_REQUIRE(ctx, pool_type >= 0 && pool_type <= 3, "seq_pool_varlen: unknown pool type %d", pool_type);
+  if (B == 0) return TTB_OK;
+  TTB_REQUIRE(ctx, in && out && cu_seqlens, "seq_pool_varlen: null pointer");
+  DeviceGuard g(ctx->device);
+  TTB_DISPATCH_FLOAT(ctx, dtype, T,
+                     (seq_pool_varlen_kernel<T><<<(int)(B < 65535 ? B : 65535), 256, 0, ctx->stream>>>((const T*)in, cu_seqlens, B, (int)H, pool_type, (T*)out)));
+  return launched(ctx, "seq_pool_varlen");
+}
+
+extern "C" int ttb_prepare_bert_masks(ttb_ctx* ctx, int64_t B, int64_t L, const int64_t* att_mask_in,
+                                      int64_t* att_mask_out, int64_t* token_type_out, int64_t* position_ids_out,
+                                      float* extended_out) {
+  if (!ctx) return TTB_ERR_INVALID;
+  TTB_REQUIRE(ctx, B >= 0 && L >= 0, "prepare_bert_masks: bad shape");
+  if (B * L == 0) return TTB_OK;
+  DeviceGuard g(ctx->device);
+  prepare_masks_kernel<<<grid_for(B * L, 256, ctx->sm_count), 256, 0, ctx->stream>>>(B, L, att_mask_in, att_mask_out, token_type_out,
+                                                                                      position_ids_out, extended_out);
+  return launched(ctx, "prepare_bert_masks");
+}
+
+static int check_transpose_args(ttb_ctx* ctx, const char* what, int64_t B, int64_t L, int64_t heads, int64_t d) {
+  TTB_REQUIRE(ctx, B >= 0 && L >= 0 && heads > 0 && d > 0, "%s: bad shape B=%lld L=%lld heads=%lld d=%lld", what,
+              (long long)B, (long long)L, (long long)heads, (long long)d);
+  return TTB_OK;
+}
+
+extern "C" int ttb_split_add_bias_transpose(ttb_ctx* ctx, int dtype, const void* qkv, const void* bias, int64_t B,
+                                            int64_t L, int64_t heads, int64_t d, void* q, void* k, void* v) {
+  return ttb_split_add_bias_transpose_pad(ctx, dtype, qkv, bias, nullptr, B, L, heads, d, q, k, v);
+}
+
+extern "C" int ttb_split_add_bias_transpose_pad(ttb_ctx* ctx, int dtype, const void* qkv, const void* bias,
+                                                const int32_t* cu_seqlens, int64_t B, int64_t maxL, int64_t heads,
+                                                int64_t d, void* q, void* k, void* v) {
+  if (!ctx) return TTB_ERR_INVALID;
+  int s = check_transpose_args(ctx, "split_add_bias_transpose", B, maxL, heads, d);
+  if (s) return s;
+  if (B * maxL == 0) return TTB_OK;
+  TTB_REQUIRE(ctx, qkv && bias && q && k && v, "split_add_bias_transpose: null pointer");
+  DeviceGuard g(ctx->device);
+  const int grid = grid_for(B * maxL * 3 * heads * d, 256, ctx->sm_count);
+  TTB_DISPATCH_FLOAT(ctx, dtype, T,
+                     (split_add_bias_transpose_kernel<T><<<grid, 256, 0, ctx->stream>>>((const T*)qkv, (const T*)bias, cu_seqlens, B, maxL,
+                                                                                      (int)heads, (int)d, (T*)q, (T*)k, (T*)v)));
+  return launched(ctx, "split_add_bias_transpose");
+}
+
+extern "C" int ttb_transpose_for_score(ttb_ctx* ctx, int dtype, const void* in, int64_t B, int64_t heads, int64_t L,
+                                       int64_t d, void* out) {
+  return ttb_transpose_for_score_pad(ctx, dtype, in, nullptr, B, L, heads, d, out);
+}
+
+extern "C" int ttb_transpose_for_score_pad(ttb_ctx* ctx, int dtype, const void* in, const int32_t* cu_seqlens,
+                                           int64_t B, int64_t maxL, int64_t heads, int64_t d, void* out) {
+  if (!ctx) return TTB_ERR_INVALID;
+  int s = check_transpose_args(ctx, "transpose_for_score", B, maxL, heads, d);
+  if (s) return s;
+  if (B * maxL == 0) return TTB_OK;
+  TTB_REQUIRE(ctx, in && out, "transpose_for_score: null pointer");
+  DeviceGuard g(ctx->device);
+  const int grid = grid_for(B * maxL * heads * d, 256, ctx->sm_count);
+  TTB_DISPATCH_FLOAT(ctx, dtype, T,
+                     (transpose_for_score_kernel<T><<<grid, 256, 0, ctx->stream>>>((const T*)in, cu_seqlens, B, maxL, (int)heads, (int)d, (T*)out)));
+  return launched(ctx, "transpose_for_score");
+}
+
+extern "C" int ttb_add_bias_transpose_for_score(ttb_ctx* ctx, int dtype, const void* in, const void* bias, int64_t B,
+                                                int64_t L, int64_t heads, int64_t d, void* out) {
+  return ttb_add_bias_transpose_for_score_pad(ctx, dtype, in, bias, nullptr, B, L, heads, d, out);
+}
+
+extern "C" int ttb_add_bias_transpose_for_score_pad(ttb_ctx* ctx, int dtype, const void* in, const void* bias,
+                                                    const int32_t* cu_seqlens, int64_t B, int64_t maxL, int64_t heads,
+                                                    int64_t d, void* out) {
+  if (!ctx) return TTB_ERR_INVALID;
+  int s = check_transpose_args(ctx, "add_bias_transpose_for_score", B, maxL, heads, d);
+  if (s) return s;
+  if (B * maxL == 0) return TTB_OK;
+  TTB_REQUIRE(ctx, in && bias && out, "add_bias_transpose_for_score: null pointer");
+  DeviceGuard g(ctx->device);
+  const int grid = grid_for(B * maxL * heads * d, 256, ctx->sm_count);
+  TTB_DISPATCH_FLOAT(ctx, dtype, T,
+                     (add_bias_transpose_kernel<T><<<grid, 256, 0, ctx->stream>>>((const T*)in, (const T*)bias, cu_seqlens, B, maxL, (int)heads,
+                                                                                (int)d, (T*)out)));
+  return launched(ctx, "add_bias_transpose_for_score");
+}
+
+extern "C" int ttb_mask_softmax(ttb_ctx* ctx, int dtype, void* scores, const float* mask, int64_t B, int64_t heads,
+                                int64_t Lq, int64_t Lk, float scale, int mask_is_2d) {
+  if (!ctx) return TTB_ERR_INVALID;
+  TTB_REQUIRE(ctx, B >= 0 && heads > 0 && Lq >= 0 && Lk > 0, "mask_softmax: bad shape");
+  if (B * Lq == 0) return TTB_OK;
+  TTB_REQUIRE(ctx, scores, "mask_softmax: null pointer");
+  DeviceGuard g(ctx->device);
+  const int grid = grid_for(B * heads * Lq, kRowsPerBlock, ctx->sm_count);
+  TTB_DISPATCH_FLOAT(ctx, dtype, T,
+                     (mask_softmax_kernel<T><<<grid, kRowsPerBlock * 32, 0, ctx->stream>>>((T*)scores, mask, B, (int)heads, Lq, Lk, scale, mask_is_2d)));
+  return launched(ctx, "mask_softmax");
+}
+
+extern "C" int ttb_quantize_rows_int8(ttb_ctx* ctx, int dtype, const void* x, int64_t M, int64_t K, int8_t* xq,
+                                      float* row_scale) {
+  if (!ctx) return TTB_ERR_INVALID;
+  TTB_REQUIRE(ctx, M >= 0 && K > 0, "quantize_rows_int8: bad shape");
+  if (M == 0) return TTB_OK;
+  TTB_REQUIRE(ctx, x && xq && row_scale, "quantize_rows_int8: null pointer");
+  DeviceGuard g(ctx->device);
+  const int grid = grid_for(M, kRowsPerBlock, ctx->sm_count);
+  TTB_DISPATCH_FLOAT(ctx, dtype, T,
+                     (quantize_rows_kernel<T><<<grid, kRowsPerBlock * 32, 0, ctx->stream>>>((const T*)x, M, (int)K, xq, row_scale)));
+  return launched(ctx, "quantize_rows_int8");
+}
+
+extern "C" int ttb_build_cu_seqlens(ttb_ctx* ctx, const int64_t* host_seq_lens, int64_t B, int32_t* cu_dev) {
+  if (!ctx) return TTB_ERR_INVALID;
+  TTB_REQUIRE(ctx, B >= 0 && (B == 0 || host_seq_lens) && cu_dev, "build_cu_seqlens: bad arguments");
+  std::vector<int32_t> cu((size_t)B + 1, 0);
+  for (int64_t b = 0; b < B; ++b) {
+    TTB_REQUIRE(ctx, host_seq_lens[b] >= 0, "build_cu_seqlens: negative length at %lld", (long long)b);
+    int64_t next = (int64_t)cu[b] + host_seq_lens[b];
+    TTB_REQUIRE(ctx, next <= INT32_MAX, "build_cu_seqlens: more than 2^31 tokens");
+    cu[b + 1] = (int32_t)next;
+  }
+  DeviceGuard g(ctx->device);
+  // pageable source: the copy has completed from the host's view when the call returns
+  TTB_CUDA(ctx, cudaMemcpyAsync(cu_dev, cu.data(), cu.size() * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+  TTB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return TTB_OK;
+}

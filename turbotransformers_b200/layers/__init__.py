@@ -1,0 +1,14 @@
+from .modeling_bert import (BertEmbeddings, BertIntermediate, BertOutput, BertAttention, BertLayer, SequencePool, BertEncoder,
+                            BertModel, BertModelNoPooler, PoolingType, BertPooler)
+from .qmodeling_bert import QBertIntermediate, QBertOutput, QBertLayer, QBertEncoder, QBertModel
+from .modules import MultiHeadedAttention, PositionwiseFeedForward
+from .modeling_gpt2 import GPT2Model
+from .modeling_smart_pad import (MultiHeadedAttentionSmartBatch, BertLayerSmartBatch, BertEncoderSmartBatch, BertModelSmartBatch,
+                                 BertModelNoPoolerSmartBatch)
+from .return_type import ReturnType
+
+__all__ = ['BertEmbeddings', 'BertIntermediate', 'BertOutput', 'BertAttention', 'BertLayer', 'BertEncoder', 'BertModel',
+           'BertModelNoPooler', 'ReturnType', 'BertPooler', 'SequencePool', 'PoolingType', 'MultiHeadedAttention',
+           'PositionwiseFeedForward', 'QBertIntermediate', 'QBertOutput', 'QBertLayer', 'QBertEncoder', 'QBertModel', 'GPT2Model',
+           'MultiHeadedAttentionSmartBatch', 'BertLayerSmartBatch', 'BertEncoderSmartBatch', 'BertModelSmartBatch',
+           'BertModelNoPoolerSmartBatch']

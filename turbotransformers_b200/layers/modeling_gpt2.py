@@ -1,0 +1,89 @@
+"""GPT-2 decoder stack (full-sequence forward) built from the same layer classes.
+
+The reference's GPT2Model wraps onnxruntime only and raises for its own "turbo" backend
+(python/turbo_transformers/layers/modeling_gpt2.py:39-40,57-58). This class composes the block the way the
+reference composes pre-LN blocks for its NMT encoder (modeling_encoder.py:81-91): MultiHeadedAttention with
+pre_layernorm + post_add_input and a causal mask, then a pre-LN feed-forward with the tanh-form GELU
+(equal to GPT-2's gelu_new), a final LayerNorm, and logits = hidden . wte^T (MatMul with b_trans).
+"""
+from typing import Optional
+
+import torch
+
+from .._cxx import cxx
+from .return_type import ReturnType, convert_returns_as_type
+from .utils import AnyTensor, convert2tt_tensor, try_convert, use_current_stream
+
+__all__ = ['GPT2Model']
+
+
+def _empty():
+    return cxx.Tensor.create_empty()
+
+
+class GPT2Model:
+    def __init__(self, embedding, blocks, final_norm, lm_head, config, backend="turbo"):
+        if backend != "turbo":
+            raise NotImplementedError("only the 'turbo' backend exists in this runtime")
+        self.embedding, self.blocks, self.final_norm, self.lm_head, self.config = embedding, blocks, final_norm, lm_head, config
+        self.backend = backend
+        self.dtype = config.torch_dtype_of_weights
+
+    def __call__(self, input_ids: AnyTensor, return_logits: bool = True, return_type: Optional[ReturnType] = None):
+        """input_ids int64 [B, L] on the GPU -> (last_hidden_state [B,L,H], logits [B,L,vocab] or None)."""
+        if isinstance(input_ids, torch.Tensor):
+            use_current_stream(input_ids)
+        ids = try_convert(input_ids)
+        x = _empty()
+        self.embedding(ids, x)
+        mask = _empty()
+        if self.dtype == torch.float32:
+            # the exact-precision path applies an explicit additive mask, as the reference's kernels do
+            B, L = ids.shape(0), ids.shape(1)
+            m = torch.triu(torch.full((L, L), -10000.0, dtype=torch.float32, device="cuda"), 1)
+            mask = convert2tt_tensor(m.unsqueeze(0).repeat(B, 1, 1).contiguous())
+        for attn, ffn in self.blocks:
+            a, probs, y = _empty(), _empty(), _empty()
+            attn(x, x, x, mask, "self", a, probs, {}, True, False, True, False)  # pre-LN, + input
+            ffn(a, y, False)
+            x = y
+        h = _empty()
+        self.final_norm(x, h)
+        logits = None
+        if return_logits:
+            logits = _empty()
+            self.lm_head(h, logits)
+            logits = convert_returns_as_type(logits, return_type)
+        return convert_returns_as_type(h, return_type), logits
+
+    @staticmethod
+    def from_torch(model, device: Optional[torch.device] = None, backend: Optional[str] = None):
+        """model: a HuggingFace GPT2Model (or the .transformer of a GPT2LMHeadModel) on a CUDA device.
+        HuggingFace stores GPT-2 projections as Conv1D weights [in, out], the layout these layers take."""
+        if backend not in (None, "turbo"):
+            raise NotImplementedError("only the 'turbo' backend exists in this runtime")
+        if device is None:
+            device = next(model.parameters()).device
+        if torch.device(device).type != 'cuda':
+            raise RuntimeError("this runtime computes on CUDA devices only (no CPU path)")
+        model.to(device)
+        cfg = model.config
+        cfg.torch_dtype_of_weights = model.wte.weight.dtype
+        eps = float(cfg.layer_norm_epsilon)
+        T = lambda p: convert2tt_tensor(p.detach().contiguous())
+        blocks = []
+        for blk in model.h:
+            attn = cxx.MultiHeadedAttention(_empty(), _empty(), _empty(), _empty(), _empty(), _empty(), T(blk.attn.c_proj.weight),
+                                            T(blk.attn.c_proj.bias), T(blk.attn.c_attn.weight), T(blk.attn.c_attn.bias),
+                                            T(blk.ln_1.weight), T(blk.ln_1.bias), cfg.n_head)
+            attn.set_pre_layernorm_eps(eps)
+            attn.set_causal(True)
+            ffn = cxx.PositionwiseFeedForward(T(blk.mlp.c_fc.weight), T(blk.mlp.c_fc.bias), T(blk.mlp.c_proj.weight),
+                                              T(blk.mlp.c_proj.bias), T(blk.ln_2.weight), T(blk.ln_2.bias))
+            ffn.set_activation("gelu")
+            ffn.set_layernorm_eps(eps)
+            blocks.append((attn, ffn))
+        embedding = cxx.TokenPositionEmbedding(T(model.wte.weight), T(model.wpe.weight))
+        final_norm = cxx.LayerNorm(T(model.ln_f.weight), T(model.ln_f.bias), eps)
+        lm_head = cxx.Linear(T(model.wte.weight), _empty(), True)  # tied embedding, stored [vocab, hidden]
+        return GPT2Model(embedding, blocks, final_norm, lm_head, cfg)

@@ -63,3 +63,23 @@ def varlen_lengths(batch=64, lo=8, hi=512, seed=0):
 def varlen_ids(lengths, vocab, seed=0):
     g = torch.Generator().manual_seed(2000 + seed)
     return [torch.randint(0, vocab, (n,), generator=g, dtype=torch.int64) for n in lengths]
+
+
+GPT2_CONFIGS = {
+    # name: (layers, hidden, heads, vocab, positions)
+    "gpt2-small": (12, 768, 12, 50257, 1024),
+    "gpt2-tiny": (2, 128, 2, 1000, 128),
+    "gpt2-mini": (2, 256, 4, 5003, 256),
+}
+
+
+def make_hf_gpt2(name="gpt2-small", seed=0, num_layers=None):
+    """A HuggingFace GPT2Model (fp32, eval, CPU) with the seeded weights described at the top of this file."""
+    from transformers.models.gpt2.modeling_gpt2 import GPT2Config, GPT2Model
+    n, h, a, v, p = GPT2_CONFIGS[name]
+    cfg = GPT2Config(vocab_size=v, n_positions=p, n_embd=h, n_layer=num_layers or n, n_head=a, resid_pdrop=0.0, embd_pdrop=0.0,
+                     attn_pdrop=0.0, layer_norm_epsilon=1e-5, activation_function="gelu_new")
+    m = GPT2Model(cfg).eval()
+    for q in m.parameters():
+        q.requires_grad_(False)
+    return reinit_(m, seed)
