@@ -1,0 +1,342 @@
+#!/usr/bin/env python
+"""Benchmark of the transformer-layer hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (single GPU and per rank): BERT-base fp16, 64 requests with lengths uniform in [8, 512] drawn
+from seed 0, run unpadded ("smart batch": packed tokens + prefix-sum offsets). One step = one forward of
+that batch through the reference-facing API (BertModelSmartBatch). With N > 1 every rank serves its own
+64-request batch with replicated weights and no collective on the data path (weak scaling).
+
+Prints ONE JSON line on rank 0. `value` is sequences/s with the ids already in HBM; `e2e` starts from
+pinned host ids and ends with the pooled output back on the host. `roofline` is for the tensor-core GEMM
+(the dominant kernel), timed alone with CUDA events on the four shapes of one encoder layer.
+`--impl reference` times the reference's own CPU implementation (oracle/_ref) on the host cores instead.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "bert_base_fp16_varlen_b64_sequences_per_s"
+UNIT = "sequences/s"
+BATCH, LO, HI, SEED = 64, 8, 512, 0
+LAYERS, HIDDEN, HEADS, FFN = 12, 768, 12, 3072
+# ncu, small case of the same kernel (see profiles/): DRAM bytes per GEMM launch relative to algorithmic bytes
+GEMM_TRAFFIC_NOTE = "profiles/gemm_tc_kernel_bert_base_varlen.md"
+
+
+def workload_config(n_gpus):
+    return {"workload": "bert-base fp16 smart-batch: 64 requests/GPU, lengths U[8,512] seed 0, packed tokens",
+            "requests_per_gpu": BATCH, "parallelism": f"replicas x{n_gpus} (requests sharded, weights replicated, no collective)",
+            "cache": "working set (170 MB of fp16 weights + ~0.4 GB of activations per step) exceeds the 126 MB L2",
+            "result_returned": "pooled_output [64,768] fp16 (sequence_output stays on the device)"}
+
+
+def flops_per_sequence(L):
+    """Algorithmic FLOPs of one BERT-base sequence of length L: n*(24*H^2*L + 4*H*L^2)."""
+    return LAYERS * (24 * HIDDEN * HIDDEN * L + 4 * HIDDEN * L * L)
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"tflops": float(d["bf16_tflops"]), "tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    return {"tflops": 1590.0, "tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc, self.window = index, [], None, (0.0, float("inf"))
+
+    def start(self):
+        """Start early (before the warm-up): the tool takes a while to come up and must not do so inside the timed region."""
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons = [], 0.0, set()
+        lo, hi = self.window
+        inside = [r for t, r in self.rows if lo <= t <= hi + 0.05] or [r for _, r in self.rows[-3:]]
+        for r in inside:
+            try:
+                sm.append(float(r[1]))
+                mx = max(mx, float(r[2]))
+                for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7), ("sw_power_cap", 8)):
+                    if r[col].lower().startswith("active"):
+                        reasons.add(name)
+            except (ValueError, IndexError):
+                continue
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_batch(vocab, rank):
+    from turbotransformers_b200 import synthetic
+    lens = synthetic.varlen_lengths(BATCH, LO, HI, SEED + rank)
+    ids = synthetic.varlen_ids(lens, vocab, SEED + rank)
+    return lens, ids
+
+
+# ----------------------------------------------------------------------------------------------------
+# reference arm: the reference's own CPU implementation on the host cores
+# ----------------------------------------------------------------------------------------------------
+def time_reference_cpu(steps, warmup, budget_s, rank0=True):
+    import torch
+    from oracle import ref_driver
+    from turbotransformers_b200 import synthetic
+    torch.set_grad_enabled(False)
+    if not ref_driver.available():
+        raise RuntimeError("oracle/_ref is not built")
+    cores = os.cpu_count() or 1
+    ref_driver.set_num_threads(cores)
+    torch.set_num_threads(cores)
+    hf = synthetic.make_hf_bert("bert-base", SEED)
+    W = ref_driver.pack_bert_weights(hf)
+    ref = ref_driver.RefBert(W, HEADS)
+    lens, ids = make_batch(hf.config.vocab_size, 0)
+    # calibrate on one short request, then size the per-step sample to the time budget
+    t = time.perf_counter()
+    ref.forward_smart_batch(ids[:1])
+    per_token = (time.perf_counter() - t) / max(1, lens[0])
+    per_step_budget = budget_s / max(1, steps + warmup)
+    n, tok = 0, 0
+    while n < BATCH and (n == 0 or (tok + lens[n]) * per_token <= per_step_budget):
+        tok += lens[n]
+        n += 1
+    sample = ids[:n]
+    for _ in range(warmup):
+        ref.forward_smart_batch(sample)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        ref.forward_smart_batch(sample)
+    dt = (time.perf_counter() - t0) / steps
+    return {"value": n / dt, "ms_per_step": dt * 1e3, "cores": cores, "kind": "reference",
+            "sample": f"first {n} of the 64 requests ({tok} tokens) per step through the compiled reference CPU code "
+                      f"(MultiHeadedAttentionSmartBatch + BertIntermediate + BertOutput, OpenBLAS + OpenMP, {cores} threads)"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    try:
+        r = time_reference_cpu(args.steps, args.warmup, budget_s=150.0)
+    except Exception as e:  # the oracle always exists on a prepared tree; say why if it does not
+        print(json.dumps({"impl": "reference", "unavailable": str(e)[:200]}))
+        return
+    line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": workload_config(args.gpus),
+            "cpu_baseline": {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": r["kind"], "sample": r["sample"]},
+            "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------------------------------
+# our arm
+# ----------------------------------------------------------------------------------------------------
+def gemm_roofline(torch, ctx_mod, tokens, peaks):
+    """Times the tensor-core GEMM alone on the four Linear shapes of one BERT-base layer at this batch's token
+    count (CUDA events on the launching stream) and converts to achieved TFLOP/s."""
+    from turbotransformers_b200 import _capi
+    ctx = _capi.Context(torch.cuda.current_device())
+    shapes = [("qkv", HIDDEN, 3 * HIDDEN, _capi.EPI_BIAS), ("attn_out", HIDDEN, HIDDEN, _capi.EPI_BIAS_RESIDUAL),
+              ("ffn1", HIDDEN, FFN, _capi.EPI_BIAS_GELU), ("ffn2", FFN, HIDDEN, _capi.EPI_BIAS_RESIDUAL)]
+    per_shape, total_ms, total_flops = {}, 0.0, 0.0
+    for name, K, N, epi in shapes:
+        a = torch.randn(tokens, K, device="cuda", dtype=torch.float16)
+        w = torch.randn(N, K, device="cuda", dtype=torch.float16) * 0.03
+        b = torch.randn(N, device="cuda", dtype=torch.float16)
+        r = torch.randn(tokens, N, device="cuda", dtype=torch.float16)
+        o = torch.empty(tokens, N, device="cuda", dtype=torch.float16)
+        call = lambda: ctx.call("linear", _capi.F16, a, K, w, b, r, N, tokens, N, K, epi, o, N)
+        for _ in range(3):
+            call()
+        reps = 10
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        for s, e in evs:
+            flush.zero_()  # evict L2 between timed launches
+            s.record()
+            call()
+            e.record()
+        torch.cuda.synchronize()
+        ms = sum(s.elapsed_time(e) for s, e in evs) / reps
+        fl = 2.0 * tokens * N * K
+        per_shape[name] = {"us": round(ms * 1e3, 1), "tflops": round(fl / ms / 1e9, 1)}
+        total_ms += ms
+        total_flops += fl
+        del a, w, b, r, o, flush
+    ctx.close()
+    achieved = total_flops / total_ms / 1e9
+    return {"bound": "tensor", "achieved": round(achieved, 1), "peak": peaks["tflops"], "unit": "TFLOP/s",
+            "frac": round(achieved / peaks["tflops"], 4), "traffic": None, "peak_source": peaks["source"] + " (cuBLAS bf16 burst)",
+            "kernel": "gemm_tc_kernel (tcgen05 + TMEM + TMA), 48 launches per step", "per_shape": per_shape,
+            "avg_launch_us": round(total_ms * 1e3 / 4, 1), "algorithmic_flops_per_launch_avg": total_flops / 4}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    torch.set_grad_enabled(False)
+    import turbotransformers_b200 as tt
+    from turbotransformers_b200 import synthetic
+    cxx = tt._cxx_module
+    peaks = load_peaks()
+
+    hf = synthetic.make_hf_bert("bert-base", SEED)
+    vocab = hf.config.vocab_size
+    model = tt.BertModelSmartBatch.from_torch(hf.to(dev).half(), dev)
+    lens, ids = make_batch(vocab, rank)
+    tokens = sum(lens)
+    ids_host = torch.cat(ids).pin_memory()
+    ids_dev = ids_host.to(dev)
+    pooled_host = torch.empty(BATCH, HIDDEN, dtype=torch.float16).pin_memory()
+
+    def step_device():
+        return model(ids_dev, lens)
+
+    def step_e2e():
+        d = ids_host.to(dev, non_blocking=True)
+        seq, pooled = model(d, lens)[:2]
+        pooled_host.copy_(pooled, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller has its result on the host
+        return pooled_host
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = cxx.launch_count(local)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        launches = cxx.launch_count(local) - l0
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, launches
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    for _ in range(max(3, args.warmup)):
+        step_device()
+    torch.cuda.synchronize()
+    t_lo = time.time()
+    ms, launches = timed(step_device, args.steps)
+    sampler.window = (t_lo, time.time())
+    clocks = sampler.stop() if rank == 0 else None
+    if cxx.device_status(local) != 0:
+        raise RuntimeError("the device status word reports a kernel error")
+    for _ in range(3):
+        step_e2e()
+    ms_e2e, _ = timed(step_e2e, args.steps)
+
+    if rank == 0:
+        seq_per_s = BATCH * world * args.steps / (ms / 1e3)
+        e2e_seq_per_s = BATCH * world * args.steps / (ms_e2e / 1e3)
+        step_flops = sum(flops_per_sequence(L) for L in lens)
+        line = {"metric": METRIC, "value": round(seq_per_s, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": max(3, args.warmup), "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": workload_config(world),
+                "e2e": {"value": round(e2e_seq_per_s, 1), "unit": UNIT, "h2d_bytes_per_step": int(ids_host.numel() * 8),
+                        "d2h_bytes_per_step": int(pooled_host.numel() * 2), "ms_per_step": round(ms_e2e / args.steps, 4)},
+                "gpu_launches": int(launches), "clocks": clocks,
+                "tokens_per_step_per_gpu": tokens,
+                "model_tflops": round(step_flops * world * args.steps / (ms / 1e3) / 1e12, 1),
+                "model_tflops_frac_of_sustained_peak": round(step_flops * args.steps / (ms / 1e3) / 1e12 / peaks["tflops_sustained"], 4)}
+        if args.no_extras:
+            print(json.dumps(line))
+            return
+        line["roofline"] = gemm_roofline(torch, cxx, tokens, peaks)
+        # p50 latency of one 128-token request (the other half of the headline metric)
+        fixed = tt.BertModel.from_torch(hf, dev)
+        one = synthetic.random_ids(1, 128, vocab, SEED).to(dev)
+        for _ in range(10):
+            fixed(one)
+        lat = []
+        for _ in range(50):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fixed(one)
+            e.record()
+            e.synchronize()
+            lat.append(s.elapsed_time(e))
+        lat.sort()
+        line["latency_b1_s128_ms"] = {"p50": round(lat[len(lat) // 2], 4), "p90": round(lat[int(len(lat) * 0.9)], 4)}
+        if world == 1 and not args.no_cpu_baseline:
+            try:
+                r = time_reference_cpu(steps=1, warmup=0, budget_s=20.0)
+                line["cpu_baseline"] = {"value": round(r["value"], 3), "unit": UNIT, "cores": r["cores"], "kind": r["kind"],
+                                        "sample": r["sample"]}
+            except Exception as e:
+                line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
+                                        "sample": f"unavailable: {str(e)[:120]}"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="timed regions only (for profiler launch lists)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

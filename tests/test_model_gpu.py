@@ -19,8 +19,10 @@ from turbotransformers_b200 import synthetic
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 DT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
-MAX_TOL = {"f32": 1e-3, "f16": 2e-2, "bf16": 6e-2}
-MEAN_TOL = {"f32": 1e-4, "f16": 2e-3, "bf16": 6e-3}
+# bf16 stores activations with 8 significant bits (fp16: 11), i.e. 8x the rounding step: its bounds are 8x fp16's
+# and the measured error on BERT-base is 0.07 max-abs after 12 layers.
+MAX_TOL = {"f32": 1e-3, "f16": 2e-2, "bf16": 1.6e-1}
+MEAN_TOL = {"f32": 1e-4, "f16": 2e-3, "bf16": 1.6e-2}
 DEV = torch.device("cuda:0")
 torch.set_grad_enabled(False)
 
@@ -171,10 +173,24 @@ def test_qbert_matches_integer_oracle_and_records_recipe_distance(dt, quantize_a
     model = tt.QBertModel.from_torch(hf32.to(DEV).to(DT[dt]), DEV, quantize_attention=quantize_attention)
     seq = model(torch.from_numpy(g["ids"]).to(DEV))[0].float().cpu().numpy()
     d = np.abs(seq - want)
-    # same scheme, but the GPU keeps activations in 16 bits between layers, so a few roundings flip
-    assert d.max() < (6e-2 if dt == "f16" else 0.12) and d.mean() < (6e-3 if dt == "f16" else 1.5e-2)
+    # Same scheme, but the GPU keeps activations in 16 bits between layers: an activation that lands on the
+    # other side of a rounding boundary moves by a whole int8 step, and twelve layers amplify that. The scheme's
+    # own distance from fp32 is 0.14 max / 0.022 mean (oracle, numpy), which bounds what "equal" can mean here;
+    # the one-layer test below is the tight one.
+    assert d.max() < (0.15 if dt == "f16" else 0.2) and d.mean() < (2.5e-2 if dt == "f16" else 3e-2)
     d_recipe = np.abs(seq - g["sequence_output"])
     assert d_recipe.max() < 0.3 and d_recipe.mean() < 0.05  # the reference recipe is itself 0.149 / 0.027 from fp32
+
+
+def test_qbert_single_layer_is_tight_against_integer_oracle():
+    hf16 = synthetic.make_hf_bert("bert-base", 0, num_layers=1).half()
+    W = ref_driver.pack_bert_weights(hf16)  # the oracle quantises the same fp16-valued weights the GPU is given
+    ids = synthetic.random_ids(2, 128, hf16.config.vocab_size, 3)
+    want = restate.q_bert_model(ids.numpy(), W, 12, True)
+    model = tt.QBertModel.from_torch(hf16.to(DEV), DEV)
+    seq = model(ids.to(DEV))[0].float().cpu().numpy()
+    d = np.abs(seq - want)
+    assert d.max() < 4e-2 and d.mean() < 4e-3
 
 
 @pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])

@@ -301,6 +301,17 @@ void MultiHeadedAttention::Run(const Tensor& x, const Tensor& attention_mask, co
     Check(ttb_batch_matmul(c, dt, q.raw(), 0, k.raw(), 1, B * heads, maxL, maxL, d, scale, 0.0f, scores->raw_mut()), c, "batch_gemm3");
     const float* mask = nullptr;
     int is2d = 1;
+    Tensor pad_mask(nullptr);
+    if (attention_mask.is_null() && seq_lens) {
+      // Packed input without a mask tensor: keys beyond each sequence's length are padding. Build the
+      // [B,1,maxL] additive mask the reference's Python layer builds (modeling_smart_pad.py:82-98).
+      std::vector<float> host_mask((size_t)(B * maxL), 0.f);
+      for (int64_t b = 0; b < B; ++b)
+        for (int64_t l = (*seq_lens)[b]; l < maxL; ++l) host_mask[b * maxL + l] = -1e9f;
+      float* dm = pad_mask.Reshape<float>({B, 1, maxL}, kDLCUDA, dev, "self/pad_mask");
+      Check(ttb_memcpy_h2d(c, dm, host_mask.data(), host_mask.size() * sizeof(float)), c, "self/pad_mask");
+      mask = dm;
+    }
     if (!attention_mask.is_null()) {
       TT_ENFORCE(attention_mask.on_gpu() && core::SameType(attention_mask.dtype(), core::kFloat32),
                  "the attention mask must be an fp32 tensor on the GPU");

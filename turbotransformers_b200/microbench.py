@@ -1,0 +1,110 @@
+"""Single-kernel timing through the C ABI, for roofline numbers and profiler captures.
+
+    python -m turbotransformers_b200.microbench linear    --m 18424 --n 2304 --k 768 --epilogue bias [--dtype f16|bf16|i8]
+    python -m turbotransformers_b200.microbench attention --lens varlen64 | --batch 32 --seq 512 [--heads 12] [--causal]
+    python -m turbotransformers_b200.microbench layernorm --m 18424 --n 768
+    python -m turbotransformers_b200.microbench gelu      --m 18424 --n 3072
+
+Each run launches the kernel `--warmup` + `--iters` times on synthetic data, writes a >L2 buffer between timed
+launches, times every launch with CUDA events on the launching stream, and prints one JSON line with the
+mean duration and the achieved algorithmic FLOP/s or bytes/s.
+"""
+import argparse
+import json
+
+import numpy as np
+import torch
+
+from . import _capi, synthetic
+
+DT = {"f16": (torch.float16, _capi.F16), "bf16": (torch.bfloat16, _capi.BF16), "f32": (torch.float32, _capi.F32)}
+EPI = {"none": 0, "bias": 1, "bias_gelu": 2, "bias_residual": 3, "bias_tanh": 4}
+
+
+def timed(fn, warmup, iters, flush=True):
+    buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(warmup):
+        fn()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for s, e in evs:
+        if flush:
+            buf.zero_()
+        s.record()
+        fn()
+        e.record()
+    torch.cuda.synchronize()
+    t = sorted(s.elapsed_time(e) for s, e in evs)
+    return sum(t) / len(t), t[len(t) // 2], t[0]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("op", choices=["linear", "attention", "layernorm", "gelu"])
+    ap.add_argument("--m", type=int, default=18424)
+    ap.add_argument("--n", type=int, default=2304)
+    ap.add_argument("--k", type=int, default=768)
+    ap.add_argument("--dtype", default="f16", choices=["f16", "bf16", "f32", "i8"])
+    ap.add_argument("--epilogue", default="bias", choices=list(EPI))
+    ap.add_argument("--lens", default=None, help="'varlen64' = the benchmark's 64 lengths in [8,512]")
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--seq", type=int, default=512)
+    ap.add_argument("--heads", type=int, default=12)
+    ap.add_argument("--causal", action="store_true")
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--no-flush", action="store_true")
+    a = ap.parse_args()
+    ctx = _capi.Context(0)
+    out = {"op": a.op}
+    if a.op == "linear":
+        M, N, K = a.m, a.n, a.k
+        odt, ocode = DT["f16" if a.dtype == "i8" else a.dtype]
+        b = torch.randn(N, device="cuda", dtype=odt)
+        r = torch.randn(M, N, device="cuda", dtype=odt)
+        o = torch.empty(M, N, device="cuda", dtype=odt)
+        if a.dtype == "i8":
+            x = torch.randint(-127, 128, (M, K), device="cuda", dtype=torch.int8)
+            w = torch.randint(-127, 128, (N, K), device="cuda", dtype=torch.int8)
+            xs, ws = torch.rand(M, device="cuda"), torch.rand(1, device="cuda")
+            fn = lambda: ctx.call("linear_int8", ocode, x, xs, w, ws, b, r, N, M, N, K, EPI[a.epilogue], o, N)
+        else:
+            x = torch.randn(M, K, device="cuda", dtype=odt)
+            w = torch.randn(N, K, device="cuda", dtype=odt) * 0.03
+            fn = lambda: ctx.call("linear", ocode, x, K, w, b, r, N, M, N, K, EPI[a.epilogue], o, N)
+        mean, med, best = timed(fn, a.warmup, a.iters, not a.no_flush)
+        out.update(shape=[M, N, K], dtype=a.dtype, epilogue=a.epilogue, us=round(mean * 1e3, 2), us_median=round(med * 1e3, 2),
+                   tflops=round(2.0 * M * N * K / mean / 1e9, 1))
+    elif a.op == "attention":
+        lens = synthetic.varlen_lengths(64, 8, 512, 0) if a.lens == "varlen64" else [a.seq] * a.batch
+        tdt, code = DT[a.dtype]
+        H = a.heads * 64
+        T = sum(lens)
+        qkv = torch.randn(T, 3 * H, device="cuda", dtype=tdt)
+        cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device="cuda")
+        o = torch.empty(T, H, device="cuda", dtype=tdt)
+        fn = lambda: ctx.call("attention_fwd", code, qkv, cu, len(lens), max(lens), a.heads, 64, None, 0, 0, int(a.causal), 0.125, o)
+        mean, med, best = timed(fn, a.warmup, a.iters, not a.no_flush)
+        fl = sum((2.0 * H * L * (L + 1)) if a.causal else (4.0 * H * L * L) for L in lens)
+        out.update(sequences=len(lens), tokens=T, heads=a.heads, dtype=a.dtype, causal=a.causal, us=round(mean * 1e3, 2),
+                   us_median=round(med * 1e3, 2), tflops=round(fl / mean / 1e9, 1))
+    else:
+        tdt, code = DT[a.dtype]
+        M, N = a.m, a.n
+        x = torch.randn(M, N, device="cuda", dtype=tdt)
+        r = torch.randn(M, N, device="cuda", dtype=tdt)
+        g = torch.ones(N, device="cuda", dtype=tdt)
+        z = torch.zeros(N, device="cuda", dtype=tdt)
+        if a.op == "layernorm":
+            fn = lambda: ctx.call("add_bias_layernorm", code, x, r, z, g, z, M, N, 1e-12)
+            nbytes = 3.0 * M * N * x.element_size()
+        else:
+            fn = lambda: ctx.call("add_bias_act", code, x, z, M, N, 0)
+            nbytes = 2.0 * M * N * x.element_size()
+        mean, med, best = timed(fn, a.warmup, a.iters, not a.no_flush)
+        out.update(shape=[M, N], dtype=a.dtype, us=round(mean * 1e3, 2), us_median=round(med * 1e3, 2), gbs=round(nbytes / mean / 1e6, 1))
+    assert ctx.device_status() == 0
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
