@@ -45,7 +45,8 @@ def linear_oracle(a, w_kn, bias, res, epi):
 @pytest.mark.parametrize("dt", ["f16", "bf16"])
 @pytest.mark.parametrize("M,N,K", [(128, 768, 768), (128, 2304, 768), (128, 3072, 768), (128, 768, 3072),
                                    (1, 768, 768), (5, 768, 3072), (200, 2304, 768), (333, 768, 3072),
-                                   (1000, 3072, 768), (4096, 1024, 1024), (257, 200, 72), (130, 50264, 768)])
+                                   (1000, 3072, 768), (4096, 1024, 1024), (257, 200, 72), (130, 50264, 768),
+                                   (2048, 3072, 768), (1500, 5120, 200)])  # the last three run on CTA pairs
 @pytest.mark.parametrize("epi", ["bias", "bias_gelu", "bias_residual"])
 def test_linear_matches_unfused_reference(ctx, dt, M, N, K, epi):
     if N > 10000 and epi != "bias":
@@ -135,7 +136,7 @@ def test_linear_rejects_bad_arguments(ctx):
 
 
 # ------------------------------------------------------------------------------------------------ int8
-@pytest.mark.parametrize("M,N,K", [(128, 3072, 768), (128, 768, 3072), (16 * 128, 2304, 768), (77, 768, 768)])
+@pytest.mark.parametrize("M,N,K", [(128, 3072, 768), (128, 768, 3072), (16 * 128, 2304, 768), (77, 768, 768), (2048, 3072, 768)])
 @pytest.mark.parametrize("epi", ["bias", "bias_gelu", "bias_residual"])
 def test_int8_linear_matches_integer_oracle(ctx, M, N, K, epi):
     r = rng(M + N)

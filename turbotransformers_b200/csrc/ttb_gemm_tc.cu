@@ -6,12 +6,15 @@
 //   warp 1      : MMA issuer    - one elected thread issues tcgen05.mma (128 x BN x 16/32 per instruction)
 //                 from shared-memory descriptors into a TMEM accumulator; tcgen05.commit releases ring
 //                 slots ("empty" mbarriers) and publishes finished accumulators ("tmem_full")
-//   warps 2..5  : epilogue      - tcgen05.ld the accumulator (one row per thread), apply
-//                 scale/bias/activation/residual in fp32, convert and store with 16-byte writes
+//   warps 2..5  : epilogue      - tcgen05.ld the accumulator (one row per thread), apply scale/bias/activation/
+//                 residual in fp32, convert, stage through a swizzled shared-memory tile and TMA-store it
 // Two accumulators (2 x BN TMEM columns) let the epilogue of tile i overlap the MMAs of tile i+1.
 // Every mbarrier wait is bounded: on expiry the CTA raises a flag, all roles fall through to the common
 // teardown (TMEM is released), and the host sees TTB_ERR_DEVICE_WAIT in the status word.
 #include <cuda.h>
+
+#include <cstdlib>
+#include <type_traits>
 
 #include "ttb_common.cuh"
 
@@ -27,14 +30,18 @@ constexpr long long kWaitCycles = 4000000000LL;  // about two seconds of SM cloc
 
 enum { KIND_F16 = 0, KIND_BF16 = 1, KIND_I8 = 2 };
 
-template <int BN> struct Cfg {
+// TWO = a pair of CTAs (one cluster of two SMs) computes a 256 x BN tile with cta_group::2 MMAs: each CTA stages its
+// own 128 rows of A and its own half (BN/2 rows) of W, so a k-block costs 32 KB of L2->SM traffic per CTA instead of 48.
+template <int BN, bool TWO = false> struct Cfg {
   static constexpr int A_BYTES = BM * BK_BYTES;
-  static constexpr int B_BYTES = BN * BK_BYTES;
+  static constexpr int B_BYTES = (TWO ? BN / 2 : BN) * BK_BYTES;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int STAGES = TWO ? 6 : ((BN == 256) ? 4 : (BN == 128 ? 6 : 8));
   static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+  // Epilogue staging: per epilogue warp two [32 rows x 128 B] swizzled tiles that TMA stores read (BN >= 64 only).
+  static constexpr int STAGING_BYTES = (BN >= 64) ? 4 * 2 * 4096 : 0;
   static constexpr int BAR_BYTES = 256;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + slack for 1024-byte alignment
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES + 1024;  // + slack for 1024-byte alignment
 };
 
 struct GemmParams {
@@ -47,7 +54,9 @@ struct GemmParams {
   const float* row_scale;  // int8: per-row activation scale
   const float* w_scale;    // int8: device scalar, weight scale
   int epilogue;
+  int tma_store;           // 1: the output tile goes through shared memory and TMA stores (needs aligned, 16-byte-multiple rows)
   int* status;
+  long long* prof;         // optional [grid][8] cycle counters (debugging aid, see TTB_GEMM_PROF)
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------
@@ -127,6 +136,90 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t adesc, uint64_t b
   }
 }
 
+// ---- two-CTA (cluster of 2) variants --------------------------------------------------------------
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared-window address: "same offset in CTA 0"
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t local_bar, uint32_t target_rank) {
+  asm volatile(
+      "{\n"
+      ".reg .b32 ra;\n"
+      "mapa.shared::cluster.u32 ra, %0, %1;\n"
+      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n"
+      "}\n" ::"r"(local_bar),
+      "r"(target_rank)
+      : "memory");
+}
+// Tile load issued by either CTA of the pair into its own shared memory; the bytes are counted on CTA 0's barrier.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(map), "r"(bar & kPeerBitMask), "r"(x), "r"(y)
+      : "memory");
+}
+// Arrives (once the MMAs issued so far have completed) on the barrier at this offset in both CTAs of the pair.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(mask)
+               : "memory");
+}
+template <int KIND>
+__device__ __forceinline__ void umma_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  if (KIND == KIND_I8) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+
+// MMA with both shared-memory descriptors given as (low word, shared high word).
+template <int KIND, bool TWO>
+__device__ __forceinline__ void umma_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
+                                        uint32_t accumulate) {
+#define TTB_UMMA_ASM(GROUP, KINDSTR)                                                        \
+  asm volatile(                                                                             \
+      "{\n"                                                                                 \
+      ".reg .pred p;\n"                                                                     \
+      ".reg .b64 da, db;\n"                                                                 \
+      "setp.ne.b32 p, %5, 0;\n"                                                             \
+      "mov.b64 da, {%1, %3};\n"                                                             \
+      "mov.b64 db, {%2, %3};\n"                                                             \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KINDSTR " [%0], da, db, %4, p;\n"           \
+      "}\n" ::"r"(d_tmem),                                                                  \
+      "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)                       \
+      : "memory")
+  if (KIND == KIND_I8) {
+    if (TWO) TTB_UMMA_ASM("2", "i8");
+    else TTB_UMMA_ASM("1", "i8");
+  } else {
+    if (TWO) TTB_UMMA_ASM("2", "f16");
+    else TTB_UMMA_ASM("1", "f16");
+  }
+#undef TTB_UMMA_ASM
+}
+
 // 32 lanes x 32 columns of 32-bit accumulators: thread t of the warp receives row (lane base + t).
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -142,6 +235,57 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// TMA store of a [32 rows x 128 B] swizzled shared-memory tile to the output matrix; rows/columns outside the
+// matrix are clipped by the hardware. Completion is tracked per issuing thread in bulk groups.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <typename OutT> __device__ __forceinline__ void unpack8(const uint4& q, float (&f)[8]);
+template <> __device__ __forceinline__ void unpack8<__half>(const uint4& q, float (&f)[8]) {
+  const __half2* h = reinterpret_cast<const __half2*>(&q);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { float2 t = __half22float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+template <> __device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4& q, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+template <typename OutT> __device__ __forceinline__ uint4 pack8(const float* f);
+template <> __device__ __forceinline__ uint4 pack8<__half>(const float* f) {
+  uint4 q;
+  __half2* h = reinterpret_cast<__half2*>(&q);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+  return q;
+}
+template <> __device__ __forceinline__ uint4 pack8<__nv_bfloat16>(const float* f) {
+  uint4 q;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return q;
+}
+
 // Shared-memory matrix descriptor for a K-major operand tile whose rows are 128 bytes, laid out by TMA
 // with the 128-byte swizzle: 8-row groups are 1024 bytes apart (SBO); LBO is not used by this layout.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
@@ -155,10 +299,10 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
 }
 
 // Instruction descriptor: accumulator format, operand formats, both operands K-major, N>>3, M>>4.
-template <int KIND, int BN> __host__ __device__ constexpr uint32_t make_idesc() {
+template <int KIND, int BN, bool TWO = false> __host__ __device__ constexpr uint32_t make_idesc() {
   return (KIND == KIND_I8 ? (2u << 4) | (1u << 7) | (1u << 10)            // S32 accum, signed 8-bit A and B
                           : (1u << 4) | ((uint32_t)KIND << 7) | ((uint32_t)KIND << 10))  // F32 accum, F16(0)/BF16(1)
-         | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+         | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((TWO ? 2 * BM : BM) >> 4) << 24);
 }
 
 __device__ __forceinline__ float tanh_fast(float x) {
@@ -178,18 +322,24 @@ template <typename OutT> __device__ __forceinline__ void load32(const OutT* p, f
 }
 
 // ---- the kernel -----------------------------------------------------------------------------------
-template <int BN, int KIND, typename OutT>
+template <int BN, int KIND, typename OutT, bool TWO>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
-  using C = Cfg<BN>;
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmO, const GemmParams p) {
+  using C = Cfg<BN, TWO>;
   constexpr int BK_ELEMS = (KIND == KIND_I8) ? BK_BYTES : BK_BYTES / 2;
-  constexpr uint32_t IDESC = make_idesc<KIND, BN>();
+  constexpr uint32_t IDESC = make_idesc<KIND, BN, TWO>();
+  constexpr int TILE_M = TWO ? 2 * BM : BM;                      // output rows per tile (per CTA pair when TWO)
+  const uint32_t rank = TWO ? cluster_ctarank() : 0u;            // 0 = the CTA that issues the MMAs
+  const int tile0 = TWO ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int tile_step = TWO ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
   const uint32_t tiles = smem_u32(smem);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint8_t* staging = smem + C::STAGES * C::STAGE_BYTES;  // 1024-byte aligned: the tile area is a multiple of 1024
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + C::STAGING_BYTES);
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (C::STAGES + s); };
@@ -199,6 +349,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long t_kernel = p.prof ? clock64() : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
@@ -207,24 +358,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+      mbar_init(tempty_bar(a), TWO ? 8 : 4);  // one arrival per epilogue warp (of both CTAs when paired)
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"((uint32_t)C::TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (TWO) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                   "r"((uint32_t)C::TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                   "r"((uint32_t)C::TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (TWO) cluster_sync_all();  // the peer's barriers are initialised before anything signals them remotely
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN;
+  const int num_m = (p.M + TILE_M - 1) / TILE_M, num_n = (p.N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (p.K + BK_ELEMS - 1) / BK_ELEMS;
 
@@ -234,14 +393,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = tile0; tile < num_tiles && ok; tile += tile_step) {
         const int m_blk = tile / num_n, n_blk = tile % num_n;
         for (int kb = 0; kb < num_kb; ++kb) {
+          const long long t_p = p.prof ? clock64() : 0;
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(full_bar(stage), (uint32_t)C::STAGE_BYTES);
+          if (p.prof) p.prof[blockIdx.x * 8 + 4] += clock64() - t_p;  // producer waiting for a free slot
           const uint32_t a_dst = tiles + stage * C::STAGE_BYTES;
-          tma_load_2d(a_dst, &tmA, full_bar(stage), kb * BK_ELEMS, m_blk * BM);
-          tma_load_2d(a_dst + C::A_BYTES, &tmB, full_bar(stage), kb * BK_ELEMS, n_blk * BN);
+          if (TWO) {
+            // CTA 0's barrier counts the bytes of both CTAs; only CTA 0 arms it.
+            if (rank == 0) mbar_expect_tx(full_bar(stage), 2u * (uint32_t)C::STAGE_BYTES);
+            tma_load_2d_pair(a_dst, &tmA, full_bar(stage), kb * BK_ELEMS, m_blk * TILE_M + (int)rank * BM);
+            tma_load_2d_pair(a_dst + C::A_BYTES, &tmB, full_bar(stage), kb * BK_ELEMS, n_blk * BN + (int)rank * (BN / 2));
+          } else {
+            mbar_expect_tx(full_bar(stage), (uint32_t)C::STAGE_BYTES);
+            tma_load_2d(a_dst, &tmA, full_bar(stage), kb * BK_ELEMS, m_blk * BM);
+            tma_load_2d(a_dst + C::A_BYTES, &tmB, full_bar(stage), kb * BK_ELEMS, n_blk * BN);
+          }
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -256,31 +424,47 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int acc_iter = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++acc_iter) {
+      // Descriptors differ only in the start-address field of their low word, so the loop below advances that
+      // word with one add per MMA instead of rebuilding 64-bit descriptors (this single thread's instruction
+      // stream is what paces the tensor core).
+      constexpr uint32_t DESC_HI = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);  // SBO, version, 128-byte swizzle
+      const uint32_t a_lo0 = ((tiles & 0x3FFFFu) >> 4) | (1u << 16);
+      uint32_t a_lo = a_lo0;
+      for (int tile = tile0; tile < num_tiles && ok; tile += tile_step, ++acc_iter) {
         const int acc = acc_iter & 1;
         const uint32_t acc_phase = (uint32_t)(acc_iter >> 1) & 1u;
+        long long t_a = p.prof ? clock64() : 0;
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        if (p.prof) p.prof[blockIdx.x * 8 + 0] += clock64() - t_a;  // MMA thread waiting for a free accumulator
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        uint32_t accumulate = 0;
         for (int kb = 0; kb < num_kb; ++kb) {
+          if (p.prof) t_a = clock64();
           if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t a_addr = tiles + stage * C::STAGE_BYTES;
-          const uint32_t b_addr = a_addr + C::A_BYTES;
+          if (p.prof) p.prof[blockIdx.x * 8 + 1] += clock64() - t_a;  // MMA thread waiting for operands
+          const uint32_t b_lo = a_lo + (uint32_t)(C::A_BYTES >> 4);
 #pragma unroll
           for (int k = 0; k < BK_BYTES / UMMA_K_BYTES; ++k) {
-            umma<KIND>(d_tmem, make_smem_desc(a_addr + k * UMMA_K_BYTES), make_smem_desc(b_addr + k * UMMA_K_BYTES), IDESC,
-                       (uint32_t)((kb | k) != 0));
+            umma_lo<KIND, TWO>(d_tmem, a_lo + (uint32_t)(k * (UMMA_K_BYTES >> 4)), b_lo + (uint32_t)(k * (UMMA_K_BYTES >> 4)), DESC_HI,
+                               IDESC, accumulate);
+            accumulate = 1;
           }
-          tc_commit(empty_bar(stage));  // the slot is free once these MMAs have read it
-          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+          // the slot is free (in both CTAs when paired) once these MMAs have read it
+          if (TWO) tc_commit_pair(empty_bar(stage));
+          else tc_commit(empty_bar(stage));
+          a_lo += (uint32_t)(C::STAGE_BYTES >> 4);
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; a_lo = a_lo0; }
         }
-        if (ok) tc_commit(tfull_bar(acc));  // accumulator complete
+        if (ok) {  // accumulator complete: wake the epilogue warps (of both CTAs when paired)
+          if (TWO) tc_commit_pair(tfull_bar(acc));
+          else tc_commit(tfull_bar(acc));
+        }
       }
     }
     __syncwarp();
@@ -294,19 +478,139 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const bool vec_ok = (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
                         (!bias || (reinterpret_cast<uintptr_t>(bias) & 15) == 0) &&
                         (!residual || ((p.ldr % 8 == 0) && (reinterpret_cast<uintptr_t>(residual) & 15) == 0));
+    const bool use_tma = (BN >= 64) && p.tma_store;
+    uint8_t* my_stage = staging + (warp - 2) * 2 * 4096;  // this warp's two [32 rows x 128 B] staging tiles
+    int store_iter = 0;
     int acc_iter = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++acc_iter) {
+    // Pulls a tile's residual rows towards L2 ahead of time, so the epilogue's loads do not each pay a DRAM
+    // round trip: lane l touches the four 128-byte lines of row l that the tile covers.
+    auto prefetch_residual = [&](int t) {
+      if (p.epilogue != TTB_EPI_BIAS_RESIDUAL || t >= num_tiles) return;
+      const int r = (t / num_n) * TILE_M + (int)rank * BM + quad * 32 + lane, c0 = (t % num_n) * BN;
+      if (r >= p.M) return;
+      const OutT* rp = residual + (long long)r * p.ldr + c0;
+#pragma unroll
+      for (int c = 0; c < BN; c += 64)
+        if (c0 + c < p.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(rp + c));
+    };
+    // Coalesced fetch of a [32 rows x 64 columns] residual block: 8 lanes per 128-byte row, 4 rows per instruction.
+    auto load_residual = [&](uint4 (&dst)[8], int rb, int c0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int grow = rb + i * 4 + (lane >> 3), gcol = c0 + (lane & 7) * 8;
+        dst[i] = (grow < p.M && gcol < p.N) ? __ldg(reinterpret_cast<const uint4*>(residual + (long long)grow * p.ldr + gcol))
+                                            : make_uint4(0, 0, 0, 0);
+      }
+    };
+    prefetch_residual(tile0);
+    auto release_accumulator = [&](int a) {  // one arrival per epilogue warp on the MMA-issuing CTA's barrier
+      if (TWO && rank != 0) mbar_arrive_remote(tempty_bar(a), 0);
+      else mbar_arrive(tempty_bar(a));
+    };
+    for (int tile = tile0; tile < num_tiles; tile += tile_step, ++acc_iter) {
       const int m_blk = tile / num_n, n_blk = tile % num_n;
       const int acc = acc_iter & 1;
       const uint32_t acc_phase = (uint32_t)(acc_iter >> 1) & 1u;
+      const int row_base = m_blk * TILE_M + (int)rank * BM + quad * 32;
+      const int row = row_base + lane;
+      uint4 res[8];
+      if (use_tma && p.epilogue == TTB_EPI_BIAS_RESIDUAL) load_residual(res, row_base, n_blk * BN);  // first chunk, before the wait
+      const long long t_e = p.prof ? clock64() : 0;
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) break;
       tc_fence_after();
-      const int row = m_blk * BM + quad * 32 + lane;
+      if (p.prof && warp == 2 && lane == 0) p.prof[blockIdx.x * 8 + 2] += clock64() - t_e;  // epilogue waiting for an accumulator
+      prefetch_residual(tile + tile_step);  // the next tile's rows, a whole mainloop ahead
       const float rs = (KIND == KIND_I8 && row < p.M) ? p.row_scale[row] * w_scale : 1.0f;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
+      if (use_tma) {
+        // ---- 64 output columns at a time: TMEM -> registers -> (bias, activation, residual) -> swizzled shared
+        //      memory tile -> one TMA store per warp. Residual rows are fetched with coalesced 16-byte loads
+        //      (8 lanes per 128-byte row) one chunk ahead and handed over through the same tile.
+        constexpr int kChunks = (BN >= 64) ? BN / 64 : 1;
+#pragma unroll 1
+        for (int cc = 0; cc < kChunks; ++cc) {
+          const int col0 = n_blk * BN + cc * 64;
+          const bool last_chunk = (cc == kChunks - 1) || (col0 + 64 >= p.N);
+          if (col0 >= p.N) break;  // warp-uniform
+          uint8_t* buf = my_stage + (store_iter & 1) * 4096;
+          // residual rows of the NEXT chunk are requested now and consumed one chunk later
+          uint4 nxt[8];
+          if (p.epilogue == TTB_EPI_BIAS_RESIDUAL && cc + 1 < kChunks) load_residual(nxt, row_base, col0 + 64);
+          uint32_t r0[32], r1[32];
+          tmem_ld32_issue(taddr + (uint32_t)(cc * 64), r0);
+          tmem_ld32_issue(taddr + (uint32_t)(cc * 64 + 32), r1);
+          tmem_ld_wait();
+          if (last_chunk) {  // the accumulator is in registers: hand the TMEM stage back to the MMA warp now
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) release_accumulator(acc);
+          }
+          float v[64];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] = (KIND == KIND_I8) ? (float)(int)r0[j] * rs : __uint_as_float(r0[j]);
+            v[32 + j] = (KIND == KIND_I8) ? (float)(int)r1[j] * rs : __uint_as_float(r1[j]);
+          }
+          if (p.epilogue != TTB_EPI_NONE) {
+#pragma unroll
+            for (int g8 = 0; g8 < 8; ++g8) {
+              if (col0 + g8 * 8 < p.N) {
+                float b[8];
+                unpack8<OutT>(__ldg(reinterpret_cast<const uint4*>(bias + col0 + g8 * 8)), b);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[g8 * 8 + j] += b[j];
+              }
+            }
+          }
+          if (p.epilogue == TTB_EPI_BIAS_GELU) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) {
+              const float x = v[j];
+              v[j] = x * 0.5f * (1.0f + tanh_fast(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+            }
+          } else if (p.epilogue == TTB_EPI_BIAS_TANH) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = tanh_fast(v[j]);
+          }
+          // the TMA store that last read this buffer (two chunks ago) must have finished reading it
+          if (lane == 0) bulk_wait_read<1>();
+          __syncwarp();
+          if (p.epilogue == TTB_EPI_BIAS_RESIDUAL) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = i * 4 + (lane >> 3), ch = lane & 7;
+              *reinterpret_cast<uint4*>(buf + r * 128 + ((ch ^ (r & 7)) << 4)) = res[i];
+            }
+            __syncwarp();
+#pragma unroll
+            for (int g8 = 0; g8 < 8; ++g8) {
+              float q[8];
+              unpack8<OutT>(*reinterpret_cast<const uint4*>(buf + lane * 128 + ((g8 ^ (lane & 7)) << 4)), q);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[g8 * 8 + j] += q[j];
+            }
+          }
+#pragma unroll
+          for (int g8 = 0; g8 < 8; ++g8)
+            *reinterpret_cast<uint4*>(buf + lane * 128 + ((g8 ^ (lane & 7)) << 4)) = pack8<OutT>(&v[g8 * 8]);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmO, smem_u32(buf), col0, row_base);
+            bulk_commit();
+          }
+          ++store_iter;
+          if (p.epilogue == TTB_EPI_BIAS_RESIDUAL) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) res[i] = nxt[i];
+          }
+        }
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), r);
+        tmem_ld32(taddr + (uint32_t)(c * 32), r);
         const int col0 = n_blk * BN + c * 32;
         if (row >= p.M || col0 >= p.N) continue;
         float v[32];
@@ -360,18 +664,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (lane == 0) release_accumulator(acc);
     }
+    // every TMA store issued by this warp must be complete before its shared memory goes away
+    if (use_tma && lane == 0) bulk_wait<0>();
+    __syncwarp();
   }
 
   // ------------------------------------------------------------------ teardown (all roles reach this)
   tc_fence_before();
   __syncthreads();
+  if (TWO) cluster_sync_all();  // neither CTA leaves while the other may still read its shared memory or signal its barriers
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::TMEM_COLS) : "memory");
+    if (TWO) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::TMEM_COLS) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::TMEM_COLS) : "memory");
   }
   if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, (int)TTB_ERR_DEVICE_WAIT);
+  if (p.prof && threadIdx.x == 0) p.prof[blockIdx.x * 8 + 3] += clock64() - t_kernel;  // whole CTA
 }
 
 // ---- host side ------------------------------------------------------------------------------------
@@ -391,7 +701,8 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 2-D row-major operand [rows, k] with `ld` elements between rows; box = [box_rows, 128 bytes of k].
+// 2-D row-major matrix [rows, k] with `ld` elements between rows; box = [box_rows, 128 bytes of k], 128-byte swizzle.
+// Used for both operands (K-major tiles) and for the output (32-row x 64-column store boxes).
 int make_map(ttb_ctx* ctx, CUtensorMap* map, int kind, const void* ptr, int64_t rows, int64_t k, int64_t ld, int box_rows) {
   EncodeTiledFn enc = encode_fn();
   if (!enc) return fail(ctx, TTB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
@@ -409,35 +720,117 @@ int make_map(ttb_ctx* ctx, CUtensorMap* map, int kind, const void* ptr, int64_t 
   return TTB_OK;
 }
 
-template <int BN, int KIND, typename OutT>
+template <int BN, int KIND, typename OutT, bool TWO>
 int launch_tc(ttb_ctx* ctx, const void* A, int64_t lda, const void* W, const GemmParams& p) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, TWO>;
+  constexpr int TILE_M = TWO ? 2 * BM : BM;
   CUtensorMap tmA, tmB;
   int s = make_map(ctx, &tmA, KIND, A, p.M, p.K, lda, BM);
   if (s) return s;
-  s = make_map(ctx, &tmB, KIND, W, p.N, p.K, p.K, BN);
+  s = make_map(ctx, &tmB, KIND, W, p.N, p.K, p.K, TWO ? BN / 2 : BN);
   if (s) return s;
-  auto kern = gemm_tc_kernel<BN, KIND, OutT>;
-  static bool configured[64] = {};  // per instantiation and device
-  if (ctx->device >= 64 || !configured[ctx->device]) {
-    TTB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-    if (ctx->device < 64) configured[ctx->device] = true;
+  GemmParams q = p;
+  CUtensorMap tmO = tmA;  // placeholder when the direct-store epilogue is used
+  const bool aligned16 = ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.bias) |
+                           reinterpret_cast<uintptr_t>(p.residual)) & 15) == 0;
+  q.tma_store = (BN >= 64 && aligned16 && p.ldo % 8 == 0 && p.N % 8 == 0 && (!p.residual || p.ldr % 8 == 0)) ? 1 : 0;
+  if (q.tma_store) {
+    const int out_kind = std::is_same<OutT, __nv_bfloat16>::value ? KIND_BF16 : KIND_F16;
+    s = make_map(ctx, &tmO, out_kind, p.out, p.M, p.N, p.ldo, 32);
+    if (s) return s;
   }
-  const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-  const int grid = num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count;
-  kern<<<grid, kThreads, C::SMEM_BYTES, ctx->stream>>>(tmA, tmB, p);
-  return launched(ctx, "gemm_tc");
+  auto kern = gemm_tc_kernel<BN, KIND, OutT, TWO>;
+  static const bool prof_on = [] { const char* e = getenv("TTB_GEMM_PROF"); return e && e[0] == '1'; }();
+  long long* prof_dev = nullptr;
+  if (prof_on) {
+    cudaMalloc(&prof_dev, 512 * 8 * sizeof(long long));
+    cudaMemset(prof_dev, 0, 512 * 8 * sizeof(long long));
+    q.prof = prof_dev;
+  }
+  auto prof_report = [&](int grid) {
+    if (!prof_on) return;
+    cudaStreamSynchronize(ctx->stream);
+    static long long h[512 * 8];
+    cudaMemcpy(h, prof_dev, sizeof(h), cudaMemcpyDeviceToHost);
+    double a[8] = {};
+    for (int b = 0; b < grid; ++b) for (int j = 0; j < 8; ++j) a[j] += (double)h[b * 8 + j] / grid;
+    fprintf(stderr, "[gemm prof] M=%d N=%d K=%d BN=%d pair=%d grid=%d | avg cycles/CTA: total %.0f, mma waits acc %.0f, mma waits operands %.0f, "
+                    "epilogue waits acc %.0f, producer waits slot %.0f\n", p.M, p.N, p.K, BN, (int)TWO, grid, a[3], a[0], a[1], a[2], a[4]);
+    cudaFree(prof_dev);
+  };
+  static bool configured[64] = {};  // per instantiation and device
+  static int max_clusters[64] = {};
+  const int dev = ctx->device < 64 ? ctx->device : 63;
+  if (ctx->device >= 64 || !configured[dev]) {
+    TTB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    if (TWO) {
+      cudaLaunchConfig_t probe = {};
+      probe.gridDim = dim3(2 * (unsigned)ctx->sm_count);
+      probe.blockDim = dim3(kThreads);
+      probe.dynamicSmemBytes = C::SMEM_BYTES;
+      cudaLaunchAttribute pa[1];
+      pa[0].id = cudaLaunchAttributeClusterDimension;
+      pa[0].val.clusterDim.x = 2;
+      pa[0].val.clusterDim.y = 1;
+      pa[0].val.clusterDim.z = 1;
+      probe.attrs = pa;
+      probe.numAttrs = 1;
+      int n = 0;
+      TTB_CUDA(ctx, cudaOccupancyMaxActiveClusters(&n, kern, &probe));
+      max_clusters[dev] = n > 0 ? n : 1;
+    }
+    configured[dev] = true;
+  }
+  const int64_t num_tiles = ((p.M + TILE_M - 1) / TILE_M) * (int64_t)((p.N + BN - 1) / BN);
+  if (!TWO) {
+    const int grid = (int)(num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count);
+    kern<<<grid, kThreads, C::SMEM_BYTES, ctx->stream>>>(tmA, tmB, tmO, q);
+    prof_report(grid);
+    return launched(ctx, "gemm_tc");
+  }
+  const int clusters = (int)(num_tiles < max_clusters[dev] ? num_tiles : max_clusters[dev]);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * (unsigned)clusters);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmO, q);
+  if (e != cudaSuccess) return fail(ctx, TTB_ERR_CUDA, "cluster launch of gemm_tc failed: %s", cudaGetErrorString(e));
+  prof_report(2 * clusters);
+  return launched(ctx, "gemm_tc_pair");
+}
+
+// TTB_GEMM_PAIR=0 disables the two-CTA variant (a debugging switch; it is on by default).
+bool pair_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("TTB_GEMM_PAIR");
+    return !(e && e[0] == '0');
+  }();
+  return on;
 }
 
 template <int KIND, typename OutT>
 int pick_tile(ttb_ctx* ctx, const void* A, int64_t lda, const void* W, const GemmParams& p) {
-  // Largest N-tile that still gives every SM a tile; small problems use narrow tiles to spread over SMs.
+  // Large problems: CTA pairs on 256 x 256 tiles (less L2->SM traffic per flop). Otherwise the largest single-CTA
+  // N-tile that still gives every SM a tile; small problems use narrow tiles to spread over SMs.
   const int64_t num_m = (p.M + BM - 1) / BM;
   auto tiles = [&](int bn) { return num_m * ((p.N + bn - 1) / bn); };
-  if (tiles(256) >= ctx->sm_count) return launch_tc<256, KIND, OutT>(ctx, A, lda, W, p);
-  if (tiles(128) >= ctx->sm_count) return launch_tc<128, KIND, OutT>(ctx, A, lda, W, p);
-  if (tiles(64) >= ctx->sm_count / 2) return launch_tc<64, KIND, OutT>(ctx, A, lda, W, p);
-  return launch_tc<32, KIND, OutT>(ctx, A, lda, W, p);
+  const int64_t pair_tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * (int64_t)((p.N + 255) / 256);
+  // Measured on B200: pairs win once the mainloop is long (K >= 2048); for short K the single-CTA kernel's shorter
+  // pipeline fill and tail win.
+  const int64_t k_bytes = (int64_t)p.K * (KIND == KIND_I8 ? 1 : 2);
+  if (pair_enabled() && pair_tiles >= ctx->sm_count / 2 && k_bytes >= 4096) return launch_tc<256, KIND, OutT, true>(ctx, A, lda, W, p);
+  if (tiles(256) >= ctx->sm_count) return launch_tc<256, KIND, OutT, false>(ctx, A, lda, W, p);
+  if (tiles(128) >= ctx->sm_count) return launch_tc<128, KIND, OutT, false>(ctx, A, lda, W, p);
+  if (tiles(64) >= ctx->sm_count / 2) return launch_tc<64, KIND, OutT, false>(ctx, A, lda, W, p);
+  return launch_tc<32, KIND, OutT, false>(ctx, A, lda, W, p);
 }
 
 int check_linear(ttb_ctx* ctx, const char* what, const void* A, const void* W, const void* bias, const void* residual,
@@ -518,7 +911,7 @@ extern "C" int ttb_linear(ttb_ctx* ctx, int dtype, const void* A, int64_t lda, c
   if (s || M == 0) return s;
   TTB_REQUIRE(ctx, lda >= K && lda % 8 == 0, "linear: lda must be >= K and a multiple of 8");
   DeviceGuard g(ctx->device);
-  GemmParams p{(int)M, (int)N, (int)K, out, ldo, bias, residual, ldr, nullptr, nullptr, epilogue, ctx->d_status};
+  GemmParams p{(int)M, (int)N, (int)K, out, ldo, bias, residual, ldr, nullptr, nullptr, epilogue, 0, ctx->d_status, nullptr};
   if (dtype == TTB_F16) return pick_tile<KIND_F16, __half>(ctx, A, lda, Wp, p);
   return pick_tile<KIND_BF16, __nv_bfloat16>(ctx, A, lda, Wp, p);
 }
@@ -532,7 +925,7 @@ extern "C" int ttb_linear_int8(ttb_ctx* ctx, int out_dtype, const int8_t* Aq, co
   if (s || M == 0) return s;
   TTB_REQUIRE(ctx, row_scale && w_scale, "linear_int8: null scale pointer");
   DeviceGuard g(ctx->device);
-  GemmParams p{(int)M, (int)N, (int)K, out, ldo, bias, residual, ldr, row_scale, w_scale, epilogue, ctx->d_status};
+  GemmParams p{(int)M, (int)N, (int)K, out, ldo, bias, residual, ldr, row_scale, w_scale, epilogue, 0, ctx->d_status, nullptr};
   if (out_dtype == TTB_F16) return pick_tile<KIND_I8, __half>(ctx, Aq, K, Wq, p);
   return pick_tile<KIND_I8, __nv_bfloat16>(ctx, Aq, K, Wq, p);
 }
