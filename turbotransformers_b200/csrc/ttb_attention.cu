@@ -65,6 +65,13 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, f
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// 2^x by the special-function unit (2 ulp); 2^-inf = +0.
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct AttnParams {
   const void* qkv;
   void* out;
@@ -179,30 +186,40 @@ attention_fwd_kernel(const AttnParams p) {
 
     // ---- scale, mask, online softmax (rows g and g+8 of this warp's 16)
     const int k0 = t * KT;
+    // Per-element masking only where a tile needs it (warp-uniform): a mask tensor, keys past the end of the
+    // sequence, or the causal diagonal. Interior tiles keep the raw scores and fold the scale into the exp2 FMA.
+    const bool edge = (p.mask != nullptr) || (k0 + KT > len) || (p.causal && k0 + KT - 1 > q0 + warp * 16);
+    float sce = sc;
+    if (edge) {
+      sce = 1.0f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = e >> 1;
+          const int key = k0 + j * 8 + t4 * 2 + (e & 1);
+          float v = s[j][e] * sc;
+          const bool dead = key >= len || (p.causal && key > qrow[r]);
+          if (p.mask && !dead && qrow[r] < len) v += mrow[r][key] * kLog2e;
+          s[j][e] = dead ? -INFINITY : v;
+        }
+      }
+    }
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int r = e >> 1;
-        const int key = k0 + j * 8 + t4 * 2 + (e & 1);
-        float v = s[j][e] * sc;
-        bool dead = key >= len || (p.causal && key > qrow[r]);
-        if (p.mask && !dead && qrow[r] < len) v += mrow[r][key] * kLog2e;
-        v = dead ? -INFINITY : v;
-        s[j][e] = v;
-        mx[r] = fmaxf(mx[r], v);
-      }
+      mx[0] = fmaxf(mx[0], fmaxf(s[j][0], s[j][1]));
+      mx[1] = fmaxf(mx[1], fmaxf(s[j][2], s[j][3]));
     }
     float corr[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-      const float m_new = fmaxf(m_run[r], mx[r]);
+      const float m_new = fmaxf(m_run[r], mx[r] * sce);
       // m_new is finite from the first tile on (key 0 is never dead); guard the degenerate all-dead row anyway
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      corr[r] = exp2f(m_run[r] - m_use);
+      corr[r] = ex2(m_run[r] - m_use);
       m_run[r] = m_new;
       mx[r] = m_use;
     }
@@ -212,7 +229,7 @@ attention_fwd_kernel(const AttnParams p) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int r = e >> 1;
-        const float pv = exp2f(s[j][e] - mx[r]);
+        const float pv = ex2(fmaf(s[j][e], sce, -mx[r]));
         s[j][e] = pv;
         rs[r] += pv;
       }
