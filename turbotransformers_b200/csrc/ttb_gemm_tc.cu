@@ -56,7 +56,6 @@ struct GemmParams {
   int epilogue;
   int tma_store;           // 1: the output tile goes through shared memory and TMA stores (needs aligned, 16-byte-multiple rows)
   int* status;
-  long long* prof;         // optional [grid][8] cycle counters (debugging aid, see TTB_GEMM_PROF)
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------
@@ -349,7 +348,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long t_kernel = p.prof ? clock64() : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
@@ -396,9 +394,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int tile = tile0; tile < num_tiles && ok; tile += tile_step) {
         const int m_blk = tile / num_n, n_blk = tile % num_n;
         for (int kb = 0; kb < num_kb; ++kb) {
-          const long long t_p = p.prof ? clock64() : 0;
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
-          if (p.prof) p.prof[blockIdx.x * 8 + 4] += clock64() - t_p;  // producer waiting for a free slot
           const uint32_t a_dst = tiles + stage * C::STAGE_BYTES;
           if (TWO) {
             // CTA 0's barrier counts the bytes of both CTAs; only CTA 0 arms it.
@@ -438,16 +434,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int tile = tile0; tile < num_tiles && ok; tile += tile_step, ++acc_iter) {
         const int acc = acc_iter & 1;
         const uint32_t acc_phase = (uint32_t)(acc_iter >> 1) & 1u;
-        long long t_a = p.prof ? clock64() : 0;
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
-        if (p.prof) p.prof[blockIdx.x * 8 + 0] += clock64() - t_a;  // MMA thread waiting for a free accumulator
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         uint32_t accumulate = 0;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (p.prof) t_a = clock64();
           if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
-          if (p.prof) p.prof[blockIdx.x * 8 + 1] += clock64() - t_a;  // MMA thread waiting for operands
           const uint32_t b_lo = a_lo + (uint32_t)(C::A_BYTES >> 4);
 #pragma unroll
           for (int k = 0; k < BK_BYTES / UMMA_K_BYTES; ++k) {
@@ -515,10 +507,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int row = row_base + lane;
       uint4 res[8];
       if (use_tma && p.epilogue == TTB_EPI_BIAS_RESIDUAL) load_residual(res, row_base, n_blk * BN);  // first chunk, before the wait
-      const long long t_e = p.prof ? clock64() : 0;
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) break;
       tc_fence_after();
-      if (p.prof && warp == 2 && lane == 0) p.prof[blockIdx.x * 8 + 2] += clock64() - t_e;  // epilogue waiting for an accumulator
       prefetch_residual(tile + tile_step);  // the next tile's rows, a whole mainloop ahead
       const float rs = (KIND == KIND_I8 && row < p.M) ? p.row_scale[row] * w_scale : 1.0f;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
@@ -681,7 +671,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::TMEM_COLS) : "memory");
   }
   if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, (int)TTB_ERR_DEVICE_WAIT);
-  if (p.prof && threadIdx.x == 0) p.prof[blockIdx.x * 8 + 3] += clock64() - t_kernel;  // whole CTA
 }
 
 // ---- host side ------------------------------------------------------------------------------------
@@ -740,24 +729,6 @@ int launch_tc(ttb_ctx* ctx, const void* A, int64_t lda, const void* W, const Gem
     if (s) return s;
   }
   auto kern = gemm_tc_kernel<BN, KIND, OutT, TWO>;
-  static const bool prof_on = [] { const char* e = getenv("TTB_GEMM_PROF"); return e && e[0] == '1'; }();
-  long long* prof_dev = nullptr;
-  if (prof_on) {
-    cudaMalloc(&prof_dev, 512 * 8 * sizeof(long long));
-    cudaMemset(prof_dev, 0, 512 * 8 * sizeof(long long));
-    q.prof = prof_dev;
-  }
-  auto prof_report = [&](int grid) {
-    if (!prof_on) return;
-    cudaStreamSynchronize(ctx->stream);
-    static long long h[512 * 8];
-    cudaMemcpy(h, prof_dev, sizeof(h), cudaMemcpyDeviceToHost);
-    double a[8] = {};
-    for (int b = 0; b < grid; ++b) for (int j = 0; j < 8; ++j) a[j] += (double)h[b * 8 + j] / grid;
-    fprintf(stderr, "[gemm prof] M=%d N=%d K=%d BN=%d pair=%d grid=%d | avg cycles/CTA: total %.0f, mma waits acc %.0f, mma waits operands %.0f, "
-                    "epilogue waits acc %.0f, producer waits slot %.0f\n", p.M, p.N, p.K, BN, (int)TWO, grid, a[3], a[0], a[1], a[2], a[4]);
-    cudaFree(prof_dev);
-  };
   static bool configured[64] = {};  // per instantiation and device
   static int max_clusters[64] = {};
   const int dev = ctx->device < 64 ? ctx->device : 63;
@@ -785,7 +756,6 @@ int launch_tc(ttb_ctx* ctx, const void* A, int64_t lda, const void* W, const Gem
   if (!TWO) {
     const int grid = (int)(num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count);
     kern<<<grid, kThreads, C::SMEM_BYTES, ctx->stream>>>(tmA, tmB, tmO, q);
-    prof_report(grid);
     return launched(ctx, "gemm_tc");
   }
   const int clusters = (int)(num_tiles < max_clusters[dev] ? num_tiles : max_clusters[dev]);
@@ -803,7 +773,6 @@ int launch_tc(ttb_ctx* ctx, const void* A, int64_t lda, const void* W, const Gem
   cfg.numAttrs = 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmO, q);
   if (e != cudaSuccess) return fail(ctx, TTB_ERR_CUDA, "cluster launch of gemm_tc failed: %s", cudaGetErrorString(e));
-  prof_report(2 * clusters);
   return launched(ctx, "gemm_tc_pair");
 }
 
@@ -911,7 +880,7 @@ extern "C" int ttb_linear(ttb_ctx* ctx, int dtype, const void* A, int64_t lda, c
   if (s || M == 0) return s;
   TTB_REQUIRE(ctx, lda >= K && lda % 8 == 0, "linear: lda must be >= K and a multiple of 8");
   DeviceGuard g(ctx->device);
-  GemmParams p{(int)M, (int)N, (int)K, out, ldo, bias, residual, ldr, nullptr, nullptr, epilogue, 0, ctx->d_status, nullptr};
+  GemmParams p{(int)M, (int)N, (int)K, out, ldo, bias, residual, ldr, nullptr, nullptr, epilogue, 0, ctx->d_status};
   if (dtype == TTB_F16) return pick_tile<KIND_F16, __half>(ctx, A, lda, Wp, p);
   return pick_tile<KIND_BF16, __nv_bfloat16>(ctx, A, lda, Wp, p);
 }
@@ -925,7 +894,7 @@ extern "C" int ttb_linear_int8(ttb_ctx* ctx, int out_dtype, const int8_t* Aq, co
   if (s || M == 0) return s;
   TTB_REQUIRE(ctx, row_scale && w_scale, "linear_int8: null scale pointer");
   DeviceGuard g(ctx->device);
-  GemmParams p{(int)M, (int)N, (int)K, out, ldo, bias, residual, ldr, row_scale, w_scale, epilogue, 0, ctx->d_status, nullptr};
+  GemmParams p{(int)M, (int)N, (int)K, out, ldo, bias, residual, ldr, row_scale, w_scale, epilogue, 0, ctx->d_status};
   if (out_dtype == TTB_F16) return pick_tile<KIND_I8, __half>(ctx, Aq, K, Wq, p);
   return pick_tile<KIND_I8, __nv_bfloat16>(ctx, Aq, K, Wq, p);
 }
