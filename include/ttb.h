@@ -176,6 +176,22 @@ int ttb_linear(ttb_ctx* ctx, int dtype, const void* A, int64_t lda, const void* 
 int ttb_linear_int8(ttb_ctx* ctx, int out_dtype, const int8_t* Aq, const float* row_scale, const int8_t* Wq,
                     const float* w_scale, const void* bias, const void* residual, int64_t ldr, int64_t M,
                     int64_t N, int64_t K, int epilogue, void* out, int64_t ldo);
+/* int8 Linear with the activations quantised on the fly, for callers that cannot allocate device memory.
+ * This entry point has no counterpart in the reference. It exists for hosts that pass the library only their
+ * inputs and outputs: a server whose arena already owns all device memory, code inside a region where the CUDA
+ * allocator must not be entered, or a foreign runtime whose FFI cannot own device buffers. It computes
+ *   out = epilogue(quantize_rows(x) . Wq^T * row_scale * *w_scale + bias)        (x: [M,K] F16/BF16, out likewise)
+ * exactly like ttb_quantize_rows_int8 followed by ttb_linear_int8, but keeps the quantised activations and their
+ * row scales in a fixed 8.25 MiB array inside the library image, which every GPU that loads the library holds
+ * until the process exits. Limits: M <= 65536 and M*K <= 8388608; larger problems get TTB_ERR_INVALID and a
+ * message that names the two-call path. It calls no allocator of any kind. The first call on each device looks
+ * the array's address up (one runtime query); make that call before starting any stream capture. All calls on a
+ * device share the one array and nothing in it carries over between calls, but two calls whose kernels overlap
+ * on the GPU (different streams, or graphs replayed concurrently) would race on it: serialise them. */
+int ttb_linear_int8_dynamic_noalloc(ttb_ctx* ctx, int dtype, const void* x, const int8_t* Wq, const float* w_scale,
+                                    const void* bias, const void* residual, int64_t ldr, int64_t M, int64_t N,
+                                    int64_t K, int epilogue, void* out, int64_t ldo);
+
 /* Per-row dynamic symmetric int8 quantisation: scale[m] = max|x[m,:]|/127, xq = rint(x/scale). */
 int ttb_quantize_rows_int8(ttb_ctx* ctx, int dtype, const void* x, int64_t M, int64_t K, int8_t* xq,
                            float* row_scale);

@@ -59,6 +59,7 @@ SIGNATURES = {
     "ttb_prepack_weight_int8": (i32, [p, i32, p, i32, i64, i64, p, p]),
     "ttb_linear": (i32, [p, i32, p, i64, p, p, p, i64, i64, i64, i64, i32, p, i64]),
     "ttb_linear_int8": (i32, [p, i32, p, p, p, p, p, p, i64, i64, i64, i64, i32, p, i64]),
+    "ttb_linear_int8_dynamic_noalloc": (i32, [p, i32, p, p, p, p, p, i64, i64, i64, i64, i32, p, i64]),
     "ttb_quantize_rows_int8": (i32, [p, i32, p, i64, i64, p, p]),
     "ttb_attention_fwd": (i32, [p, i32, p, p, i64, i64, i64, i64, p, i64, i64, i32, f32, p]),
     "ttb_embedding_ln": (i32, [p, i32, p, p, p, p, i64, i64, i64, p, p, p, p, p, i64, i64, i64, i64, f32, p]),
