@@ -216,7 +216,7 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
     torch.set_grad_enabled(False)
     import turbotransformers_b200 as tt
-    from turbotransformers_b200 import synthetic
+    from turbotransformers_b200 import sharding, synthetic
     cxx = tt._cxx_module
     peaks = load_peaks()
 
@@ -255,10 +255,7 @@ def run_ours(args):
         barrier()
         ms = e0.elapsed_time(e1)
         launches = cxx.launch_count(local) - l0
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
+        ms = sharding.reduce_max_ms(ms, dev)  # the job is as slow as its slowest rank
         return ms, launches
 
     sampler = ClockSampler(local)
