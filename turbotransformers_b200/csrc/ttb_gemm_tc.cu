@@ -25,7 +25,7 @@ namespace {
 constexpr int BM = 128;          // rows of A per tile == TMEM lanes
 constexpr int BK_BYTES = 128;    // bytes of K per ring slot row: one 128-byte swizzle span
 constexpr int UMMA_K_BYTES = 32; // K bytes consumed by one tcgen05.mma (16 x 16-bit, 32 x 8-bit)
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;    // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue (two per TMEM lane quarter)
 constexpr long long kWaitCycles = 4000000000LL;  // about two seconds of SM clock
 
 enum { KIND_F16 = 0, KIND_BF16 = 1, KIND_I8 = 2 };
@@ -38,8 +38,8 @@ template <int BN, bool TWO = false> struct Cfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = TWO ? 6 : ((BN == 256) ? 4 : (BN == 128 ? 6 : 8));
   static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
-  // Epilogue staging: per epilogue warp two [32 rows x 128 B] swizzled tiles that TMA stores read (BN >= 64 only).
-  static constexpr int STAGING_BYTES = (BN >= 64) ? 4 * 2 * 4096 : 0;
+  // Epilogue staging: per epilogue warp one [32 rows x 128 B] swizzled tile that its TMA stores read (BN >= 64 only).
+  static constexpr int STAGING_BYTES = (BN >= 64) ? 8 * 4096 : 0;
   static constexpr int BAR_BYTES = 256;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES + 1024;  // + slack for 1024-byte alignment
 };
@@ -356,7 +356,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), TWO ? 8 : 4);  // one arrival per epilogue warp (of both CTAs when paired)
+      mbar_init(tempty_bar(a), TWO ? 16 : 8);  // one arrival per epilogue warp (of both CTAs when paired)
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -461,8 +461,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
-    const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    // Two warps share each TMEM lane quarter and split the tile's 64-column chunks between them, so one warp's
+    // TMEM / shared-memory / store latencies are covered by the other warp on the same scheduler.
+    const int quad = warp & 3;          // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
+    const int half = (warp - 2) >> 2;   // which half of the tile's column chunks this warp takes
     const OutT* bias = static_cast<const OutT*>(p.bias);
     const OutT* residual = static_cast<const OutT*>(p.residual);
     OutT* out = static_cast<OutT*>(p.out);
@@ -471,8 +474,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         (!bias || (reinterpret_cast<uintptr_t>(bias) & 15) == 0) &&
                         (!residual || ((p.ldr % 8 == 0) && (reinterpret_cast<uintptr_t>(residual) & 15) == 0));
     const bool use_tma = (BN >= 64) && p.tma_store;
-    uint8_t* my_stage = staging + (warp - 2) * 2 * 4096;  // this warp's two [32 rows x 128 B] staging tiles
-    int store_iter = 0;
+    uint8_t* buf = staging + (warp - 2) * 4096;  // this warp's [32 rows x 128 B] staging tile
     int acc_iter = 0;
     // Pulls a tile's residual rows towards L2 ahead of time, so the epilogue's loads do not each pay a DRAM
     // round trip: lane l touches the four 128-byte lines of row l that the tile covers.
@@ -505,65 +507,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t acc_phase = (uint32_t)(acc_iter >> 1) & 1u;
       const int row_base = m_blk * TILE_M + (int)rank * BM + quad * 32;
       const int row = row_base + lane;
+      constexpr int kChunks = (BN >= 64) ? BN / 64 : 1;
+      constexpr int kPerWarp = (kChunks >= 2) ? kChunks / 2 : 1;
+      // this warp's chunks of the tile: [c_beg, c_end), clipped to the columns that exist
+      const int valid_chunks = min(kChunks, (p.N - n_blk * BN + 63) / 64);
+      const int c_beg = (kChunks >= 2) ? half * kPerWarp : 0;
+      const int c_end = (kChunks >= 2 || half == 0) ? min(c_beg + kPerWarp, valid_chunks) : 0;
+      const bool staged_work = use_tma && c_beg < c_end;
       uint4 res[8];
-      if (use_tma && p.epilogue == TTB_EPI_BIAS_RESIDUAL) load_residual(res, row_base, n_blk * BN);  // first chunk, before the wait
+      if (staged_work && p.epilogue == TTB_EPI_BIAS_RESIDUAL) load_residual(res, row_base, n_blk * BN + c_beg * 64);  // before the wait
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) break;
       tc_fence_after();
       prefetch_residual(tile + tile_step);  // the next tile's rows, a whole mainloop ahead
       const float rs = (KIND == KIND_I8 && row < p.M) ? p.row_scale[row] * w_scale : 1.0f;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
-      if (use_tma) {
+      if (use_tma || half == 1) {
+        if (!staged_work) {  // nothing to do for this warp on this tile: just hand the accumulator back
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) release_accumulator(acc);
+          continue;
+        }
         // ---- 64 output columns at a time: TMEM -> registers -> (bias, activation, residual) -> swizzled shared
         //      memory tile -> one TMA store per warp. Residual rows are fetched with coalesced 16-byte loads
-        //      (8 lanes per 128-byte row) one chunk ahead and handed over through the same tile.
-        constexpr int kChunks = (BN >= 64) ? BN / 64 : 1;
+        //      (8 lanes per 128-byte row) and handed over through the same tile.
 #pragma unroll 1
-        for (int cc = 0; cc < kChunks; ++cc) {
+        for (int cc = c_beg; cc < c_end; ++cc) {
           const int col0 = n_blk * BN + cc * 64;
-          const bool last_chunk = (cc == kChunks - 1) || (col0 + 64 >= p.N);
-          if (col0 >= p.N) break;  // warp-uniform
-          uint8_t* buf = my_stage + (store_iter & 1) * 4096;
-          // residual rows of the NEXT chunk are requested now and consumed one chunk later
-          uint4 nxt[8];
-          if (p.epilogue == TTB_EPI_BIAS_RESIDUAL && cc + 1 < kChunks) load_residual(nxt, row_base, col0 + 64);
-          uint32_t r0[32], r1[32];
-          tmem_ld32_issue(taddr + (uint32_t)(cc * 64), r0);
-          tmem_ld32_issue(taddr + (uint32_t)(cc * 64 + 32), r1);
-          tmem_ld_wait();
-          if (last_chunk) {  // the accumulator is in registers: hand the TMEM stage back to the MMA warp now
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) release_accumulator(acc);
-          }
-          float v[64];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            v[j] = (KIND == KIND_I8) ? (float)(int)r0[j] * rs : __uint_as_float(r0[j]);
-            v[32 + j] = (KIND == KIND_I8) ? (float)(int)r1[j] * rs : __uint_as_float(r1[j]);
-          }
-          if (p.epilogue != TTB_EPI_NONE) {
-#pragma unroll
-            for (int g8 = 0; g8 < 8; ++g8) {
-              if (col0 + g8 * 8 < p.N) {
-                float b[8];
-                unpack8<OutT>(__ldg(reinterpret_cast<const uint4*>(bias + col0 + g8 * 8)), b);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[g8 * 8 + j] += b[j];
-              }
-            }
-          }
-          if (p.epilogue == TTB_EPI_BIAS_GELU) {
-#pragma unroll
-            for (int j = 0; j < 64; ++j) {
-              const float x = v[j];
-              v[j] = x * 0.5f * (1.0f + tanh_fast(0.7978845608028654f * (x + 0.044715f * x * x * x)));
-            }
-          } else if (p.epilogue == TTB_EPI_BIAS_TANH) {
-#pragma unroll
-            for (int j = 0; j < 64; ++j) v[j] = tanh_fast(v[j]);
-          }
-          // the TMA store that last read this buffer (two chunks ago) must have finished reading it
-          if (lane == 0) bulk_wait_read<1>();
+          if (cc != c_beg && p.epilogue == TTB_EPI_BIAS_RESIDUAL) load_residual(res, row_base, col0);
+          // the TMA store that last read this warp's staging tile must have finished reading it
+          if (lane == 0) bulk_wait_read<0>();
           __syncwarp();
           if (p.epilogue == TTB_EPI_BIAS_RESIDUAL) {
 #pragma unroll
@@ -572,31 +545,70 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               *reinterpret_cast<uint4*>(buf + r * 128 + ((ch ^ (r & 7)) << 4)) = res[i];
             }
             __syncwarp();
-#pragma unroll
-            for (int g8 = 0; g8 < 8; ++g8) {
-              float q[8];
-              unpack8<OutT>(*reinterpret_cast<const uint4*>(buf + lane * 128 + ((g8 ^ (lane & 7)) << 4)), q);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[g8 * 8 + j] += q[j];
-            }
           }
+          // two 32-column halves, to keep the live register set small
 #pragma unroll
-          for (int g8 = 0; g8 < 8; ++g8)
-            *reinterpret_cast<uint4*>(buf + lane * 128 + ((g8 ^ (lane & 7)) << 4)) = pack8<OutT>(&v[g8 * 8]);
+          for (int hh = 0; hh < 2; ++hh) {
+            const int colh = col0 + hh * 32;
+            uint4 bq[4];
+            if (p.epilogue != TTB_EPI_NONE) {
+#pragma unroll
+              for (int g8 = 0; g8 < 4; ++g8)
+                bq[g8] = (colh + g8 * 8 < p.N) ? __ldg(reinterpret_cast<const uint4*>(bias + colh + g8 * 8)) : make_uint4(0, 0, 0, 0);
+            }
+            uint32_t r0[32];
+            tmem_ld32_issue(taddr + (uint32_t)(cc * 64 + hh * 32), r0);
+            tmem_ld_wait();
+            if (hh == 1 && cc == c_end - 1) {  // this warp's share of the accumulator is in registers: hand it back now
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) release_accumulator(acc);
+            }
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = (KIND == KIND_I8) ? (float)(int)r0[j] * rs : __uint_as_float(r0[j]);
+            if (p.epilogue != TTB_EPI_NONE) {
+#pragma unroll
+              for (int g8 = 0; g8 < 4; ++g8) {
+                float bb[8];
+                unpack8<OutT>(bq[g8], bb);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[g8 * 8 + j] += bb[j];
+              }
+            }
+            if (p.epilogue == TTB_EPI_BIAS_GELU) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {  // 0.5x(1 + tanh(0.79788456(x + 0.044715x^3))), regrouped to six operations
+                const float x = v[j], hx = 0.5f * x;
+                const float t = tanh_fast(x * fmaf(x * x, 0.7978845608028654f * 0.044715f, 0.7978845608028654f));
+                v[j] = fmaf(hx, t, hx);
+              }
+            } else if (p.epilogue == TTB_EPI_BIAS_TANH) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = tanh_fast(v[j]);
+            } else if (p.epilogue == TTB_EPI_BIAS_RESIDUAL) {
+#pragma unroll
+              for (int g8 = 0; g8 < 4; ++g8) {
+                float q[8];
+                unpack8<OutT>(*reinterpret_cast<const uint4*>(buf + lane * 128 + (((hh * 4 + g8) ^ (lane & 7)) << 4)), q);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[g8 * 8 + j] += q[j];
+              }
+            }
+#pragma unroll
+            for (int g8 = 0; g8 < 4; ++g8)
+              *reinterpret_cast<uint4*>(buf + lane * 128 + (((hh * 4 + g8) ^ (lane & 7)) << 4)) = pack8<OutT>(&v[g8 * 8]);
+          }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
           if (lane == 0) {
             tma_store_2d(&tmO, smem_u32(buf), col0, row_base);
             bulk_commit();
           }
-          ++store_iter;
-          if (p.epilogue == TTB_EPI_BIAS_RESIDUAL) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) res[i] = nxt[i];
-          }
         }
         continue;
       }
+      // ---- direct path (narrow tiles or unaligned output): the first warp of each lane quarter walks the tile
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
