@@ -83,6 +83,10 @@ int ttb_plan_activations(ttb_ctx* ctx, int64_t batch, int64_t tokens, int64_t he
 int ttb_memcpy_h2d(ttb_ctx* ctx, void* device_dst, const void* host_src, size_t bytes);
 int ttb_memcpy_d2h(ttb_ctx* ctx, void* host_dst, const void* device_src, size_t bytes);
 
+/* Device-to-device copy of `rows` rows of `width_bytes` between pitched buffers, on the context's stream (asynchronous). */
+int ttb_copy_2d(ttb_ctx* ctx, void* dst, size_t dst_pitch_bytes, const void* src, size_t src_pitch_bytes, size_t width_bytes,
+                size_t rows);
+
 /* ---- A1: kernels::MatMul (turbo_transformers/layers/kernels/mat_mul.cpp:30-118).
  * C[M,N] = alpha * op(A) * op(B) + beta * C, row-major; op = transpose when the flag is non-zero.
  * A is [M,K] (or [K,M] if a_trans), B is [K,N] (or [N,K] if b_trans). Exact-precision SIMT path,
@@ -200,13 +204,14 @@ int ttb_quantize_rows_int8(ttb_ctx* ctx, int dtype, const void* x, int64_t M, in
  * TransposeForScore and all *Pad kernels (multi_headed_attention.cpp:320-354,
  * multi_headed_attention_smart_batch.cpp:362-393) with one kernel that never writes the score matrix.
  *   qkv   : [T, 3*heads*d] rows = tokens, columns q|k|v (bias already added), dtype F16/BF16, d == 64
+ *   total_tokens : T = cu_seqlens[B], the number of rows of qkv (known to the host; bounds the tile loads)
  *   cu_seqlens : device int32 [B+1]; sequence b owns token rows [cu[b], cu[b+1])
  *   mask  : optional fp32 additive mask, element (b, i, j) at mask[b*mask_batch_stride + i*mask_row_stride + j]
  *           (mask_row_stride = 0 for a per-key mask); NULL for none
  *   causal: non-zero masks keys j > i
  *   out   : [T, heads*d]
  */
-int ttb_attention_fwd(ttb_ctx* ctx, int dtype, const void* qkv, const int32_t* cu_seqlens, int64_t B,
+int ttb_attention_fwd(ttb_ctx* ctx, int dtype, const void* qkv, int64_t total_tokens, const int32_t* cu_seqlens, int64_t B,
                       int64_t max_seqlen, int64_t heads, int64_t d, const float* mask,
                       int64_t mask_batch_stride, int64_t mask_row_stride, int causal, float scale, void* out);
 

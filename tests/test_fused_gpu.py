@@ -92,6 +92,27 @@ def test_linear_plain_and_tanh_epilogues_and_strided_io(ctx, dt):
     assert maxdiff(host(out2), linear_oracle(a, w, bias, None, "bias_tanh")) < (4e-3 if dt == "f16" else 2e-2)
 
 
+@pytest.mark.parametrize("M,N,K", [(300, 1001, 256), (2100, 5003, 768)])  # the second runs on CTA pairs
+def test_linear_ragged_width_into_padded_rows_then_compacted(ctx, M, N, K):
+    # how a 50257-wide vocabulary projection runs: no bias, rows padded to a multiple of 8 elements, then ttb_copy_2d
+    dt = "f16"
+    r = rng(N)
+    a = rounded(r.standard_normal((M, K)).astype(np.float32), dt)
+    w = rounded(r.standard_normal((K, N)).astype(np.float32) * 0.05, dt)
+    Wp = prepack(ctx, w, dt)
+    Np = (N + 7) // 8 * 8
+    padded = torch.full((M, Np), 7.0, dtype=torch.float16, device="cuda")
+    ctx.call("linear", code(dt), dev(a, dt), K, Wp, None, None, 0, M, N, K, EPIS["none"], padded, Np)
+    assert ctx.device_status() == _capi.OK
+    want = restate.mat_mul(a, False, w, False)
+    got = host(padded)
+    assert maxdiff(got[:, N:], 7.0) == 0.0  # the padding columns are not written
+    assert maxdiff(got[:, :N], want) < 2.0 ** -10 * max(1.0, float(np.abs(want).max())) + 2e-3
+    out = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    ctx.call("copy_2d", out, N * 2, padded, Np * 2, N * 2, M)
+    assert maxdiff(host(out), got[:, :N]) == 0.0
+
+
 def test_linear_weight_given_as_out_in(ctx):
     # is_trans_weight=True in the reference: the weight arrives as [N,K] and is only converted
     r = rng(5)
@@ -192,24 +213,30 @@ def attention_oracle(qkv, lens, heads, mask=None, causal=False):
     return np.concatenate(outs)
 
 
+@pytest.mark.parametrize("kernel", ["auto", "tensor_memory", "mma_sync"])
 @pytest.mark.parametrize("dt", ["f16", "bf16"])
 @pytest.mark.parametrize("lens,heads", [([128], 12), ([4, 1], 12), ([9, 7, 13], 4), ([37, 5, 128, 64], 12),
-                                        ([511, 8, 300, 65, 64, 63, 1], 12), ([512], 16)])
-def test_attention_varlen(ctx, dt, lens, heads):
+                                        ([511, 8, 300, 65, 64, 63, 1], 12), ([512], 16), ([512, 512, 480], 2)])
+def test_attention_varlen(ctx, dt, lens, heads, kernel, monkeypatch):
+    # both attention kernels are checked on every shape; "auto" is what callers get
+    if kernel != "auto":
+        monkeypatch.setenv("TTB_ATTN_TC", "2" if kernel == "tensor_memory" else "0")
     r = rng(sum(lens))
     H, T = heads * 64, sum(lens)
     qkv = rounded(r.standard_normal((T, 3 * H)).astype(np.float32), dt)
     want = attention_oracle(qkv, lens, heads)
     cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32).cuda()
     out = torch.full((T, H), float("nan"), dtype=TORCH_DT[dt], device="cuda")
-    ctx.call("attention_fwd", code(dt), dev(qkv, dt), cu, len(lens), max(lens), heads, 64, None, 0, 0, 0, 0.125, out)
+    ctx.call("attention_fwd", code(dt), dev(qkv, dt), T, cu, len(lens), max(lens), heads, 64, None, 0, 0, 0, 0.125, out)
     got = host(out)
     assert np.isfinite(got).all()
     assert maxdiff(got, want) < (4e-3 if dt == "f16" else 3e-2)
 
 
+@pytest.mark.parametrize("kernel", ["tensor_memory", "mma_sync"])
 @pytest.mark.parametrize("dt", ["f16", "bf16"])
-def test_attention_masks_and_causal(ctx, dt):
+def test_attention_masks_and_causal(ctx, dt, kernel, monkeypatch):
+    monkeypatch.setenv("TTB_ATTN_TC", "2" if kernel == "tensor_memory" else "0")  # mask tensors always take mma.sync
     r = rng(21)
     lens, heads = [70, 33, 128], 4
     H, T, B, maxL = heads * 64, sum(lens), len(lens), max(lens)
@@ -221,15 +248,15 @@ def test_attention_masks_and_causal(ctx, dt):
     m2 = np.where(r.random((B, maxL)) < 0.25, -10000.0, 0.0).astype(np.float32)
     m2[:, 0] = 0
     out = torch.zeros((T, H), dtype=TORCH_DT[dt], device="cuda")
-    ctx.call("attention_fwd", code(dt), Q, cu, B, maxL, heads, 64, dev(m2), maxL, 0, 0, 0.125, out)
+    ctx.call("attention_fwd", code(dt), Q, T, cu, B, maxL, heads, 64, dev(m2), maxL, 0, 0, 0.125, out)
     assert maxdiff(host(out), attention_oracle(qkv, lens, heads, m2)) < tol
     # per-query mask [B, maxL, maxL]
     m3 = np.where(r.random((B, maxL, maxL)) < 0.25, -1e9, 0.0).astype(np.float32)
     m3[:, :, 0] = 0
-    ctx.call("attention_fwd", code(dt), Q, cu, B, maxL, heads, 64, dev(m3), maxL * maxL, maxL, 0, 0.125, out)
+    ctx.call("attention_fwd", code(dt), Q, T, cu, B, maxL, heads, 64, dev(m3), maxL * maxL, maxL, 0, 0.125, out)
     assert maxdiff(host(out), attention_oracle(qkv, lens, heads, m3)) < tol
     # causal flag == explicit lower-triangular mask
-    ctx.call("attention_fwd", code(dt), Q, cu, B, maxL, heads, 64, None, 0, 0, 1, 0.125, out)
+    ctx.call("attention_fwd", code(dt), Q, T, cu, B, maxL, heads, 64, None, 0, 0, 1, 0.125, out)
     assert maxdiff(host(out), attention_oracle(qkv, lens, heads, None, causal=True)) < tol
 
 
@@ -241,14 +268,14 @@ def test_attention_permutation_property_at_benchmark_size(ctx):
     qkv = torch.randn(T, 3 * H, device="cuda", dtype=torch.float16)
     cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32).cuda()
     out = torch.empty(T, H, device="cuda", dtype=torch.float16)
-    ctx.call("attention_fwd", _capi.F16, qkv, cu, 64, max(lens), heads, 64, None, 0, 0, 0, 0.125, out)
+    ctx.call("attention_fwd", _capi.F16, qkv, T, cu, 64, max(lens), heads, 64, None, 0, 0, 0, 0.125, out)
     starts = np.concatenate([[0], np.cumsum(lens)])
     order = list(range(63, -1, -1))
     qkv_r = torch.cat([qkv[starts[b]:starts[b + 1]] for b in order])
     lens_r = [lens[b] for b in order]
     cu_r = torch.tensor(np.concatenate([[0], np.cumsum(lens_r)]), dtype=torch.int32).cuda()
     out_r = torch.empty_like(out)
-    ctx.call("attention_fwd", _capi.F16, qkv_r, cu_r, 64, max(lens), heads, 64, None, 0, 0, 0, 0.125, out_r)
+    ctx.call("attention_fwd", _capi.F16, qkv_r, T, cu_r, 64, max(lens), heads, 64, None, 0, 0, 0, 0.125, out_r)
     want = torch.cat([out[starts[b]:starts[b + 1]] for b in order])
     assert torch.equal(out_r, want)
     # rows of a softmax-weighted average stay inside the value range of their sequence

@@ -37,6 +37,7 @@ SIGNATURES = {
     "ttb_plan_activations": (i32, [p, i64, i64, i64, i64, i64, i64, i32, C.POINTER(sz)]),
     "ttb_memcpy_h2d": (i32, [p, p, p, sz]),
     "ttb_memcpy_d2h": (i32, [p, p, p, sz]),
+    "ttb_copy_2d": (i32, [p, p, sz, p, sz, sz, sz]),
     "ttb_matmul": (i32, [p, i32, p, i32, p, i32, i64, i64, i64, f32, f32, p]),
     "ttb_batch_matmul": (i32, [p, i32, p, i32, p, i32, i64, i64, i64, i64, f32, f32, p]),
     "ttb_split_add_bias_transpose": (i32, [p, i32, p, p, i64, i64, i64, i64, p, p, p]),
@@ -61,7 +62,7 @@ SIGNATURES = {
     "ttb_linear_int8": (i32, [p, i32, p, p, p, p, p, p, i64, i64, i64, i64, i32, p, i64]),
     "ttb_linear_int8_dynamic_noalloc": (i32, [p, i32, p, p, p, p, p, i64, i64, i64, i64, i32, p, i64]),
     "ttb_quantize_rows_int8": (i32, [p, i32, p, i64, i64, p, p]),
-    "ttb_attention_fwd": (i32, [p, i32, p, p, i64, i64, i64, i64, p, i64, i64, i32, f32, p]),
+    "ttb_attention_fwd": (i32, [p, i32, p, i64, p, i64, i64, i64, i64, p, i64, i64, i32, f32, p]),
     "ttb_embedding_ln": (i32, [p, i32, p, p, p, p, i64, i64, i64, p, p, p, p, p, i64, i64, i64, i64, f32, p]),
     "ttb_build_cu_seqlens": (i32, [p, p, i64, p]),
 }

@@ -79,7 +79,7 @@ void PackedLinear::Int8(bool is_trans, const int8_t** wq, const float** scale) c
 }
 
 void PackedLinear::Forward(const Tensor& x, int64_t M, int epilogue, const void* residual, void* out, bool is_trans,
-                           const char* name) const {
+                           const char* name, int64_t ldo) const {
   const int dt = FloatType(x, name);
   SameTypeDevice(x, weight_, name);
   const int64_t K = in_dim(is_trans), N = out_dim(is_trans);
@@ -87,6 +87,8 @@ void PackedLinear::Forward(const Tensor& x, int64_t M, int epilogue, const void*
   ttb_ctx* c = DeviceContext(x.device_id());
   const void* bias = bias_.is_null() ? nullptr : bias_.raw();
   if (!bias && epilogue == TTB_EPI_BIAS) epilogue = TTB_EPI_NONE;
+  if (ldo == 0) ldo = N;
+  TT_ENFORCE(ldo == N || (dt != TTB_F32 && !use_int8_), "%s: a padded output pitch is only supported on the 16-bit path", name);
   if (dt == TTB_F32) {
     // exact path: the reference's sequence MatMul -> elementwise kernel
     Check(ttb_matmul(c, dt, x.raw(), 0, weight_.raw(), is_trans ? 1 : 0, M, N, K, 1.0f, 0.0f, out), c, name);
@@ -111,7 +113,7 @@ void PackedLinear::Forward(const Tensor& x, int64_t M, int epilogue, const void*
     Check(ttb_linear_int8(c, dt, xq.data<int8_t>(), xs.data<float>(), wq, ws, bias, residual, N, M, N, K, epilogue, out, N), c, name);
     return;
   }
-  Check(ttb_linear(c, dt, x.raw(), K, Packed(is_trans), bias, residual, N, M, N, K, epilogue, out, N), c, name);
+  Check(ttb_linear(c, dt, x.raw(), K, Packed(is_trans), bias, residual, N, M, N, K, epilogue, out, ldo), c, name);
 }
 
 // ===================================================================================================
@@ -279,7 +281,7 @@ void MultiHeadedAttention::Run(const Tensor& x, const Tensor& attention_mask, co
       if (MaskIs2D(attention_mask)) { mbs = Lk; mrs = 0; }
       else { mrs = Lk; mbs = attention_mask.shape(-2) * Lk; }
     }
-    Check(ttb_attention_fwd(c, dt, qkv.raw(), cu, B, maxL, heads, d, mask, mbs, mrs, causal_ ? 1 : 0, scale, context.raw_mut()), c,
+    Check(ttb_attention_fwd(c, dt, qkv.raw(), T, cu, B, maxL, heads, d, mask, mbs, mrs, causal_ ? 1 : 0, scale, context.raw_mut()), c,
           "attention_fwd");
     if (att_score) *att_score = Tensor(nullptr);
   } else {
@@ -513,8 +515,22 @@ void TokenPositionEmbedding::operator()(const Tensor& input_ids, Tensor* output)
 
 void Linear::operator()(const Tensor& input, Tensor* output) const {
   FloatType(input, "Linear input");
-  output->Reshape(input.dtype(), WithLast(input, dense_.out_dim(is_trans_)), kDLCUDA, input.device_id(), "Linear/Reshape");
-  dense_.Forward(input, input.rows(), TTB_EPI_BIAS, nullptr, output->raw_mut(), is_trans_, "Linear");
+  const int dt = core::ToTTBDtype(input.dtype());
+  const int64_t N = dense_.out_dim(is_trans_), M = input.rows();
+  output->Reshape(input.dtype(), WithLast(input, N), kDLCUDA, input.device_id(), "Linear/Reshape");
+  if (dt != TTB_F32 && N % 8 != 0) {
+    // An output row that is not a multiple of 16 bytes (e.g. a 50257-wide vocabulary) would force the GEMM onto scalar
+    // stores. Compute into a row-padded scratch with the fast epilogue, then compact: one extra pass over the output
+    // at copy bandwidth instead of a several-times slower GEMM.
+    const int64_t Np = (N + 7) / 8 * 8;
+    ttb_ctx* c = DeviceContext(input.device_id());
+    Tensor padded(nullptr);
+    padded.Reshape(input.dtype(), {M, Np}, kDLCUDA, input.device_id(), "Linear/padded");
+    dense_.Forward(input, M, TTB_EPI_BIAS, nullptr, padded.raw_mut(), is_trans_, "Linear", Np);
+    Check(ttb_copy_2d(c, output->raw_mut(), (size_t)N * 2, padded.raw(), (size_t)Np * 2, (size_t)N * 2, (size_t)M), c, "Linear/compact");
+    return;
+  }
+  dense_.Forward(input, M, TTB_EPI_BIAS, nullptr, output->raw_mut(), is_trans_, "Linear");
 }
 
 }  // namespace layers

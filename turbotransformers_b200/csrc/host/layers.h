@@ -38,8 +38,9 @@ class PackedLinear {
   bool use_int8() const { return use_int8_; }
 
   // out[M,N] = epilogue(x[M,K] . W + bias); picks the kernel by dtype / int8 flag.
+  // `ldo` (elements between output rows) defaults to N.
   void Forward(const core::Tensor& x, int64_t M, int epilogue, const void* residual, void* out, bool is_trans,
-               const char* name) const;
+               const char* name, int64_t ldo = 0) const;
 
  private:
   core::Tensor weight_, bias_;

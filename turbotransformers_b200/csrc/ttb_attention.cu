@@ -289,8 +289,14 @@ attention_fwd_kernel(const AttnParams p) {
 
 }  // namespace
 
-extern "C" int ttb_attention_fwd(ttb_ctx* ctx, int dtype, const void* qkv, const int32_t* cu_seqlens, int64_t B,
-                                 int64_t max_seqlen, int64_t heads, int64_t d, const float* mask,
+namespace ttb {
+int attention_tc_mode();
+int attention_tc_launch(ttb_ctx* ctx, int dtype, const void* qkv, int64_t tokens, const int32_t* cu, int64_t B, int64_t max_seqlen,
+                        int64_t heads, int causal, float scale, void* out);
+}  // namespace ttb
+
+extern "C" int ttb_attention_fwd(ttb_ctx* ctx, int dtype, const void* qkv, int64_t total_tokens, const int32_t* cu_seqlens,
+                                 int64_t B, int64_t max_seqlen, int64_t heads, int64_t d, const float* mask,
                                  int64_t mask_batch_stride, int64_t mask_row_stride, int causal, float scale,
                                  void* out) {
   if (!ctx) return TTB_ERR_INVALID;
@@ -301,7 +307,17 @@ extern "C" int ttb_attention_fwd(ttb_ctx* ctx, int dtype, const void* qkv, const
   TTB_REQUIRE(ctx, qkv && cu_seqlens && out, "attention_fwd: null pointer");
   TTB_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(out)) % 16 == 0,
               "attention_fwd: qkv and out must be 16-byte aligned");
+  TTB_REQUIRE(ctx, total_tokens >= 0, "attention_fwd: negative token count");
   DeviceGuard g(ctx->device);
+  // The tensor-memory kernel (128-row tiles, one CTA set-up per tile) wins on long, nearly equal-length batches; ragged
+  // batches of short sequences and causal masks run faster on the 64-row mma.sync kernel below (measured on B200:
+  // b32 s512: 119 vs 137 us; 64 sequences U[8,512]: 141 vs 105 us; b8 s1024 causal: 80 vs 74 us).
+  const bool long_and_dense = !causal && max_seqlen >= 384 && total_tokens * 10 >= B * max_seqlen * 9;
+  const int tc_mode = attention_tc_mode();
+  if (!mask && total_tokens > 0 && (tc_mode == 2 || (tc_mode == 1 && long_and_dense))) {
+    const int s = attention_tc_launch(ctx, dtype, qkv, total_tokens, cu_seqlens, B, max_seqlen, heads, causal, scale, out);
+    if (s != TTB_ERR_UNSUPPORTED) return s;
+  }
   AttnParams p{qkv, out, cu_seqlens, mask, mask_batch_stride, mask_row_stride, (int)heads, causal ? 1 : 0, scale};
   dim3 grid((unsigned)((max_seqlen + QT - 1) / QT), (unsigned)heads, (unsigned)B);
   if (dtype == TTB_F16) attention_fwd_kernel<__half><<<grid, kWarps * 32, 0, ctx->stream>>>(p);

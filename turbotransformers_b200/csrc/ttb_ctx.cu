@@ -116,6 +116,15 @@ extern "C" int ttb_memcpy_d2h(ttb_ctx* c, void* dst, const void* src, size_t byt
   return TTB_OK;
 }
 
+extern "C" int ttb_copy_2d(ttb_ctx* c, void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width, size_t rows) {
+  if (!c) return TTB_ERR_INVALID;
+  if (width == 0 || rows == 0) return TTB_OK;
+  TTB_REQUIRE(c, dst && src && dst_pitch >= width && src_pitch >= width, "copy_2d: bad arguments");
+  DeviceGuard g(c->device);
+  TTB_CUDA(c, cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width, rows, cudaMemcpyDeviceToDevice, c->stream));
+  return TTB_OK;
+}
+
 // ---------------------------------------------------------------------------------------------
 // pool
 // ---------------------------------------------------------------------------------------------

@@ -734,7 +734,10 @@ int launch_tc(ttb_ctx* ctx, const void* A, int64_t lda, const void* W, const Gem
   CUtensorMap tmO = tmA;  // placeholder when the direct-store epilogue is used
   const bool aligned16 = ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.bias) |
                            reinterpret_cast<uintptr_t>(p.residual)) & 15) == 0;
-  q.tma_store = (BN >= 64 && aligned16 && p.ldo % 8 == 0 && p.N % 8 == 0 && (!p.residual || p.ldr % 8 == 0)) ? 1 : 0;
+  // The staged epilogue reads bias and residual eight columns at a time, so a ragged N is only allowed with neither;
+  // the TMA store itself clips the columns past N.
+  q.tma_store = (BN >= 64 && aligned16 && p.ldo % 8 == 0 && (p.N % 8 == 0 || p.epilogue == TTB_EPI_NONE) &&
+                 (!p.residual || p.ldr % 8 == 0)) ? 1 : 0;
   if (q.tma_store) {
     const int out_kind = std::is_same<OutT, __nv_bfloat16>::value ? KIND_BF16 : KIND_F16;
     s = make_map(ctx, &tmO, out_kind, p.out, p.M, p.N, p.ldo, 32);

@@ -82,7 +82,7 @@ def main():
         qkv = torch.randn(T, 3 * H, device="cuda", dtype=tdt)
         cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device="cuda")
         o = torch.empty(T, H, device="cuda", dtype=tdt)
-        fn = lambda: ctx.call("attention_fwd", code, qkv, cu, len(lens), max(lens), a.heads, 64, None, 0, 0, int(a.causal), 0.125, o)
+        fn = lambda: ctx.call("attention_fwd", code, qkv, T, cu, len(lens), max(lens), a.heads, 64, None, 0, 0, int(a.causal), 0.125, o)
         mean, med, best = timed(fn, a.warmup, a.iters, not a.no_flush)
         fl = sum((2.0 * H * L * (L + 1)) if a.causal else (4.0 * H * L * L) for L in lens)
         out.update(sequences=len(lens), tokens=T, heads=a.heads, dtype=a.dtype, causal=a.causal, us=round(mean * 1e3, 2),

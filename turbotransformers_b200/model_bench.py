@@ -1,0 +1,92 @@
+"""Whole-model timing of the benchmark configurations other than the headline one (which bench.py measures).
+
+    python -m turbotransformers_b200.model_bench --config c1     # BERT-base fp32 b1 s128
+    python -m turbotransformers_b200.model_bench --config sweep  # BERT-base fp16, batch {1,8,32} x seq {32,128,512}
+    python -m turbotransformers_b200.model_bench --config c3     # BERT-base int8, batch {1,16,64}, seq 128
+    python -m turbotransformers_b200.model_bench --config c4     # BERT-large fp16, 32 sequences of 512 (one GPU's shard of 256)
+    python -m turbotransformers_b200.model_bench --config c5     # GPT-2 small fp16, b8 s1024, logits
+
+One JSON line per point: sequences/s, ms per forward (mean and p50 over CUDA-event-timed iterations, inputs resident on
+the device), and the algorithmic TFLOP/s (padding never counts; causal attention counts the lower triangle only).
+Weights are seeded synthetic (synthetic.py); ids are uniform.
+"""
+import argparse
+import json
+
+import torch
+
+import turbotransformers_b200 as tt
+from turbotransformers_b200 import synthetic
+
+
+def enc_flops(layers, H, L, causal=False):
+    att = 2.0 * H * L * (L + 1) if causal else 4.0 * H * L * L
+    return layers * (24.0 * H * H * L + att)
+
+
+def timeit(fn, warmup, iters):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    evs = []
+    for _ in range(iters):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        evs.append((s, e))
+    torch.cuda.synchronize()
+    t = sorted(s.elapsed_time(e) for s, e in evs)
+    return sum(t) / len(t), t[len(t) // 2]
+
+
+def report(name, batch, seq, flops_per_seq, mean_ms, p50_ms, **extra):
+    print(json.dumps({"config": name, "batch": batch, "seq_len": seq, "ms_mean": round(mean_ms, 4), "ms_p50": round(p50_ms, 4),
+                      "sequences_per_s": round(batch / (mean_ms / 1e3), 1),
+                      "tflops": round(batch * flops_per_seq / (mean_ms / 1e3) / 1e12, 1), **extra}), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", required=True, choices=["c1", "sweep", "c3", "c4", "c5"])
+    ap.add_argument("--iters", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    a = ap.parse_args()
+    torch.set_grad_enabled(False)
+    dev = torch.device("cuda:0")
+    if a.config in ("c1", "sweep", "c3"):
+        hf = synthetic.make_hf_bert("bert-base", 0)
+        V = hf.config.vocab_size
+        if a.config == "c1":
+            model = tt.BertModel.from_torch(hf.to(dev), dev)
+            points, name = [(1, 128)], "bert-base fp32"
+        elif a.config == "sweep":
+            model = tt.BertModel.from_torch(hf.to(dev).half(), dev)
+            points, name = [(b, s) for b in (1, 8, 32) for s in (32, 128, 512)], "bert-base fp16"
+        else:
+            model = tt.QBertModel.from_torch(hf.to(dev).half(), dev)
+            points, name = [(1, 128), (16, 128), (64, 128)], "bert-base int8 (all six Linears)"
+        for b, s in points:
+            ids = synthetic.random_ids(b, s, V, 0).to(dev)
+            mean, p50 = timeit(lambda: model(ids), a.warmup, a.iters)
+            report(name, b, s, enc_flops(12, 768, s), mean, p50)
+    elif a.config == "c4":
+        hf = synthetic.make_hf_bert("bert-large", 0)
+        model = tt.BertModel.from_torch(hf.to(dev).half(), dev)
+        ids = synthetic.random_ids(32, 512, hf.config.vocab_size, 0).to(dev)
+        mean, p50 = timeit(lambda: model(ids), a.warmup, a.iters)
+        report("bert-large fp16 (32 of the 256 sequences: one GPU's shard at 8 GPUs)", 32, 512, enc_flops(24, 1024, 512), mean, p50)
+    else:
+        hf = synthetic.make_hf_gpt2("gpt2-small", 0)
+        model = tt.GPT2Model.from_torch(hf.to(dev).half(), dev)
+        ids = synthetic.random_ids(8, 1024, hf.config.vocab_size, 0).to(dev)
+        mean, p50 = timeit(lambda: model(ids), a.warmup, a.iters)
+        fl = enc_flops(12, 768, 1024, causal=True) + 2.0 * 1024 * 768 * hf.config.vocab_size
+        report("gpt2-small fp16, full-sequence forward with tied-embedding logits", 8, 1024, fl, mean, p50)
+        mean, p50 = timeit(lambda: model(ids, return_logits=False), a.warmup, a.iters)
+        report("gpt2-small fp16, hidden states only", 8, 1024, enc_flops(12, 768, 1024, causal=True), mean, p50)
+    assert tt._cxx_module.device_status(0) == 0
+
+
+if __name__ == "__main__":
+    main()
