@@ -43,6 +43,10 @@ typedef enum {
   TTB_EPI_BIAS_RESIDUAL = 3, /* out = acc + bias + residual                 (MatMul + AddInputBias)       */
   TTB_EPI_BIAS_TANH = 4      /* out = tanh(acc + bias)                      (MatMul + AddBiasAct<Tanh>)   */
 } ttb_epilogue;
+/* May be OR-ed into ttb_linear's `epilogue` when N is not a multiple of 8 and ldo is: declares columns
+ * [N, round_up(N, 8)) of every output row scratch (the fast store path overwrites them with zeros). Without it
+ * such an output takes a slower element-wise store that leaves those columns untouched. */
+#define TTB_EPI_FLAG_ROW_PADDING_IS_SCRATCH 0x100
 
 /* ---- context: replaces core::CUDADeviceContext (turbo_transformers/core/cuda_device_context.cpp:23-60),
  * one per device (and per host thread, if callers want concurrency) instead of one global singleton. ---- */

@@ -102,11 +102,15 @@ def test_linear_ragged_width_into_padded_rows_then_compacted(ctx, M, N, K):
     Wp = prepack(ctx, w, dt)
     Np = (N + 7) // 8 * 8
     padded = torch.full((M, Np), 7.0, dtype=torch.float16, device="cuda")
-    ctx.call("linear", code(dt), dev(a, dt), K, Wp, None, None, 0, M, N, K, EPIS["none"], padded, Np)
-    assert ctx.device_status() == _capi.OK
     want = restate.mat_mul(a, False, w, False)
+    tol = 2.0 ** -10 * max(1.0, float(np.abs(want).max())) + 2e-3
+    ctx.call("linear", code(dt), dev(a, dt), K, Wp, None, None, 0, M, N, K, EPIS["none"], padded, Np)
     got = host(padded)
-    assert maxdiff(got[:, N:], 7.0) == 0.0  # the padding columns are not written
+    assert maxdiff(got[:, N:], 7.0) == 0.0  # without the flag the padding columns are not written
+    assert maxdiff(got[:, :N], want) < tol
+    ctx.call("linear", code(dt), dev(a, dt), K, Wp, None, None, 0, M, N, K, EPIS["none"] | 0x100, padded, Np)  # padding declared scratch
+    assert ctx.device_status() == _capi.OK
+    got = host(padded)
     assert maxdiff(got[:, :N], want) < 2.0 ** -10 * max(1.0, float(np.abs(want).max())) + 2e-3
     out = torch.empty((M, N), dtype=torch.float16, device="cuda")
     ctx.call("copy_2d", out, N * 2, padded, Np * 2, N * 2, M)

@@ -113,6 +113,7 @@ void PackedLinear::Forward(const Tensor& x, int64_t M, int epilogue, const void*
     Check(ttb_linear_int8(c, dt, xq.data<int8_t>(), xs.data<float>(), wq, ws, bias, residual, N, M, N, K, epilogue, out, N), c, name);
     return;
   }
+  if (ldo != N) epilogue |= TTB_EPI_FLAG_ROW_PADDING_IS_SCRATCH;  // only Linear's own row-padded scratch gets here
   Check(ttb_linear(c, dt, x.raw(), K, Packed(is_trans), bias, residual, N, M, N, K, epilogue, out, ldo), c, name);
 }
 

@@ -734,9 +734,10 @@ int launch_tc(ttb_ctx* ctx, const void* A, int64_t lda, const void* W, const Gem
   CUtensorMap tmO = tmA;  // placeholder when the direct-store epilogue is used
   const bool aligned16 = ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.bias) |
                            reinterpret_cast<uintptr_t>(p.residual)) & 15) == 0;
-  // The staged epilogue reads bias and residual eight columns at a time, so a ragged N is only allowed with neither;
-  // the TMA store itself clips the columns past N.
-  q.tma_store = (BN >= 64 && aligned16 && p.ldo % 8 == 0 && (p.N % 8 == 0 || p.epilogue == TTB_EPI_NONE) &&
+  // The staged epilogue reads bias and residual eight columns at a time, and a TMA store clips a row at 16-byte
+  // granularity: with a ragged N it writes zeros into the columns up to the next multiple of 8. So a ragged N takes
+  // this route only without bias/residual and when the caller declared those columns scratch (p.tma_store on entry).
+  q.tma_store = (BN >= 64 && aligned16 && p.ldo % 8 == 0 && (p.N % 8 == 0 || (p.epilogue == TTB_EPI_NONE && p.tma_store)) &&
                  (!p.residual || p.ldr % 8 == 0)) ? 1 : 0;
   if (q.tma_store) {
     const int out_kind = std::is_same<OutT, __nv_bfloat16>::value ? KIND_BF16 : KIND_F16;
@@ -891,11 +892,13 @@ extern "C" int ttb_linear(ttb_ctx* ctx, int dtype, const void* A, int64_t lda, c
                           int64_t ldo) {
   if (!ctx) return TTB_ERR_INVALID;
   TTB_REQUIRE(ctx, dtype == TTB_F16 || dtype == TTB_BF16, "linear: dtype must be F16 or BF16 (use ttb_matmul for F32)");
+  const int pad_scratch = (epilogue & TTB_EPI_FLAG_ROW_PADDING_IS_SCRATCH) ? 1 : 0;
+  epilogue &= ~TTB_EPI_FLAG_ROW_PADDING_IS_SCRATCH;
   int s = check_linear(ctx, "linear", A, Wp, bias, residual, M, N, K, epilogue, out, ldo, 8);
   if (s || M == 0) return s;
   TTB_REQUIRE(ctx, lda >= K && lda % 8 == 0, "linear: lda must be >= K and a multiple of 8");
   DeviceGuard g(ctx->device);
-  GemmParams p{(int)M, (int)N, (int)K, out, ldo, bias, residual, ldr, nullptr, nullptr, epilogue, 0, ctx->d_status};
+  GemmParams p{(int)M, (int)N, (int)K, out, ldo, bias, residual, ldr, nullptr, nullptr, epilogue, pad_scratch, ctx->d_status};
   if (dtype == TTB_F16) return pick_tile<KIND_F16, __half>(ctx, A, lda, Wp, p);
   return pick_tile<KIND_BF16, __nv_bfloat16>(ctx, A, lda, Wp, p);
 }

@@ -53,6 +53,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--pad-rows", action="store_true", help="linear: output rows padded to a multiple of 8 elements, padding declared scratch")
     a = ap.parse_args()
     ctx = _capi.Context(0)
     out = {"op": a.op}
@@ -70,7 +71,13 @@ def main():
         else:
             x = torch.randn(M, K, device="cuda", dtype=odt)
             w = torch.randn(N, K, device="cuda", dtype=odt) * 0.03
-            fn = lambda: ctx.call("linear", ocode, x, K, w, b, r, N, M, N, K, EPI[a.epilogue], o, N)
+            ldo, flag = ((N + 7) // 8 * 8, 0x100) if a.pad_rows else (N, 0)
+            o = torch.empty(M, ldo, device="cuda", dtype=odt)
+            if a.epilogue == "none":
+                b = None
+            if a.epilogue != "bias_residual":
+                r = None
+            fn = lambda: ctx.call("linear", ocode, x, K, w, b, r, N if r is not None else 0, M, N, K, EPI[a.epilogue] | flag, o, ldo)
         mean, med, best = timed(fn, a.warmup, a.iters, not a.no_flush)
         out.update(shape=[M, N, K], dtype=a.dtype, epilogue=a.epilogue, us=round(mean * 1e3, 2), us_median=round(med * 1e3, 2),
                    tflops=round(2.0 * M * N * K / mean / 1e9, 1))
