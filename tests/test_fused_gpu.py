@@ -285,3 +285,33 @@ def test_attention_permutation_property_at_benchmark_size(ctx):
     # rows of a softmax-weighted average stay inside the value range of their sequence
     v = qkv[:, 2 * H:].float()
     assert out.float().abs().max() <= v.abs().max() + 1e-3
+
+
+def test_attention_kernels_agree_on_repeated_launches_at_benchmark_size(ctx, monkeypatch):
+    # The tensor-memory kernel hands buffers between its warps through barriers; a missing one shows up as an
+    # intermittent mismatch at full size, not on small cases. 25 launches against the mma.sync kernel's output.
+    from turbotransformers_b200 import synthetic
+    lens = synthetic.varlen_lengths(64, 8, 512, 0)
+    heads, H, T = 12, 768, sum(lens)
+    qkv = torch.randn(T, 3 * H, device="cuda", dtype=torch.float16)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device="cuda")
+    out = torch.empty(T, H, device="cuda", dtype=torch.float16)
+
+    def run():
+        ctx.call("attention_fwd", _capi.F16, qkv, T, cu, len(lens), max(lens), heads, 64, None, 0, 0, 0, 0.125, out)
+        torch.cuda.synchronize()
+        assert ctx.device_status() == _capi.OK
+
+    monkeypatch.setenv("TTB_ATTN_TC", "0")
+    run()
+    ref = out.clone()
+    monkeypatch.setenv("TTB_ATTN_TC", "2")
+    first = None
+    for _ in range(25):
+        out.zero_()
+        run()
+        assert (out.float() - ref.float()).abs().max().item() < 4e-3
+        if first is None:
+            first = out.clone()
+        assert torch.equal(out, first)  # and bit-identical from launch to launch
+

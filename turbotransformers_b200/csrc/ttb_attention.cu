@@ -102,6 +102,8 @@ attention_fwd_kernel(const AttnParams p) {
   __shared__ __align__(128) uint8_t sK[2][KT * 128];
   __shared__ __align__(128) uint8_t sV[2][KT * 128];
 
+  pdl_trigger();
+  pdl_wait();  // before the first global read and before any CTA can leave
   const int b = blockIdx.z, h = blockIdx.y;
   const int tok0 = p.cu[b];
   const int len = p.cu[b + 1] - tok0;
@@ -309,18 +311,18 @@ extern "C" int ttb_attention_fwd(ttb_ctx* ctx, int dtype, const void* qkv, int64
               "attention_fwd: qkv and out must be 16-byte aligned");
   TTB_REQUIRE(ctx, total_tokens >= 0, "attention_fwd: negative token count");
   DeviceGuard g(ctx->device);
-  // The tensor-memory kernel (128-row tiles, one CTA set-up per tile) wins on long, nearly equal-length batches; ragged
-  // batches of short sequences and causal masks run faster on the 64-row mma.sync kernel below (measured on B200:
-  // b32 s512: 119 vs 137 us; 64 sequences U[8,512]: 141 vs 105 us; b8 s1024 causal: 80 vs 74 us).
-  const bool long_and_dense = !causal && max_seqlen >= 384 && total_tokens * 10 >= B * max_seqlen * 9;
+  // The persistent tensor-memory kernel wins once there is enough work to fill its pipeline (measured on B200, whole
+  // BERT-base step of 64 sequences U[8,512]: 4.52 ms against 4.75 ms with the mma.sync kernel below); a handful of short
+  // sequences finish sooner on the many small CTAs of the mma.sync kernel, which also serves every call with a mask tensor.
+  const bool enough_work = total_tokens >= 4096;
   const int tc_mode = attention_tc_mode();
-  if (!mask && total_tokens > 0 && (tc_mode == 2 || (tc_mode == 1 && long_and_dense))) {
+  if (!mask && total_tokens > 0 && (tc_mode == 2 || (tc_mode == 1 && enough_work))) {
     const int s = attention_tc_launch(ctx, dtype, qkv, total_tokens, cu_seqlens, B, max_seqlen, heads, causal, scale, out);
     if (s != TTB_ERR_UNSUPPORTED) return s;
   }
   AttnParams p{qkv, out, cu_seqlens, mask, mask_batch_stride, mask_row_stride, (int)heads, causal ? 1 : 0, scale};
   dim3 grid((unsigned)((max_seqlen + QT - 1) / QT), (unsigned)heads, (unsigned)B);
-  if (dtype == TTB_F16) attention_fwd_kernel<__half><<<grid, kWarps * 32, 0, ctx->stream>>>(p);
-  else attention_fwd_kernel<__nv_bfloat16><<<grid, kWarps * 32, 0, ctx->stream>>>(p);
+  if (dtype == TTB_F16) launch_pdl(attention_fwd_kernel<__half>, grid, dim3(kWarps * 32), 0, ctx->stream, p);
+  else launch_pdl(attention_fwd_kernel<__nv_bfloat16>, grid, dim3(kWarps * 32), 0, ctx->stream, p);
   return launched(ctx, "attention_fwd");
 }

@@ -1,16 +1,27 @@
 // Self-attention over packed variable-length batches on the 5th-generation tensor cores.
 //
-// One CTA = 128 query rows of one (sequence, head). Keys/values stream in 128-row tiles.
-//   warp 0     : TMA loader   - Q once, then K_j and V_j tiles (128-byte-swizzled, straight out of the [T, 3H] QKV
-//                matrix: a tile is a [128 rows x 64 columns] box at column offset part*H + head*64) into a 2-slot ring
-//   warp 1     : MMA issuer   - S = Q K_j^T (128x128x64, accumulator in TMEM), then O_j = P_j V_j (128x64x128) with
-//                P_j read from shared memory and V_j used in place as an MN-major operand (no transpose anywhere)
-//   warps 2..5 : softmax      - one query row per thread: tcgen05.ld the scores, running max / sum in fp32, exp2 with the
-//                scale folded in, P_j written to shared memory as the next MMA's K-major A operand. O accumulates in
-//                TMEM across tiles and is rescaled there only when the running maximum has grown by more than 2^8
-// TMEM: S (128 columns) + O (64 columns) inside a 256-column allocation, so two CTAs fit on an SM and one CTA's
-// softmax overlaps the other's MMAs. Every wait is bounded; on expiry the CTA raises a flag, frees its TMEM and the host
-// sees TTB_ERR_DEVICE_WAIT.
+// Persistent kernel, one CTA per SM. A work item is a pair of 128-row query tiles ("slots" 0 and 1) of one
+// (sequence, head); keys/values stream in 128-row tiles shared by both slots.
+//   warp 0      : TMA loader  - Q tiles (double-buffered per slot), then K_j / V_j tiles into a 3-stage ring. Every tile is
+//                 a [128 rows x 64 columns] 128-byte-swizzled box straight out of the [T, 3H] QKV matrix.
+//   warp 1      : MMA issuer  - S_s = Q_s K_j^T (128x128x64, fp32 in TMEM) and O_s += P_s V_j (128x64x128) with P_s read
+//                 from TMEM and V_j used in place as an MN-major operand. Issue order
+//                 QK(0,0) QK(1,0) | QK(0,j+1) PV(1,j-1) QK(1,j+1) PV(0,j) | ...
+//                 QK(s,j+1) goes out as soon as the softmax warps hold the scores of tile j in registers, so the next
+//                 scores are in TMEM before the current tile's softmax ends; the two slots run half a period apart.
+//                 A wait in the issuing thread only returns once the MMAs it has already issued have drained, so this
+//                 thread waits on one barrier per MMA group: the softmax warps vouch for the K/V tiles a group reads.
+//   warps 4..7  : softmax of slot 0, warps 8..11: softmax of slot 1 (warps 2, 3 idle; registers are moved from the first
+//                 warpgroup to the softmax ones with setmaxnreg) - one query row per thread: scores from TMEM, running
+//                 max / sum in fp32, exp2 with the scale folded in, P written back to TMEM as packed 16-bit pairs.
+//                 O accumulates in TMEM across key tiles. The row maximum is taken on a row's first tile only; later
+//                 tiles reuse it and fall back to a rescale of O only if a probability would leave the 16-bit range
+//                 (row sum above 2^15), which real score distributions do not reach. The final division by the running
+//                 sum makes the result independent of the reference maximum.
+// TMEM (all 512 columns): S0 | S1 (128 each) | O0 | O1 (64 each) | P0 | P1 (64 each).
+// Work items are ordered longest sequence first and dealt round-robin to the CTAs, so the CTAs finish together.
+// Every wait is bounded; on expiry the CTA raises a flag, frees its TMEM and the host sees TTB_ERR_DEVICE_WAIT.
+#include <algorithm>
 #include <cstdlib>
 #include <type_traits>
 
@@ -23,20 +34,35 @@ using namespace ttb::sm100;
 namespace {
 
 constexpr int QT = 128, KT = 128, D = 64;
-constexpr int kThreads = 192;
-constexpr int TILE_BYTES = 128 * 128;          // a [128 rows x 128 B] tile
-constexpr int SMEM_Q = 0, SMEM_K = TILE_BYTES, SMEM_V = 3 * TILE_BYTES, SMEM_P = 5 * TILE_BYTES;  // K,V: 2 slots; P: 2 atoms
-constexpr int SMEM_BARS = 7 * TILE_BYTES;
-constexpr int SMEM_BYTES = 7 * TILE_BYTES + 128;  // two CTAs per SM: 2 x (112.1 KB + 1 KB reserved) <= 228 KB
-constexpr uint32_t TMEM_COLS = 256;
+constexpr int kStages = 3;
+constexpr int kMaxB = 512;       // sequences per launch that the in-kernel schedule tables hold
+constexpr int kSortMaxB = 256;   // above this the (quadratic) length ranking is skipped and sequences keep their order
+constexpr int kThreads = 384;    // three warpgroups: {loader, MMA, two idle warps}, softmax slot 0, softmax slot 1
+constexpr int TILE_BYTES = 128 * 128;  // a [128 rows x 128 B] tile
+constexpr int SMEM_Q = 0;                                  // [slot][buffer]: 4 tiles
+constexpr int SMEM_K = 4 * TILE_BYTES;                     // kStages tiles
+constexpr int SMEM_V = (4 + kStages) * TILE_BYTES;         // kStages tiles
+constexpr int SMEM_CU = (4 + 2 * kStages) * TILE_BYTES;    // int[kMaxB + 1] token offsets
+constexpr int SMEM_PREFIX = SMEM_CU + (kMaxB + 1) * 4;     // int[kMaxB + 1] items before each ranked sequence
+constexpr int SMEM_ORDER = SMEM_PREFIX + (kMaxB + 1) * 4;  // uint16[kMaxB] sequence at each rank
+constexpr int SMEM_BARS = (SMEM_ORDER + kMaxB * 2 + 63) / 64 * 64;
+constexpr int kNumBars = 8 + 4 * kStages + 8;
+constexpr int SMEM_BYTES = SMEM_BARS + kNumBars * 8 + 64;
+constexpr uint32_t TMEM_COLS = 512;
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRowSumLimit = 32768.0f;  // a tile row sum below this keeps every probability inside fp16 / bf16 range
 
 struct Params {
   void* out;
   const int32_t* cu;
-  int heads, causal;
+  int batch, heads, causal;
   float scale;
   int* status;
+};
+
+struct Item {
+  int tok0, len, q0, head;
+  int n0, n1;  // key tiles slot 0 / slot 1 visit (0 = slot idle)
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -55,210 +81,358 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, f
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <typename T>
-__global__ void __launch_bounds__(kThreads, 2)
-attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
-  const int b = blockIdx.z, h = blockIdx.y;
-  const int tok0 = p.cu[b];
-  const int len = p.cu[b + 1] - tok0;
-  const int q0 = blockIdx.x * QT;
-  if (q0 >= len) return;  // whole CTA, before any barrier or TMEM use
+// Item `i` of the launch: rank-ordered (sequence, 256-row pair) x head.
+__device__ __forceinline__ Item decode_item(int i, const Params& p, const int* s_cu, const int* s_prefix, const uint16_t* s_order) {
+  Item it;
+  it.head = i % p.heads;
+  const int pidx = i / p.heads;
+  int lo = 0, hi = p.batch;  // largest r with s_prefix[r] <= pidx
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (s_prefix[mid] <= pidx) lo = mid;
+    else hi = mid;
+  }
+  const int seq = s_order[lo];
+  it.tok0 = s_cu[seq];
+  it.len = s_cu[seq + 1] - it.tok0;
+  it.q0 = (pidx - s_prefix[lo]) * (2 * QT);
+  const int n_all = (it.len + KT - 1) / KT;
+  const bool act1 = it.q0 + QT < it.len;
+  if (p.causal) {
+    it.n0 = min(n_all, it.q0 / KT + 1);
+    it.n1 = act1 ? min(n_all, it.q0 / KT + 2) : 0;
+  } else {
+    it.n0 = n_all;
+    it.n1 = act1 ? n_all : 0;
+  }
+  return it;
+}
 
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
   constexpr int FMT = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
-  constexpr uint32_t IDESC_S = idesc_f16(FMT, 128, KT, 0);   // Q (K-major) x K^T (K-major)
-  constexpr uint32_t IDESC_O = idesc_f16(FMT, 128, D, 1);    // P (K-major) x V (MN-major)
+  constexpr uint32_t IDESC_S = idesc_f16(FMT, 128, KT, 0);  // Q (K-major) x K^T (K-major)
+  constexpr uint32_t IDESC_O = idesc_f16(FMT, 128, D, 1);   // P (TMEM) x V (MN-major)
 
   extern __shared__ __align__(1024) uint8_t smem[];  // the swizzled tiles need 1024-byte alignment
   const uint32_t base = smem_u32(smem);
   if (base & 1023u) {  // cannot happen with the alignment above; refuse rather than compute garbage
+    pdl_wait();
     if (threadIdx.x == 0) atomicExch(p.status, (int)TTB_ERR_DEVICE_WAIT);
     return;
   }
+  int* s_cu = reinterpret_cast<int*>(smem + SMEM_CU);
+  int* s_prefix = reinterpret_cast<int*>(smem + SMEM_PREFIX);
+  uint16_t* s_order = reinterpret_cast<uint16_t*>(smem + SMEM_ORDER);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_BARS);
   const uint32_t bar0 = smem_u32(bars);
-  const uint32_t q_full = bar0, s_full = bar0 + 8, s_empty = bar0 + 16, p_full = bar0 + 24;
-  auto kv_full = [&](int s) { return bar0 + 32 + 8u * s; };
-  auto kv_empty = [&](int s) { return bar0 + 48 + 8u * s; };
-  auto o_full = [&](int s) { return bar0 + 64 + 8u * s; };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  auto q_full = [&](int s, int b) { return bar0 + 8u * (s * 2 + b); };
+  auto q_empty = [&](int s, int b) { return bar0 + 8u * (4 + s * 2 + b); };
+  auto k_full = [&](int st) { return bar0 + 8u * (8 + st); };
+  auto k_empty = [&](int st) { return bar0 + 8u * (8 + kStages + st); };
+  auto v_full = [&](int st) { return bar0 + 8u * (8 + 2 * kStages + st); };
+  auto v_empty = [&](int st) { return bar0 + 8u * (8 + 3 * kStages + st); };
+  auto s_full = [&](int s) { return bar0 + 8u * (8 + 4 * kStages + s); };
+  auto p_ready = [&](int s) { return bar0 + 8u * (10 + 4 * kStages + s); };
+  auto o_done = [&](int s) { return bar0 + 8u * (12 + 4 * kStages + s); };
+  auto s_free = [&](int s) { return bar0 + 8u * (14 + 4 * kStages + s); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int H = p.heads * D;
-  int kv_end = len;
-  if (p.causal && q0 + QT < kv_end) kv_end = q0 + QT;
-  const int n_tiles = (kv_end + KT - 1) / KT;
 
+  pdl_trigger();
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    mbar_init(s_full, 1);
-    mbar_init(s_empty, 4);
-    mbar_init(p_full, 4);
+    for (int i = 0; i < 8 + 4 * kStages; ++i) mbar_init(bar0 + 8u * i, 1);  // q and k/v full/empty
     for (int s = 0; s < 2; ++s) {
-      mbar_init(kv_full(s), 1);
-      mbar_init(kv_empty(s), 1);
-      mbar_init(o_full(s), 1);
+      mbar_init(s_full(s), 1);
+      mbar_init(p_ready(s), 4);  // one arrival per softmax warp
+      mbar_init(o_done(s), 1);
+      mbar_init(s_free(s), 4);   // one arrival per softmax warp
     }
     *abort_flag = 0;
     mbar_init_fence();
   }
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+  pdl_wait();  // everything above ran in the shadow of the previous kernel; global memory is touched from here on
+  // ---- schedule tables (every CTA builds the same ones) -----------------------------------------------------------
+  for (int i = threadIdx.x; i <= p.batch; i += kThreads) s_cu[i] = p.cu[i];
+  __syncthreads();
+  // rank sequences by descending key-tile count (ties by index): the rank is the position in the item order
+  for (int i = threadIdx.x; i < p.batch; i += kThreads) {
+    int rank = i;
+    if (p.batch <= kSortMaxB) {
+      const int mine = (s_cu[i + 1] - s_cu[i] + KT - 1) / KT;
+      rank = 0;
+      for (int j = 0; j < p.batch; ++j) {
+        const int other = (s_cu[j + 1] - s_cu[j] + KT - 1) / KT;
+        rank += (other > mine || (other == mine && j < i)) ? 1 : 0;
+      }
+    }
+    s_order[rank] = (uint16_t)i;
+  }
+  __syncthreads();
+  if (warp == 0) {  // exclusive scan of the pair counts in rank order
+    int carry = 0;
+    for (int r0 = 0; r0 < p.batch; r0 += 32) {
+      const int r = r0 + lane;
+      int pairs = 0;
+      if (r < p.batch) {
+        const int seq = s_order[r];
+        pairs = (s_cu[seq + 1] - s_cu[seq] + 2 * QT - 1) / (2 * QT);
+      }
+      int incl = pairs;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      if (r < p.batch) s_prefix[r] = carry + incl - pairs;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) s_prefix[p.batch] = carry;
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tmem_s = tmem, tmem_o0 = tmem + 128;
+  const int n_items = s_prefix[p.batch] * p.heads;
+  auto tmem_s = [&](int s) { return tmem + (uint32_t)(s * 128); };
+  auto tmem_o = [&](int s) { return tmem + (uint32_t)(256 + s * 64); };
+  auto tmem_p = [&](int s) { return tmem + (uint32_t)(384 + s * 64); };
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ loader
-    if (lane == 0) {
-      mbar_expect_tx(q_full, TILE_BYTES);
-      tma_load_2d(base + SMEM_Q, &tm, q_full, h * D, tok0 + q0);
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(kv_empty(s), (((uint32_t)j >> 1) & 1u) ^ 1u, abort_flag)) break;
-        mbar_expect_tx(kv_full(s), 2 * TILE_BYTES);
-        tma_load_2d(base + SMEM_K + s * TILE_BYTES, &tm, kv_full(s), H + h * D, tok0 + j * KT);
-        tma_load_2d(base + SMEM_V + s * TILE_BYTES, &tm, kv_full(s), 2 * H + h * D, tok0 + j * KT);
-      }
-      if (*abort_flag) {  // let copies in flight land before shared memory is released
-        const long long t0 = clock64();
-        while (clock64() - t0 < 4000000LL) {
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+    if (warp == 0) {
+      // ------------------------------------------------------------------ loader
+      if (lane == 0) {
+        uint32_t kvc = 0, nq0 = 0, nq1 = 0;
+        bool ok = true;
+        for (int i = blockIdx.x; i < n_items && ok; i += gridDim.x) {
+          const Item it = decode_item(i, p, s_cu, s_prefix, s_order);
+          auto load_q = [&](int s, uint32_t& nq) {
+            const int b = nq & 1;
+            if (!mbar_wait(q_empty(s, b), ((nq >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; return; }
+            mbar_expect_tx(q_full(s, b), TILE_BYTES);
+            tma_load_2d(base + SMEM_Q + (s * 2 + b) * TILE_BYTES, &tm, q_full(s, b), it.head * D, it.tok0 + it.q0 + s * QT);
+            ++nq;
+          };
+          if (it.n0 > 0) load_q(0, nq0);
+          if (ok && it.n1 > 0) load_q(1, nq1);
+          const int nmax = max(it.n0, it.n1);
+          for (int j = 0; j < nmax && ok; ++j, ++kvc) {
+            const int st = kvc % kStages;
+            const uint32_t par = ((kvc / kStages) & 1u) ^ 1u;
+            if (!mbar_wait(k_empty(st), par, abort_flag)) { ok = false; break; }
+            mbar_expect_tx(k_full(st), TILE_BYTES);
+            tma_load_2d(base + SMEM_K + st * TILE_BYTES, &tm, k_full(st), H + it.head * D, it.tok0 + j * KT);
+            if (!mbar_wait(v_empty(st), par, abort_flag)) { ok = false; break; }
+            mbar_expect_tx(v_full(st), TILE_BYTES);
+            tma_load_2d(base + SMEM_V + st * TILE_BYTES, &tm, v_full(st), 2 * H + it.head * D, it.tok0 + j * KT);
+          }
+        }
+        if (*abort_flag) {  // let copies in flight land before shared memory is released
+          const long long t0 = clock64();
+          while (clock64() - t0 < 4000000LL) {
+          }
         }
       }
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      bool ok = mbar_wait(q_full, 0, abort_flag);
-      const uint32_t q_lo = desc_lo(base + SMEM_Q), p_lo = desc_lo(base + SMEM_P);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j & 1;
-        const uint32_t par2 = ((uint32_t)j >> 1) & 1u;
-        if (!mbar_wait(kv_full(s), par2, abort_flag)) break;
-        if (j > 0 && !mbar_wait(s_empty, (uint32_t)(j - 1) & 1u, abort_flag)) break;  // softmax has read S_{j-1}
-        tc_fence_after();
-        const uint32_t k_lo = desc_lo(base + SMEM_K + s * TILE_BYTES), v_lo = desc_lo(base + SMEM_V + s * TILE_BYTES);
+      __syncwarp();
+    } else if (warp == 1) {
+      // ------------------------------------------------------------------ MMA issuer
+      if (lane == 0) {
+        uint32_t kvc = 0, nq[2] = {0, 0}, tcount[2] = {0, 0};
+        bool ok = true;
+        for (int i = blockIdx.x; i < n_items && ok; i += gridDim.x) {
+          const Item it = decode_item(i, p, s_cu, s_prefix, s_order);
+          const int ns[2] = {it.n0, it.n1};
+          uint32_t q_lo[2] = {0, 0};
+          int qbuf[2] = {0, 0};
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) umma_f16(tmem_s, q_lo + k * 2, k_lo + k * 2, IDESC_S, k != 0);  // 32 bytes of d per step
-        tc_commit(s_full);
-        if (!mbar_wait(p_full, (uint32_t)j & 1u, abort_flag)) break;  // P_j is in shared memory
-        tc_fence_after();
+          for (int s = 0; s < 2; ++s) {
+            if (!ok || ns[s] == 0) continue;
+            qbuf[s] = nq[s] & 1;
+            if (!mbar_wait(q_full(s, qbuf[s]), (nq[s] >> 1) & 1u, abort_flag)) { ok = false; continue; }
+            q_lo[s] = desc_lo(base + SMEM_Q + (s * 2 + qbuf[s]) * TILE_BYTES);
+            ++nq[s];
+          }
+          // K_0 of this item; every later tile is vouched for by the softmax warps before they release P
+          if (ok && !mbar_wait(k_full(kvc % kStages), (kvc / kStages) & 1u, abort_flag)) ok = false;
+          if (!ok) break;
+          // QK(s, j) with j > 0 follows the softmax warps' release of S_s (scores of tile j-1 are in their registers and
+          // K_j has landed); tile t of this item is the slot's (tbase[s] + t)-th since the kernel started
+          const uint32_t tbase[2] = {tcount[0], tcount[1]};
+          auto qk = [&](auto slot_c, int j) {
+            constexpr int s = decltype(slot_c)::value;
+            if (j > 0) {
+              if (!mbar_wait(s_free(s), (tbase[s] + (uint32_t)(j - 1)) & 1u, abort_flag)) { ok = false; return; }
+              tc_fence_after();
+            }
+            const uint32_t c = kvc + (uint32_t)j;
+            const int st = c % kStages;
+            const uint32_t k_lo = desc_lo(base + SMEM_K + st * TILE_BYTES);
 #pragma unroll
-        for (int k = 0; k < KT / 16; ++k) {
-          // 16 keys per step: P advances 32 bytes inside its 64-key atom (atoms are one tile apart),
-          // V advances 16 rows of 128 bytes
-          const uint32_t a = p_lo + (uint32_t)((k >> 2) * (TILE_BYTES >> 4) + (k & 3) * 2);
-          umma_f16(tmem_o0, a, v_lo + (uint32_t)(k * (16 * 128 >> 4)), IDESC_O, (j | k) != 0);  // O accumulates over tiles
+            for (int k = 0; k < D / 16; ++k) umma_f16(tmem_s(s), q_lo[s] + k * 2, k_lo + k * 2, IDESC_S, k != 0);  // 32 bytes of d per step
+            tc_commit(s_full(s));
+            if (s == 1 || j >= ns[1]) tc_commit(k_empty(st));      // last reader of K_j
+            if (j == ns[s] - 1) tc_commit(q_empty(s, qbuf[s]));    // last reader of Q_s
+          };
+          auto pv = [&](auto slot_c, int j) {
+            constexpr int s = decltype(slot_c)::value;
+            const uint32_t c = kvc + (uint32_t)j;
+            const int st = c % kStages;
+            // P_j in TMEM, O rescaled if needed, V_j in shared memory
+            if (!mbar_wait(p_ready(s), tcount[s] & 1u, abort_flag)) { ok = false; return; }
+            tc_fence_after();
+            const uint32_t v_lo = desc_lo(base + SMEM_V + st * TILE_BYTES);
+#pragma unroll
+            for (int k = 0; k < KT / 16; ++k)  // 16 keys per MMA: 8 TMEM columns of P, 16 rows (of 128 bytes) of V
+              umma_f16_ts(tmem_o(s), tmem_p(s) + (uint32_t)(k * 8), v_lo + (uint32_t)(k * (16 * 128 >> 4)), IDESC_O, (j | k) != 0);
+            tc_commit(o_done(s));
+            ++tcount[s];
+            if (s == 1 || j >= ns[1]) tc_commit(v_empty(st));  // last reader of V_j
+          };
+          constexpr std::integral_constant<int, 0> S0{};
+          constexpr std::integral_constant<int, 1> S1{};
+          const int nmax = max(it.n0, it.n1);
+          tc_fence_after();
+          if (it.n0 > 0) qk(S0, 0);
+          if (it.n1 > 0) qk(S1, 0);
+          // the two slots run half a period apart: while one slot's softmax works on tile j, the other slot's events arrive
+          for (int j = 0; j <= nmax && ok; ++j) {
+            if (j + 1 < it.n0) qk(S0, j + 1);
+            if (ok && j > 0 && j <= it.n1) pv(S1, j - 1);
+            if (ok && j + 1 < it.n1) qk(S1, j + 1);
+            if (ok && j < it.n0) pv(S0, j);
+          }
+          kvc += (uint32_t)nmax;
         }
-        tc_commit(o_full(s));    // O_j complete (and P_j consumed)
-        tc_commit(kv_empty(s));  // K_j / V_j consumed
       }
+      __syncwarp();
     }
-    __syncwarp();
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     // ------------------------------------------------------------------ softmax + output (one query row per thread)
-    const int quad = warp & 3;
+    const int slot = (warp - 4) >> 2;
+    const int quad = warp & 3;                  // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may touch
     const int row = quad * 32 + lane;           // row within the tile == TMEM lane
-    const int qrow = q0 + row;                  // row within the sequence
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    const uint32_t ts = tmem_s(slot) + lane_addr, to = tmem_o(slot) + lane_addr, tp = tmem_p(slot) + lane_addr;
     const float sc = p.scale * kLog2e;
-    uint8_t* prow = smem + SMEM_P + row * 128;  // this row inside a P atom (atoms are TILE_BYTES apart)
-    // m_used is the maximum the probabilities are expressed against. It only follows the true running maximum when
-    // that has grown by more than 2^8, so the accumulator in TMEM is rescaled rarely (usually once, on the second tile,
-    // or never); the final division by l_run makes the result independent of which reference maximum was used.
-    float m_used = -INFINITY, l_run = 0.f;
+    uint32_t tcount = 0, kvc = 0;
     bool ok = true;
 
-    for (int j = 0; j < n_tiles; ++j) {
-      const int k0 = j * KT;
-      // s_full_j also means every earlier MMA of this CTA has completed: P_{j-1} is consumed and O holds tiles < j
-      if (!mbar_wait(s_full, (uint32_t)j & 1u, abort_flag)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t sr[4][32];
+    for (int i = blockIdx.x; i < n_items && ok; i += gridDim.x) {
+      const Item it = decode_item(i, p, s_cu, s_prefix, s_order);
+      const int nmax = max(it.n0, it.n1);
+      const int n_tiles = slot ? it.n1 : it.n0;
+      const uint32_t kv0 = kvc;
+      kvc += (uint32_t)nmax;
+      if (n_tiles == 0) continue;
+      const int q0 = it.q0 + slot * QT;
+      const int qrow = q0 + row;  // row within the sequence
+      float m_used = -INFINITY, l_run = 0.f;
+
+      for (int j = 0; j < n_tiles; ++j, ++tcount) {
+        const int k0 = j * KT;
+        if (!__all_sync(0xffffffffu, mbar_wait(s_full(slot), tcount & 1u, abort_flag))) { ok = false; break; }  // warp-uniform
+        tc_fence_after();
+        uint32_t sr[4][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32_issue(tmem_s + lane_addr + (uint32_t)(c * 32), sr[c]);
-      tmem_ld_wait();
-      const bool edge = (k0 + KT > len) || (p.causal && k0 + KT - 1 > q0 + quad * 32);
-      if (edge) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int key = k0 + c * 32 + i;
-            if (key >= len || (p.causal && key > qrow)) sr[c][i] = 0xff800000u;  // -inf
-          }
-      }
-      float mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-#pragma unroll
-        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sr[c][i]));
-      const float m_new = fmaxf(m_used, mx * sc);
-      const bool grow = (m_new - m_used > 8.0f) || (m_used == -INFINITY && m_new != -INFINITY);
-      if (j == 0) {
-        if (grow) m_used = m_new;
-      } else if (__any_sync(0xffffffffu, grow)) {
-        const float corr = grow ? ex2(m_used - m_new) : 1.0f;  // 2^-inf = 0 covers a row that had seen no live key yet
-        if (grow) m_used = m_new;
-        l_run *= corr;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-          tmem_ld32_issue(tmem_o0 + lane_addr + (uint32_t)(c * 32), r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
-          tmem_st32(tmem_o0 + lane_addr + (uint32_t)(c * 32), r);
+        for (int c = 0; c < 4; ++c) tmem_ld32_issue(ts + (uint32_t)(c * 32), sr[c]);
+        const uint32_t kvj = kv0 + (uint32_t)j;
+        if (j + 1 < n_tiles) {  // the next score MMA reads K_{j+1}
+          if (!__all_sync(0xffffffffu, mbar_wait(k_full((kvj + 1) % kStages), ((kvj + 1) / kStages) & 1u, abort_flag))) { ok = false; break; }
         }
+        tmem_ld_wait();
+        tc_fence_before();  // S_j is in registers: the scores of tile j+1 may overwrite it (one phase per tile)
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free(slot));
+        // the MMA released by this tile's P reads V_j
+        if (!__all_sync(0xffffffffu, mbar_wait(v_full(kvj % kStages), (kvj / kStages) & 1u, abort_flag))) { ok = false; break; }
+        if ((k0 + KT > it.len) || (p.causal && k0 + KT - 1 > q0 + quad * 32)) {  // edge tile: keys past the end / above the diagonal
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const int key = k0 + c * 32 + e;
+              if (key >= it.len || (p.causal && key > qrow)) sr[c][e] = 0xff800000u;  // -inf
+            }
+        }
+        // Reference maximum: taken on the first tile; later tiles keep it unless the guard below trips.
+        bool need_max = (j == 0);
+        float rs0, rs1;
+        uint32_t pk[2][32];
+        while (true) {
+          if (need_max) {
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+#pragma unroll
+              for (int c = 0; c < 4; ++c) mx[c] = fmaxf(mx[c], __uint_as_float(sr[c][e]));
+            const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * sc);
+            if (j > 0) {
+              // O holds tiles < j once PV(j-1) has completed; nothing writes it again until this warp releases P_j
+              if (!__all_sync(0xffffffffu, mbar_wait(o_done(slot), (tcount - 1) & 1u, abort_flag))) { ok = false; break; }
+              tc_fence_after();
+              const float corr = ex2(m_used - m_new);  // 2^-inf = 0 covers a row that had seen no live key yet
+              l_run *= corr;
+#pragma unroll
+              for (int c = 0; c < 2; ++c) {
+                uint32_t r[32];
+                tmem_ld32_issue(to + (uint32_t)(c * 32), r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * corr);
+                tmem_st32(to + (uint32_t)(c * 32), r);
+              }
+            }
+            m_used = m_new;
+          }
+          const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
+          rs0 = 0.f;
+          rs1 = 0.f;
+#pragma unroll
+          for (int cc = 0; cc < 2; ++cc) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+              const float a0 = ex2(fmaf(__uint_as_float(sr[cc * 2][e]), sc, -m_sub)), a1 = ex2(fmaf(__uint_as_float(sr[cc * 2][e + 1]), sc, -m_sub));
+              const float b0 = ex2(fmaf(__uint_as_float(sr[cc * 2 + 1][e]), sc, -m_sub)), b1 = ex2(fmaf(__uint_as_float(sr[cc * 2 + 1][e + 1]), sc, -m_sub));
+              rs0 += a0 + a1;
+              rs1 += b0 + b1;
+              pk[cc][e >> 1] = pack2<T>(a0, a1);
+              pk[cc][16 + (e >> 1)] = pack2<T>(b0, b1);
+            }
+          }
+          // every probability is below the row sum: under the limit none of them leaves the 16-bit range
+          if (need_max || !__any_sync(0xffffffffu, !(rs0 + rs1 < kRowSumLimit))) break;
+          need_max = true;  // a score far above the reference: redo this tile against its true maximum
+        }
+        if (!ok) break;
+        l_run += rs0 + rs1;
+        // P_s is read by PV(j-1), which is issued after the scores of this tile: it must have completed before P_j lands
+        if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(o_done(slot), (tcount - 1) & 1u, abort_flag))) { ok = false; break; }
+        tmem_st32(tp, pk[0]);
+        tmem_st32(tp + 32u, pk[1]);
         tmem_st_wait();
+        tc_fence_before();  // S_j read, O rescaled, P_j written
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_ready(slot));
       }
-      const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
-      float rs = 0.f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint8_t* atom = prow + (c >> 1) * TILE_BYTES;  // keys 0..63 -> atom 0, 64..127 -> atom 1
-#pragma unroll
-        for (int g8 = 0; g8 < 4; ++g8) {
-          float e[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            e[i] = ex2(fmaf(__uint_as_float(sr[c][g8 * 8 + i]), sc, -m_sub));
-            rs += e[i];
-          }
-          uint4 q;
-          q.x = pack2<T>(e[0], e[1]);
-          q.y = pack2<T>(e[2], e[3]);
-          q.z = pack2<T>(e[4], e[5]);
-          q.w = pack2<T>(e[6], e[7]);
-          const int chunk = (c & 1) * 4 + g8;
-          *reinterpret_cast<uint4*>(atom + ((chunk ^ (row & 7)) << 4)) = q;
-        }
-      }
-      l_run += rs;
-      tc_fence_before();                                            // S_j read, O rescaled
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P_j visible to the MMA's shared-memory reads
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(s_empty);
-        mbar_arrive(p_full);
-      }
-    }
-    if (ok && n_tiles > 0) {
-      const int last = n_tiles - 1;
-      ok = mbar_wait(o_full(last & 1), ((uint32_t)last >> 1) & 1u, abort_flag);
+      if (!ok) break;
+      // ---- output: O / l, 128 contiguous bytes per row
+      if (!__all_sync(0xffffffffu, mbar_wait(o_done(slot), (tcount - 1) & 1u, abort_flag))) { ok = false; break; }
       tc_fence_after();
-    }
-    if (ok) {
       const float inv = 1.0f / l_run;
-      T* op = static_cast<T*>(p.out) + (long long)(tok0 + qrow) * H + h * D;  // 128 contiguous bytes per row
+      T* op = static_cast<T*>(p.out) + (long long)(it.tok0 + qrow) * H + it.head * D;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
-        tmem_ld32_issue(tmem_o0 + lane_addr + (uint32_t)(c * 32), r);
+        tmem_ld32_issue(to + (uint32_t)(c * 32), r);
         tmem_ld_wait();
-        if (qrow < len) {
+        if (qrow < it.len) {
 #pragma unroll
           for (int g8 = 0; g8 < 4; ++g8) {
             uint4 q;
@@ -270,6 +444,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
           }
         }
       }
+      // The next item's first PV (which overwrites O) waits for this warp's next p_ready arrival, which follows
+      // these loads in program order.
     }
   }
 
@@ -286,8 +462,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
 
 namespace ttb {
 
-// TTB_ATTN_TC: 0 = never use the tensor-memory kernel, 2 = use it whenever it can run (tests use this to cover ragged
-// and causal batches), anything else / unset = let the dispatcher choose by shape. Read on every call.
+// TTB_ATTN_TC: 0 = never use the tensor-memory kernel, 2 = use it whenever it can run, anything else / unset = let the
+// dispatcher choose by shape. Read on every call.
 int attention_tc_mode() {
   const char* e = getenv("TTB_ATTN_TC");
   if (e && e[0] == '0') return 0;
@@ -296,15 +472,20 @@ int attention_tc_mode() {
 }
 
 // Launches the tcgen05 attention kernel. qkv is [tokens, 3*heads*64] in fp16/bf16; no mask tensor (callers with one use
-// the mma.sync kernel). Returns TTB_ERR_UNSUPPORTED when the tensor map cannot be encoded so the caller can fall back.
+// the mma.sync kernel). Returns TTB_ERR_UNSUPPORTED when the batch does not fit the schedule tables or the tensor map
+// cannot be encoded, so the caller can fall back.
 int attention_tc_launch(ttb_ctx* ctx, int dtype, const void* qkv, int64_t tokens, const int32_t* cu, int64_t B, int64_t max_seqlen,
                         int64_t heads, int causal, float scale, void* out) {
+  if (B > kMaxB || B < 1 || heads < 1) return TTB_ERR_UNSUPPORTED;
   const int64_t H = heads * D;
   CUtensorMap tm;
   if (!encode_tile_map(&tm, qkv, 2, dtype == TTB_BF16, (uint64_t)tokens, (uint64_t)(3 * H), (uint64_t)(3 * H), 128))
     return TTB_ERR_UNSUPPORTED;
-  Params p{out, cu, (int)heads, causal ? 1 : 0, scale, ctx->d_status};
-  dim3 grid((unsigned)((max_seqlen + QT - 1) / QT), (unsigned)heads, (unsigned)B);
+  Params p{out, cu, (int)B, (int)heads, causal ? 1 : 0, scale, ctx->d_status};
+  // upper bound of the item count from what the host knows; idle CTAs leave after building the tables
+  const int64_t pairs_bound = std::min<int64_t>(tokens / (2 * QT) + B, B * ((max_seqlen + 2 * QT - 1) / (2 * QT)));
+  const int64_t items_bound = std::max<int64_t>(1, pairs_bound * heads);
+  dim3 grid((unsigned)std::min<int64_t>(ctx->sm_count, items_bound));
   static bool configured[64] = {};
   const int dev = ctx->device < 64 ? ctx->device : 63;
   if (!configured[dev]) {
@@ -312,8 +493,8 @@ int attention_tc_launch(ttb_ctx* ctx, int dtype, const void* qkv, int64_t tokens
     TTB_CUDA(ctx, cudaFuncSetAttribute(attention_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     configured[dev] = true;
   }
-  if (dtype == TTB_F16) attention_tc_kernel<__half><<<grid, kThreads, SMEM_BYTES, ctx->stream>>>(tm, p);
-  else attention_tc_kernel<__nv_bfloat16><<<grid, kThreads, SMEM_BYTES, ctx->stream>>>(tm, p);
+  if (dtype == TTB_F16) launch_pdl(attention_tc_kernel<__half>, grid, dim3(kThreads), SMEM_BYTES, ctx->stream, tm, p);
+  else launch_pdl(attention_tc_kernel<__nv_bfloat16>, grid, dim3(kThreads), SMEM_BYTES, ctx->stream, tm, p);
   return launched(ctx, "attention_tc");
 }
 

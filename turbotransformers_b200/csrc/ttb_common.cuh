@@ -1,5 +1,6 @@
 // Shared internals of libttb: the context object, error plumbing and dtype helpers.
 #pragma once
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -65,6 +66,38 @@ inline int launched(ttb_ctx* ctx, const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(ctx, TTB_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));
   return TTB_OK;
+}
+
+// ---- programmatic dependent launch ------------------------------------------------------------------------------
+// A kernel launched through launch_pdl may be scheduled before the kernel ahead of it in the stream has finished: its
+// CTAs run their set-up (barrier initialisation, tensor-memory allocation, descriptor fetches) in the shadow of that
+// kernel's tail. Such a kernel must execute pdl_wait() in EVERY CTA before it reads or writes global memory (and before
+// any early return, so that "this grid is complete" keeps implying "everything ahead of it in the stream is complete");
+// pdl_trigger() lets the grid behind it start its own set-up. Set TTB_PDL=0 to launch everything fully serialised.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("TTB_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
 struct DeviceGuard {

@@ -25,6 +25,8 @@ __global__ void __launch_bounds__(kRowsPerBlock * 32)
 layernorm_rows_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ bias,
                       const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ out, int64_t M, int N,
                       float eps) {
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int warps_total = gridDim.x * kRowsPerBlock;
   for (int64_t row = (int64_t)blockIdx.x * kRowsPerBlock + (threadIdx.x >> 5); row < M; row += warps_total) {
@@ -112,7 +114,7 @@ int launch_layernorm(ttb_ctx* ctx, const T* x, const T* residual, const T* bias,
   const int grid = grid_for(M, kRowsPerBlock, ctx->sm_count);
   const int block = kRowsPerBlock * 32;
 #define LN_CASE(IT)                                                                                             \
-  layernorm_rows_kernel<T, IT, ADD><<<grid, block, 0, ctx->stream>>>(x, residual, bias, gamma, beta, out, M, (int)N, eps)
+  launch_pdl(layernorm_rows_kernel<T, IT, ADD>, dim3(grid), dim3(block), 0, ctx->stream, x, residual, bias, gamma, beta, out, M, (int)N, eps)
   const bool aligned = (N % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) |
                                          reinterpret_cast<uintptr_t>(gamma) | reinterpret_cast<uintptr_t>(beta) |
                                          (ADD ? (reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(bias)) : 0)) %

@@ -329,6 +329,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   constexpr int BK_ELEMS = (KIND == KIND_I8) ? BK_BYTES : BK_BYTES / 2;
   constexpr uint32_t IDESC = make_idesc<KIND, BN, TWO>();
   constexpr int TILE_M = TWO ? 2 * BM : BM;                      // output rows per tile (per CTA pair when TWO)
+  pdl_trigger();  // the next kernel in the stream may start its own set-up; it waits for this grid before touching memory
   const uint32_t rank = TWO ? cluster_ctarank() : 0u;            // 0 = the CTA that issues the MMAs
   const int tile0 = TWO ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int tile_step = TWO ? (int)(gridDim.x >> 1) : (int)gridDim.x;
@@ -380,6 +381,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (TWO) cluster_sync_all();  // the peer's barriers are initialised before anything signals them remotely
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();  // everything above ran in the shadow of the previous kernel; its results are visible from here on
 
   const int num_m = (p.M + TILE_M - 1) / TILE_M, num_n = (p.N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
@@ -771,7 +773,8 @@ int launch_tc(ttb_ctx* ctx, const void* A, int64_t lda, const void* W, const Gem
   const int64_t num_tiles = ((p.M + TILE_M - 1) / TILE_M) * (int64_t)((p.N + BN - 1) / BN);
   if (!TWO) {
     const int grid = (int)(num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count);
-    kern<<<grid, kThreads, C::SMEM_BYTES, ctx->stream>>>(tmA, tmB, tmO, q);
+    cudaError_t e = launch_pdl(kern, dim3((unsigned)grid), dim3(kThreads), C::SMEM_BYTES, ctx->stream, tmA, tmB, tmO, q);
+    if (e != cudaSuccess) return fail(ctx, TTB_ERR_CUDA, "launch of gemm_tc failed: %s", cudaGetErrorString(e));
     return launched(ctx, "gemm_tc");
   }
   const int clusters = (int)(num_tiles < max_clusters[dev] ? num_tiles : max_clusters[dev]);
@@ -780,13 +783,15 @@ int launch_tc(ttb_ctx* ctx, const void* A, int64_t lda, const void* W, const Gem
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = C::SMEM_BYTES;
   cfg.stream = ctx->stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmO, q);
   if (e != cudaSuccess) return fail(ctx, TTB_ERR_CUDA, "cluster launch of gemm_tc failed: %s", cudaGetErrorString(e));
   return launched(ctx, "gemm_tc_pair");

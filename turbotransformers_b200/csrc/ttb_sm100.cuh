@@ -123,6 +123,21 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint32_t a_lo, uint32_
       : "memory");
 }
 
+// D[tmem] (+)= A[tmem] * B[smem]: A is read from tensor memory (lane = row, each 32-bit column holds two consecutive
+// 16-bit K elements), B through a shared-memory descriptor.
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 db;\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // Instruction descriptor for kind::f16: fp32 accumulator, operand format fmt (0 = fp16, 1 = bf16), A K-major,
 // B K-major (b_mn = 0) or MN-major (b_mn = 1), shape M x N.
 __host__ __device__ constexpr uint32_t idesc_f16(int fmt, int M, int N, int b_mn) {
