@@ -54,27 +54,67 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: through NVML in a thread of this process
+    (cheap reads every 25 ms), or, when the NVML binding is missing, through an `nvidia-smi -lms` child process."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
         self.index, self.rows, self.proc, self.window = index, [], None, (0.0, float("inf"))
+        self.nvml, self.handle, self.alive, self.thread = None, None, False, None
 
     def start(self):
-        """Start early (before the warm-up): the tool takes a while to come up and must not do so inside the timed region."""
+        """Start early (before the warm-up): whatever comes up slowly must not do so inside the timed region."""
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20",
+            import pynvml
+            pynvml.nvmlInit()
+            # NVML numbers devices by PCI order; CUDA_VISIBLE_DEVICES may remap, so go through the UUID of the CUDA device
+            import torch
+            uuid = "GPU-" + str(torch.cuda.get_device_properties(self.index).uuid)
+            try:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            except pynvml.NVMLError:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.nvml, self.alive = pynvml, True
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:  # no binding / no NVML: fall back to the command-line tool
+            self.nvml = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
                                           "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
+
+    def _poll(self):
+        n = self.nvml
+        bits = (("hw_slowdown", n.nvmlClocksThrottleReasonHwSlowdown), ("hw_thermal_slowdown", n.nvmlClocksThrottleReasonHwThermalSlowdown),
+                ("sw_thermal_slowdown", n.nvmlClocksThrottleReasonSwThermalSlowdown), ("sw_power_cap", n.nvmlClocksThrottleReasonSwPowerCap))
+        try:
+            mx = n.nvmlDeviceGetMaxClockInfo(self.handle, n.NVML_CLOCK_SM)
+        except n.NVMLError:
+            mx = 0
+        while self.alive:
+            try:
+                sm = n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)
+                mask = n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                row = [str(self.index), str(sm), str(mx), "", ""] + ["Active" if mask & b else "Not Active" for _, b in bits]
+                self.rows.append((time.time(), row))
+            except n.NVMLError:
+                pass
+            time.sleep(0.025)
 
     def _read(self):
         for line in self.proc.stdout:
             self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
 
     def stop(self):
+        if self.nvml:
+            self.alive = False
+            if self.thread:
+                self.thread.join(timeout=1)
         if self.proc:
             self.proc.terminate()
             try:
@@ -94,7 +134,8 @@ class ClockSampler:
             except (ValueError, IndexError):
                 continue
         sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons), "samples": len(sm),
+                "source": "nvml" if self.nvml else "nvidia-smi"}
 
 
 def make_batch(vocab, rank):
@@ -323,8 +364,8 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="timed regions only (for profiler launch lists)")

@@ -1,25 +1,26 @@
 // Self-attention over packed variable-length batches on the 5th-generation tensor cores.
 //
-// Persistent kernel, one CTA per SM. A work item is a pair of 128-row query tiles ("slots" 0 and 1) of one
-// (sequence, head); keys/values stream in 128-row tiles shared by both slots.
-//   warp 0      : TMA loader  - Q tiles (double-buffered per slot), then K_j / V_j tiles into a 3-stage ring. Every tile is
-//                 a [128 rows x 64 columns] 128-byte-swizzled box straight out of the [T, 3H] QKV matrix.
-//   warp 1      : MMA issuer  - S_s = Q_s K_j^T (128x128x64, fp32 in TMEM) and O_s += P_s V_j (128x64x128) with P_s read
-//                 from TMEM and V_j used in place as an MN-major operand. Issue order
-//                 QK(0,0) QK(1,0) | QK(0,j+1) PV(1,j-1) QK(1,j+1) PV(0,j) | ...
-//                 QK(s,j+1) goes out as soon as the softmax warps hold the scores of tile j in registers, so the next
-//                 scores are in TMEM before the current tile's softmax ends; the two slots run half a period apart.
-//                 A wait in the issuing thread only returns once the MMAs it has already issued have drained, so this
-//                 thread waits on one barrier per MMA group: the softmax warps vouch for the K/V tiles a group reads.
-//   warps 4..7  : softmax of slot 0, warps 8..11: softmax of slot 1 (warps 2, 3 idle; registers are moved from the first
+// Persistent kernel, one CTA per SM, two independent streams per CTA. A work item is one 128-row query tile of one
+// (sequence, head); a stream takes every other item of its CTA and walks the key/value tiles (128 rows) of one item
+// after the other as one flat sequence of tiles g = 0, 1, 2, ...
+//   warps 0, 2  : TMA loaders of stream 0 / 1 - the item's Q tile (double-buffered), then K_g / V_g into a 2-stage ring.
+//                 Every tile is a [128 rows x 64 columns] 128-byte-swizzled box straight out of the [T, 3H] QKV matrix.
+//   warps 1, 3  : MMA issuers of stream 0 / 1 - S = Q K_g^T (128x128x64, fp32 in TMEM) and O += P V_g (128x64x128) with P
+//                 read from TMEM and V used in place as an MN-major operand. Per stream the order is
+//                 QK(0) | QK(g+1) PV(g) | ..., across item boundaries: QK(g+1) goes out as soon as the softmax warps hold
+//                 the scores of tile g in registers, so the next scores are in TMEM before the current softmax ends. A
+//                 wait in an issuing thread only returns once the MMAs that thread has issued have drained, so each
+//                 stream has its own issuer, and an issuer waits on one barrier per MMA group: the softmax warps vouch
+//                 for the Q/K/V tiles a group reads.
+//   warps 4..7  : softmax of stream 0, warps 8..11: of stream 1 (registers are moved from the first
 //                 warpgroup to the softmax ones with setmaxnreg) - one query row per thread: scores from TMEM, running
 //                 max / sum in fp32, exp2 with the scale folded in, P written back to TMEM as packed 16-bit pairs.
-//                 O accumulates in TMEM across key tiles. The row maximum is taken on a row's first tile only; later
+//                 O accumulates in TMEM across key tiles. The row maximum is taken on an item's first tile only; later
 //                 tiles reuse it and fall back to a rescale of O only if a probability would leave the 16-bit range
 //                 (row sum above 2^15), which real score distributions do not reach. The final division by the running
 //                 sum makes the result independent of the reference maximum.
 // TMEM (all 512 columns): S0 | S1 (128 each) | O0 | O1 (64 each) | P0 | P1 (64 each).
-// Work items are ordered longest sequence first and dealt round-robin to the CTAs, so the CTAs finish together.
+// Items are ordered longest sequence first and dealt round-robin to the streams, so the streams finish together.
 // Every wait is bounded; on expiry the CTA raises a flag, frees its TMEM and the host sees TTB_ERR_DEVICE_WAIT.
 #include <algorithm>
 #include <cstdlib>
@@ -34,20 +35,18 @@ using namespace ttb::sm100;
 namespace {
 
 constexpr int QT = 128, KT = 128, D = 64;
-constexpr int kStages = 3;
 constexpr int kMaxB = 512;       // sequences per launch that the in-kernel schedule tables hold
 constexpr int kSortMaxB = 256;   // above this the (quadratic) length ranking is skipped and sequences keep their order
-constexpr int kThreads = 384;    // three warpgroups: {loader, MMA, two idle warps}, softmax slot 0, softmax slot 1
+constexpr int kThreads = 384;    // three warpgroups: {loader 0, MMA 0, loader 1, MMA 1}, softmax stream 0, softmax stream 1
 constexpr int TILE_BYTES = 128 * 128;  // a [128 rows x 128 B] tile
-constexpr int SMEM_Q = 0;                                  // [slot][buffer]: 4 tiles
-constexpr int SMEM_K = 4 * TILE_BYTES;                     // kStages tiles
-constexpr int SMEM_V = (4 + kStages) * TILE_BYTES;         // kStages tiles
-constexpr int SMEM_CU = (4 + 2 * kStages) * TILE_BYTES;    // int[kMaxB + 1] token offsets
+// per stream: Q[2], K[2], V[2]
+constexpr int SMEM_STREAM = 6 * TILE_BYTES;
+constexpr int SMEM_CU = 2 * SMEM_STREAM;                   // int[kMaxB + 1] token offsets
 constexpr int SMEM_PREFIX = SMEM_CU + (kMaxB + 1) * 4;     // int[kMaxB + 1] items before each ranked sequence
 constexpr int SMEM_ORDER = SMEM_PREFIX + (kMaxB + 1) * 4;  // uint16[kMaxB] sequence at each rank
 constexpr int SMEM_BARS = (SMEM_ORDER + kMaxB * 2 + 63) / 64 * 64;
-constexpr int kNumBars = 8 + 4 * kStages + 8;
-constexpr int SMEM_BYTES = SMEM_BARS + kNumBars * 8 + 64;
+constexpr int kBarsPerStream = 16;
+constexpr int SMEM_BYTES = SMEM_BARS + 2 * kBarsPerStream * 8 + 64;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRowSumLimit = 32768.0f;  // a tile row sum below this keeps every probability inside fp16 / bf16 range
@@ -62,7 +61,7 @@ struct Params {
 
 struct Item {
   int tok0, len, q0, head;
-  int n0, n1;  // key tiles slot 0 / slot 1 visit (0 = slot idle)
+  int n;  // key tiles this query tile visits
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -81,7 +80,7 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, f
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// Item `i` of the launch: rank-ordered (sequence, 256-row pair) x head.
+// Item `i` of the launch: rank-ordered (sequence, 128-row query tile) x head.
 __device__ __forceinline__ Item decode_item(int i, const Params& p, const int* s_cu, const int* s_prefix, const uint16_t* s_order) {
   Item it;
   it.head = i % p.heads;
@@ -95,18 +94,20 @@ __device__ __forceinline__ Item decode_item(int i, const Params& p, const int* s
   const int seq = s_order[lo];
   it.tok0 = s_cu[seq];
   it.len = s_cu[seq + 1] - it.tok0;
-  it.q0 = (pidx - s_prefix[lo]) * (2 * QT);
+  const int qt = pidx - s_prefix[lo];
+  it.q0 = qt * QT;
   const int n_all = (it.len + KT - 1) / KT;
-  const bool act1 = it.q0 + QT < it.len;
-  if (p.causal) {
-    it.n0 = min(n_all, it.q0 / KT + 1);
-    it.n1 = act1 ? min(n_all, it.q0 / KT + 2) : 0;
-  } else {
-    it.n0 = n_all;
-    it.n1 = act1 ? n_all : 0;
-  }
+  it.n = p.causal ? min(n_all, qt + 1) : n_all;
   return it;
 }
+
+// Where one side (score MMAs or output MMAs) of a stream stands in the stream's flat tile sequence.
+struct Cursor {
+  int i;        // item, >= n_items when the stream is exhausted
+  int j, n;     // tile within the item, tiles of the item
+  uint32_t g;   // tiles before this one in the stream
+  uint32_t nq;  // items before this one in the stream
+};
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -127,30 +128,33 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
   uint16_t* s_order = reinterpret_cast<uint16_t*>(smem + SMEM_ORDER);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_BARS);
   const uint32_t bar0 = smem_u32(bars);
-  auto q_full = [&](int s, int b) { return bar0 + 8u * (s * 2 + b); };
-  auto q_empty = [&](int s, int b) { return bar0 + 8u * (4 + s * 2 + b); };
-  auto k_full = [&](int st) { return bar0 + 8u * (8 + st); };
-  auto k_empty = [&](int st) { return bar0 + 8u * (8 + kStages + st); };
-  auto v_full = [&](int st) { return bar0 + 8u * (8 + 2 * kStages + st); };
-  auto v_empty = [&](int st) { return bar0 + 8u * (8 + 3 * kStages + st); };
-  auto s_full = [&](int s) { return bar0 + 8u * (8 + 4 * kStages + s); };
-  auto p_ready = [&](int s) { return bar0 + 8u * (10 + 4 * kStages + s); };
-  auto o_done = [&](int s) { return bar0 + 8u * (12 + 4 * kStages + s); };
-  auto s_free = [&](int s) { return bar0 + 8u * (14 + 4 * kStages + s); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+  auto bar = [&](int s, int k) { return bar0 + 8u * (s * kBarsPerStream + k); };
+  auto q_full = [&](int s, int b) { return bar(s, b); };
+  auto q_empty = [&](int s, int b) { return bar(s, 2 + b); };
+  auto k_full = [&](int s, int st) { return bar(s, 4 + st); };
+  auto k_empty = [&](int s, int st) { return bar(s, 6 + st); };
+  auto v_full = [&](int s, int st) { return bar(s, 8 + st); };
+  auto v_empty = [&](int s, int st) { return bar(s, 10 + st); };
+  auto s_full = [&](int s) { return bar(s, 12); };
+  auto s_free = [&](int s) { return bar(s, 13); };
+  auto p_ready = [&](int s) { return bar(s, 14); };
+  auto o_done = [&](int s) { return bar(s, 15); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kBarsPerStream);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  auto smem_q = [&](int s, int b) { return base + (uint32_t)(s * SMEM_STREAM + b * TILE_BYTES); };
+  auto smem_k = [&](int s, int st) { return base + (uint32_t)(s * SMEM_STREAM + (2 + st) * TILE_BYTES); };
+  auto smem_v = [&](int s, int st) { return base + (uint32_t)(s * SMEM_STREAM + (4 + st) * TILE_BYTES); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int H = p.heads * D;
 
   pdl_trigger();
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 8 + 4 * kStages; ++i) mbar_init(bar0 + 8u * i, 1);  // q and k/v full/empty
     for (int s = 0; s < 2; ++s) {
-      mbar_init(s_full(s), 1);
-      mbar_init(p_ready(s), 4);  // one arrival per softmax warp
+      for (int k = 0; k < 13; ++k) mbar_init(bar(s, k), 1);  // TMA and MMA-commit barriers
+      mbar_init(s_free(s), 4);                                // one arrival per softmax warp
+      mbar_init(p_ready(s), 4);
       mbar_init(o_done(s), 1);
-      mbar_init(s_free(s), 4);   // one arrival per softmax warp
     }
     *abort_flag = 0;
     mbar_init_fence();
@@ -174,22 +178,22 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
     s_order[rank] = (uint16_t)i;
   }
   __syncthreads();
-  if (warp == 0) {  // exclusive scan of the pair counts in rank order
+  if (warp == 0) {  // exclusive scan of the query-tile counts in rank order
     int carry = 0;
     for (int r0 = 0; r0 < p.batch; r0 += 32) {
       const int r = r0 + lane;
-      int pairs = 0;
+      int tiles = 0;
       if (r < p.batch) {
         const int seq = s_order[r];
-        pairs = (s_cu[seq + 1] - s_cu[seq] + 2 * QT - 1) / (2 * QT);
+        tiles = (s_cu[seq + 1] - s_cu[seq] + QT - 1) / QT;
       }
-      int incl = pairs;
+      int incl = tiles;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const int v = __shfl_up_sync(0xffffffffu, incl, o);
         if (lane >= o) incl += v;
       }
-      if (r < p.batch) s_prefix[r] = carry + incl - pairs;
+      if (r < p.batch) s_prefix[r] = carry + incl - tiles;
       carry += __shfl_sync(0xffffffffu, incl, 31);
     }
     if (lane == 0) s_prefix[p.batch] = carry;
@@ -199,38 +203,34 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const int n_items = s_prefix[p.batch] * p.heads;
+  const int stride = 2 * (int)gridDim.x;  // a stream's items: 2 * blockIdx.x + stream, then every `stride`-th
   auto tmem_s = [&](int s) { return tmem + (uint32_t)(s * 128); };
   auto tmem_o = [&](int s) { return tmem + (uint32_t)(256 + s * 64); };
   auto tmem_p = [&](int s) { return tmem + (uint32_t)(384 + s * 64); };
 
   if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
-    if (warp == 0) {
-      // ------------------------------------------------------------------ loader
+    if (warp == 0 || warp == 2) {
+      // ------------------------------------------------------------------ loader of stream `s`
+      const int s = warp >> 1;
       if (lane == 0) {
-        uint32_t kvc = 0, nq0 = 0, nq1 = 0;
+        uint32_t g = 0, nq = 0;
         bool ok = true;
-        for (int i = blockIdx.x; i < n_items && ok; i += gridDim.x) {
+        for (int i = 2 * (int)blockIdx.x + s; i < n_items && ok; i += stride, ++nq) {
           const Item it = decode_item(i, p, s_cu, s_prefix, s_order);
-          auto load_q = [&](int s, uint32_t& nq) {
-            const int b = nq & 1;
-            if (!mbar_wait(q_empty(s, b), ((nq >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; return; }
-            mbar_expect_tx(q_full(s, b), TILE_BYTES);
-            tma_load_2d(base + SMEM_Q + (s * 2 + b) * TILE_BYTES, &tm, q_full(s, b), it.head * D, it.tok0 + it.q0 + s * QT);
-            ++nq;
-          };
-          if (it.n0 > 0) load_q(0, nq0);
-          if (ok && it.n1 > 0) load_q(1, nq1);
-          const int nmax = max(it.n0, it.n1);
-          for (int j = 0; j < nmax && ok; ++j, ++kvc) {
-            const int st = kvc % kStages;
-            const uint32_t par = ((kvc / kStages) & 1u) ^ 1u;
-            if (!mbar_wait(k_empty(st), par, abort_flag)) { ok = false; break; }
-            mbar_expect_tx(k_full(st), TILE_BYTES);
-            tma_load_2d(base + SMEM_K + st * TILE_BYTES, &tm, k_full(st), H + it.head * D, it.tok0 + j * KT);
-            if (!mbar_wait(v_empty(st), par, abort_flag)) { ok = false; break; }
-            mbar_expect_tx(v_full(st), TILE_BYTES);
-            tma_load_2d(base + SMEM_V + st * TILE_BYTES, &tm, v_full(st), 2 * H + it.head * D, it.tok0 + j * KT);
+          const int b = nq & 1;
+          if (!mbar_wait(q_empty(s, b), ((nq >> 1) & 1u) ^ 1u, abort_flag)) break;
+          mbar_expect_tx(q_full(s, b), TILE_BYTES);
+          tma_load_2d(smem_q(s, b), &tm, q_full(s, b), it.head * D, it.tok0 + it.q0);
+          for (int j = 0; j < it.n; ++j, ++g) {
+            const int st = g & 1;
+            const uint32_t par = ((g >> 1) & 1u) ^ 1u;
+            if (!mbar_wait(k_empty(s, st), par, abort_flag)) { ok = false; break; }
+            mbar_expect_tx(k_full(s, st), TILE_BYTES);
+            tma_load_2d(smem_k(s, st), &tm, k_full(s, st), H + it.head * D, it.tok0 + j * KT);
+            if (!mbar_wait(v_empty(s, st), par, abort_flag)) { ok = false; break; }
+            mbar_expect_tx(v_full(s, st), TILE_BYTES);
+            tma_load_2d(smem_v(s, st), &tm, v_full(s, st), 2 * H + it.head * D, it.tok0 + j * KT);
           }
         }
         if (*abort_flag) {  // let copies in flight land before shared memory is released
@@ -240,74 +240,62 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
         }
       }
       __syncwarp();
-    } else if (warp == 1) {
-      // ------------------------------------------------------------------ MMA issuer
+    } else {
+      // ------------------------------------------------------------------ MMA issuer of stream `s` (warp 1: 0, warp 3: 1)
+      const int s = warp >> 1;
       if (lane == 0) {
-        uint32_t kvc = 0, nq[2] = {0, 0}, tcount[2] = {0, 0};
         bool ok = true;
-        for (int i = blockIdx.x; i < n_items && ok; i += gridDim.x) {
-          const Item it = decode_item(i, p, s_cu, s_prefix, s_order);
-          const int ns[2] = {it.n0, it.n1};
-          uint32_t q_lo[2] = {0, 0};
-          int qbuf[2] = {0, 0};
-#pragma unroll
-          for (int s = 0; s < 2; ++s) {
-            if (!ok || ns[s] == 0) continue;
-            qbuf[s] = nq[s] & 1;
-            if (!mbar_wait(q_full(s, qbuf[s]), (nq[s] >> 1) & 1u, abort_flag)) { ok = false; continue; }
-            q_lo[s] = desc_lo(base + SMEM_Q + (s * 2 + qbuf[s]) * TILE_BYTES);
-            ++nq[s];
+        Cursor qc, pc;  // score side and output side
+        auto advance = [&](Cursor& c) {
+          ++c.g;
+          if (++c.j == c.n) {
+            c.j = 0;
+            c.i += stride;
+            ++c.nq;
+            c.n = (c.i < n_items) ? decode_item(c.i, p, s_cu, s_prefix, s_order).n : 0;
           }
-          // K_0 of this item; every later tile is vouched for by the softmax warps before they release P
-          if (ok && !mbar_wait(k_full(kvc % kStages), (kvc / kStages) & 1u, abort_flag)) ok = false;
-          if (!ok) break;
-          // QK(s, j) with j > 0 follows the softmax warps' release of S_s (scores of tile j-1 are in their registers and
-          // K_j has landed); tile t of this item is the slot's (tbase[s] + t)-th since the kernel started
-          const uint32_t tbase[2] = {tcount[0], tcount[1]};
-          auto qk = [&](auto slot_c, int j) {
-            constexpr int s = decltype(slot_c)::value;
-            if (j > 0) {
-              if (!mbar_wait(s_free(s), (tbase[s] + (uint32_t)(j - 1)) & 1u, abort_flag)) { ok = false; return; }
-              tc_fence_after();
-            }
-            const uint32_t c = kvc + (uint32_t)j;
-            const int st = c % kStages;
-            const uint32_t k_lo = desc_lo(base + SMEM_K + st * TILE_BYTES);
+        };
+        qc.i = 2 * (int)blockIdx.x + s;
+        qc.j = 0;
+        qc.g = 0;
+        qc.nq = 0;
+        qc.n = (qc.i < n_items) ? decode_item(qc.i, p, s_cu, s_prefix, s_order).n : 0;
+        pc = qc;
+        // S = Q K_g^T. Q and K_g are in shared memory and S is free when this is called.
+        auto qk = [&]() {
+          const int st = qc.g & 1, qb = qc.nq & 1;
+          const uint32_t q_lo = desc_lo(smem_q(s, qb)), k_lo = desc_lo(smem_k(s, st));
 #pragma unroll
-            for (int k = 0; k < D / 16; ++k) umma_f16(tmem_s(s), q_lo[s] + k * 2, k_lo + k * 2, IDESC_S, k != 0);  // 32 bytes of d per step
-            tc_commit(s_full(s));
-            if (s == 1 || j >= ns[1]) tc_commit(k_empty(st));      // last reader of K_j
-            if (j == ns[s] - 1) tc_commit(q_empty(s, qbuf[s]));    // last reader of Q_s
-          };
-          auto pv = [&](auto slot_c, int j) {
-            constexpr int s = decltype(slot_c)::value;
-            const uint32_t c = kvc + (uint32_t)j;
-            const int st = c % kStages;
-            // P_j in TMEM, O rescaled if needed, V_j in shared memory
-            if (!mbar_wait(p_ready(s), tcount[s] & 1u, abort_flag)) { ok = false; return; }
+          for (int k = 0; k < D / 16; ++k) umma_f16(tmem_s(s), q_lo + k * 2, k_lo + k * 2, IDESC_S, k != 0);  // 32 bytes of d per step
+          tc_commit(s_full(s));
+          tc_commit(k_empty(s, st));
+          if (qc.j == qc.n - 1) tc_commit(q_empty(s, qb));  // last reader of this item's Q
+          advance(qc);
+        };
+        // first tile: nothing is in flight yet, so waiting here costs nothing
+        if (qc.i < n_items) {
+          ok = mbar_wait(q_full(s, 0), 0, abort_flag) && mbar_wait(k_full(s, 0), 0, abort_flag);
+          if (ok) qk();
+        }
+        while (ok && pc.i < n_items) {
+          // scores of the next tile, once the softmax warps hold the current tile's scores in registers (they also vouch
+          // for the Q and K tiles the MMA reads)
+          if (qc.i < n_items) {
+            if (!mbar_wait(s_free(s), (qc.g - 1) & 1u, abort_flag)) break;
             tc_fence_after();
-            const uint32_t v_lo = desc_lo(base + SMEM_V + st * TILE_BYTES);
-#pragma unroll
-            for (int k = 0; k < KT / 16; ++k)  // 16 keys per MMA: 8 TMEM columns of P, 16 rows (of 128 bytes) of V
-              umma_f16_ts(tmem_o(s), tmem_p(s) + (uint32_t)(k * 8), v_lo + (uint32_t)(k * (16 * 128 >> 4)), IDESC_O, (j | k) != 0);
-            tc_commit(o_done(s));
-            ++tcount[s];
-            if (s == 1 || j >= ns[1]) tc_commit(v_empty(st));  // last reader of V_j
-          };
-          constexpr std::integral_constant<int, 0> S0{};
-          constexpr std::integral_constant<int, 1> S1{};
-          const int nmax = max(it.n0, it.n1);
-          tc_fence_after();
-          if (it.n0 > 0) qk(S0, 0);
-          if (it.n1 > 0) qk(S1, 0);
-          // the two slots run half a period apart: while one slot's softmax works on tile j, the other slot's events arrive
-          for (int j = 0; j <= nmax && ok; ++j) {
-            if (j + 1 < it.n0) qk(S0, j + 1);
-            if (ok && j > 0 && j <= it.n1) pv(S1, j - 1);
-            if (ok && j + 1 < it.n1) qk(S1, j + 1);
-            if (ok && j < it.n0) pv(S0, j);
+            qk();
           }
-          kvc += (uint32_t)nmax;
+          // O (+)= P V_g once the softmax warps have released P (and vouched for V_g)
+          if (!mbar_wait(p_ready(s), pc.g & 1u, abort_flag)) break;
+          tc_fence_after();
+          const int st = pc.g & 1;
+          const uint32_t v_lo = desc_lo(smem_v(s, st));
+#pragma unroll
+          for (int k = 0; k < KT / 16; ++k)  // 16 keys per MMA: 8 TMEM columns of P, 16 rows (of 128 bytes) of V
+            umma_f16_ts(tmem_o(s), tmem_p(s) + (uint32_t)(k * 8), v_lo + (uint32_t)(k * (16 * 128 >> 4)), IDESC_O, (pc.j | k) != 0);
+          tc_commit(o_done(s));
+          tc_commit(v_empty(s, st));
+          advance(pc);
         }
       }
       __syncwarp();
@@ -315,44 +303,41 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     // ------------------------------------------------------------------ softmax + output (one query row per thread)
-    const int slot = (warp - 4) >> 2;
+    const int s = (warp - 4) >> 2;
     const int quad = warp & 3;                  // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may touch
     const int row = quad * 32 + lane;           // row within the tile == TMEM lane
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-    const uint32_t ts = tmem_s(slot) + lane_addr, to = tmem_o(slot) + lane_addr, tp = tmem_p(slot) + lane_addr;
+    const uint32_t ts = tmem_s(s) + lane_addr, to = tmem_o(s) + lane_addr, tp = tmem_p(s) + lane_addr;
     const float sc = p.scale * kLog2e;
-    uint32_t tcount = 0, kvc = 0;
+    uint32_t g = 0, nq = 0;
     bool ok = true;
 
-    for (int i = blockIdx.x; i < n_items && ok; i += gridDim.x) {
+    for (int i = 2 * (int)blockIdx.x + s; i < n_items && ok; i += stride, ++nq) {
       const Item it = decode_item(i, p, s_cu, s_prefix, s_order);
-      const int nmax = max(it.n0, it.n1);
-      const int n_tiles = slot ? it.n1 : it.n0;
-      const uint32_t kv0 = kvc;
-      kvc += (uint32_t)nmax;
-      if (n_tiles == 0) continue;
-      const int q0 = it.q0 + slot * QT;
-      const int qrow = q0 + row;  // row within the sequence
+      const bool has_next = i + stride < n_items;
+      const int qrow = it.q0 + row;  // row within the sequence
       float m_used = -INFINITY, l_run = 0.f;
 
-      for (int j = 0; j < n_tiles; ++j, ++tcount) {
+      for (int j = 0; j < it.n; ++j, ++g) {
         const int k0 = j * KT;
-        if (!__all_sync(0xffffffffu, mbar_wait(s_full(slot), tcount & 1u, abort_flag))) { ok = false; break; }  // warp-uniform
+        if (!__all_sync(0xffffffffu, mbar_wait(s_full(s), g & 1u, abort_flag))) { ok = false; break; }  // warp-uniform
         tc_fence_after();
         uint32_t sr[4][32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32_issue(ts + (uint32_t)(c * 32), sr[c]);
-        const uint32_t kvj = kv0 + (uint32_t)j;
-        if (j + 1 < n_tiles) {  // the next score MMA reads K_{j+1}
-          if (!__all_sync(0xffffffffu, mbar_wait(k_full((kvj + 1) % kStages), ((kvj + 1) / kStages) & 1u, abort_flag))) { ok = false; break; }
+        // the stream's next score MMA reads K_{g+1}, and the next item's Q when this is the item's last tile
+        if (j + 1 < it.n || has_next) {
+          bool landed = mbar_wait(k_full(s, (g + 1) & 1), ((g + 1) >> 1) & 1u, abort_flag);
+          if (j + 1 == it.n) landed = mbar_wait(q_full(s, (nq + 1) & 1), ((nq + 1) >> 1) & 1u, abort_flag) && landed;
+          if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }
         }
         tmem_ld_wait();
-        tc_fence_before();  // S_j is in registers: the scores of tile j+1 may overwrite it (one phase per tile)
+        tc_fence_before();  // S_g is in registers: the next scores may overwrite it (one phase per tile)
         __syncwarp();
-        if (lane == 0) mbar_arrive(s_free(slot));
-        // the MMA released by this tile's P reads V_j
-        if (!__all_sync(0xffffffffu, mbar_wait(v_full(kvj % kStages), (kvj / kStages) & 1u, abort_flag))) { ok = false; break; }
-        if ((k0 + KT > it.len) || (p.causal && k0 + KT - 1 > q0 + quad * 32)) {  // edge tile: keys past the end / above the diagonal
+        if (lane == 0) mbar_arrive(s_free(s));
+        // the output MMA released by this tile's P reads V_g
+        if (!__all_sync(0xffffffffu, mbar_wait(v_full(s, g & 1), (g >> 1) & 1u, abort_flag))) { ok = false; break; }
+        if ((k0 + KT > it.len) || (p.causal && k0 + KT - 1 > it.q0 + quad * 32)) {  // edge tile: keys past the end / above the diagonal
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
@@ -374,8 +359,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
               for (int c = 0; c < 4; ++c) mx[c] = fmaxf(mx[c], __uint_as_float(sr[c][e]));
             const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * sc);
             if (j > 0) {
-              // O holds tiles < j once PV(j-1) has completed; nothing writes it again until this warp releases P_j
-              if (!__all_sync(0xffffffffu, mbar_wait(o_done(slot), (tcount - 1) & 1u, abort_flag))) { ok = false; break; }
+              // O holds tiles < j once PV(g-1) has completed; nothing writes it again until this warp releases P_g
+              if (!__all_sync(0xffffffffu, mbar_wait(o_done(s), (g - 1) & 1u, abort_flag))) { ok = false; break; }
               tc_fence_after();
               const float corr = ex2(m_used - m_new);  // 2^-inf = 0 covers a row that had seen no live key yet
               l_run *= corr;
@@ -412,18 +397,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
         }
         if (!ok) break;
         l_run += rs0 + rs1;
-        // P_s is read by PV(j-1), which is issued after the scores of this tile: it must have completed before P_j lands
-        if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(o_done(slot), (tcount - 1) & 1u, abort_flag))) { ok = false; break; }
+        // P is read by PV(g-1), which is issued after the scores of this tile: it must have completed before P_g lands
+        if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(o_done(s), (g - 1) & 1u, abort_flag))) { ok = false; break; }
         tmem_st32(tp, pk[0]);
         tmem_st32(tp + 32u, pk[1]);
         tmem_st_wait();
-        tc_fence_before();  // S_j read, O rescaled, P_j written
+        tc_fence_before();  // O rescaled, P_g written
         __syncwarp();
-        if (lane == 0) mbar_arrive(p_ready(slot));
+        if (lane == 0) mbar_arrive(p_ready(s));
       }
       if (!ok) break;
       // ---- output: O / l, 128 contiguous bytes per row
-      if (!__all_sync(0xffffffffu, mbar_wait(o_done(slot), (tcount - 1) & 1u, abort_flag))) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(o_done(s), (g - 1) & 1u, abort_flag))) { ok = false; break; }
       tc_fence_after();
       const float inv = 1.0f / l_run;
       T* op = static_cast<T*>(p.out) + (long long)(it.tok0 + qrow) * H + it.head * D;
@@ -444,8 +429,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
           }
         }
       }
-      // The next item's first PV (which overwrites O) waits for this warp's next p_ready arrival, which follows
-      // these loads in program order.
+      // The next item's first output MMA (which overwrites O, and reads the P written after these loads) waits for this
+      // warp's next p_ready arrival, which follows these loads in program order.
     }
   }
 
@@ -482,10 +467,10 @@ int attention_tc_launch(ttb_ctx* ctx, int dtype, const void* qkv, int64_t tokens
   if (!encode_tile_map(&tm, qkv, 2, dtype == TTB_BF16, (uint64_t)tokens, (uint64_t)(3 * H), (uint64_t)(3 * H), 128))
     return TTB_ERR_UNSUPPORTED;
   Params p{out, cu, (int)B, (int)heads, causal ? 1 : 0, scale, ctx->d_status};
-  // upper bound of the item count from what the host knows; idle CTAs leave after building the tables
-  const int64_t pairs_bound = std::min<int64_t>(tokens / (2 * QT) + B, B * ((max_seqlen + 2 * QT - 1) / (2 * QT)));
-  const int64_t items_bound = std::max<int64_t>(1, pairs_bound * heads);
-  dim3 grid((unsigned)std::min<int64_t>(ctx->sm_count, items_bound));
+  // upper bound of the item count from what the host knows; a CTA runs two streams, idle CTAs leave after the tables
+  const int64_t tiles_bound = std::min<int64_t>(tokens / QT + B, B * ((max_seqlen + QT - 1) / QT));
+  const int64_t items_bound = std::max<int64_t>(1, tiles_bound * heads);
+  dim3 grid((unsigned)std::min<int64_t>(ctx->sm_count, (items_bound + 1) / 2));
   static bool configured[64] = {};
   const int dev = ctx->device < 64 ? ctx->device : 63;
   if (!configured[dev]) {

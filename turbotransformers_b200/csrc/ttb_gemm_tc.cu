@@ -797,13 +797,14 @@ int launch_tc(ttb_ctx* ctx, const void* A, int64_t lda, const void* W, const Gem
   return launched(ctx, "gemm_tc_pair");
 }
 
-// TTB_GEMM_PAIR=0 disables the two-CTA variant (a debugging switch; it is on by default).
-bool pair_enabled() {
-  static const bool on = [] {
+// TTB_GEMM_PAIR: 0 disables the two-CTA variant, 2 uses it for every shape with at least half a wave of pair tiles
+// (measurement switches); unset = chosen by shape.
+int pair_mode() {
+  static const int mode = [] {
     const char* e = getenv("TTB_GEMM_PAIR");
-    return !(e && e[0] == '0');
+    return (e && e[0] == '0') ? 0 : ((e && e[0] == '2') ? 2 : 1);
   }();
-  return on;
+  return mode;
 }
 
 template <int KIND, typename OutT>
@@ -813,10 +814,12 @@ int pick_tile(ttb_ctx* ctx, const void* A, int64_t lda, const void* W, const Gem
   const int64_t num_m = (p.M + BM - 1) / BM;
   auto tiles = [&](int bn) { return num_m * ((p.N + bn - 1) / bn); };
   const int64_t pair_tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * (int64_t)((p.N + 255) / 256);
-  // Measured on B200: pairs win once the mainloop is long (K >= 2048); for short K the single-CTA kernel's shorter
-  // pipeline fill and tail win.
+  // Measured on B200 in back-to-back launches at M = 18424 (single CTA -> pair, TFLOP/s): N=2304 K=768 1097 -> 1228,
+  // N=3072 K=768 1088 -> 1165, N=768 K=3072 1171 -> 1273, but N=768 K=768 789 -> 756: pairs win unless both the
+  // mainloop and the row of tiles are short.
   const int64_t k_bytes = (int64_t)p.K * (KIND == KIND_I8 ? 1 : 2);
-  if (pair_enabled() && pair_tiles >= ctx->sm_count / 2 && k_bytes >= 4096) return launch_tc<256, KIND, OutT, true>(ctx, A, lda, W, p);
+  const bool pair_pays = k_bytes >= 4096 || p.N >= 1536;
+  if (pair_mode() && pair_tiles >= ctx->sm_count / 2 && (pair_pays || pair_mode() == 2)) return launch_tc<256, KIND, OutT, true>(ctx, A, lda, W, p);
   if (tiles(256) >= ctx->sm_count) return launch_tc<256, KIND, OutT, false>(ctx, A, lda, W, p);
   if (tiles(128) >= ctx->sm_count) return launch_tc<128, KIND, OutT, false>(ctx, A, lda, W, p);
   if (tiles(64) >= ctx->sm_count / 2) return launch_tc<64, KIND, OutT, false>(ctx, A, lda, W, p);
