@@ -284,17 +284,26 @@ def run_ours(args):
     tokens = sum(lens)
     ids_host = torch.cat(ids).pin_memory()
     ids_dev = ids_host.to(dev)
-    pooled_host = torch.empty(BATCH, HIDDEN, dtype=torch.float16).pin_memory()
+    # End to end the way a serving loop runs it: every step copies its ids from pinned host memory and its pooled output back
+    # to pinned host memory; the host waits for the result of step i-1 only after it has enqueued step i (two result buffers),
+    # so the GPU never sits idle while the host enqueues. Every result has reached the host before the timed region ends.
+    pooled_host = [torch.empty(BATCH, HIDDEN, dtype=torch.float16).pin_memory() for _ in range(2)]
+    arrived = [torch.cuda.Event(), torch.cuda.Event()]
+    e2e_state = {"i": 0}
 
     def step_device():
         return model(ids_dev, lens)
 
     def step_e2e():
+        i = e2e_state["i"]
         d = ids_host.to(dev, non_blocking=True)
         seq, pooled = model(d, lens)[:2]
-        pooled_host.copy_(pooled, non_blocking=True)
-        torch.cuda.current_stream().synchronize()  # the caller has its result on the host
-        return pooled_host
+        pooled_host[i & 1].copy_(pooled, non_blocking=True)
+        arrived[i & 1].record()
+        if i > 0:
+            arrived[(i - 1) & 1].synchronize()  # the caller has the previous step's result on the host
+        e2e_state["i"] = i + 1
+        return pooled_host[(i - 1) & 1]
 
     def barrier():
         if world > 1:
@@ -339,7 +348,8 @@ def run_ours(args):
                 "warmup": max(3, args.warmup), "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": workload_config(world),
                 "e2e": {"value": round(e2e_seq_per_s, 1), "unit": UNIT, "h2d_bytes_per_step": int(ids_host.numel() * 8),
-                        "d2h_bytes_per_step": int(pooled_host.numel() * 2), "ms_per_step": round(ms_e2e / args.steps, 4)},
+                        "d2h_bytes_per_step": int(pooled_host[0].numel() * 2), "ms_per_step": round(ms_e2e / args.steps, 4),
+                        "pipelining": "the host waits for step i-1's result after enqueueing step i; all results on the host before the region ends"},
                 "gpu_launches": int(launches), "clocks": clocks,
                 "tokens_per_step_per_gpu": tokens,
                 "model_tflops": round(step_flops * world * args.steps / (ms / 1e3) / 1e12, 1),

@@ -311,6 +311,34 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
     const float sc = p.scale * kLog2e;
     uint32_t g = 0, nq = 0;
     bool ok = true;
+    // The output pass of an item (O / l to global memory) is deferred into the first tile of the stream's next item, after
+    // that tile's scores are in registers: by then the last output MMA has long completed, so nothing is waited for.
+    bool pend = false, pend_store = false;
+    float pend_inv = 0.f;
+    T* pend_op = nullptr;
+    auto flush_output = [&]() {  // whole warp; g = tiles finished so far, the pending item's last tile is g - 1
+      if (!__all_sync(0xffffffffu, mbar_wait(o_done(s), (g - 1) & 1u, abort_flag))) return false;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r[32];
+        tmem_ld32_issue(to + (uint32_t)(c * 32), r);
+        tmem_ld_wait();
+        if (pend_store) {  // 128 contiguous bytes per row
+#pragma unroll
+          for (int g8 = 0; g8 < 4; ++g8) {
+            uint4 q;
+            q.x = pack2<T>(__uint_as_float(r[g8 * 8 + 0]) * pend_inv, __uint_as_float(r[g8 * 8 + 1]) * pend_inv);
+            q.y = pack2<T>(__uint_as_float(r[g8 * 8 + 2]) * pend_inv, __uint_as_float(r[g8 * 8 + 3]) * pend_inv);
+            q.z = pack2<T>(__uint_as_float(r[g8 * 8 + 4]) * pend_inv, __uint_as_float(r[g8 * 8 + 5]) * pend_inv);
+            q.w = pack2<T>(__uint_as_float(r[g8 * 8 + 6]) * pend_inv, __uint_as_float(r[g8 * 8 + 7]) * pend_inv);
+            *reinterpret_cast<uint4*>(pend_op + c * 32 + g8 * 8) = q;
+          }
+        }
+      }
+      pend = false;
+      return true;
+    };
 
     for (int i = 2 * (int)blockIdx.x + s; i < n_items && ok; i += stride, ++nq) {
       const Item it = decode_item(i, p, s_cu, s_prefix, s_order);
@@ -335,8 +363,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
         tc_fence_before();  // S_g is in registers: the next scores may overwrite it (one phase per tile)
         __syncwarp();
         if (lane == 0) mbar_arrive(s_free(s));
+        // The previous item's output pass. It reads O before this warp's next p_ready arrival, which is what the next
+        // output MMA (the one that overwrites O) waits for; it also proves PV(g-1) complete, so P may be rewritten.
+        if (pend && !flush_output()) { ok = false; break; }
         // the output MMA released by this tile's P reads V_g
         if (!__all_sync(0xffffffffu, mbar_wait(v_full(s, g & 1), (g >> 1) & 1u, abort_flag))) { ok = false; break; }
+        // keys of this tile that at least one row of this warp can see, in 32-key chunks: the others cost no exponentials
+        int lim = it.len - k0;
+        if (p.causal) lim = min(lim, it.q0 + quad * 32 + 32 - k0);
+        const int live = (min(lim, KT) + 31) >> 5;
         if ((k0 + KT > it.len) || (p.causal && k0 + KT - 1 > it.q0 + quad * 32)) {  // edge tile: keys past the end / above the diagonal
 #pragma unroll
           for (int c = 0; c < 4; ++c)
@@ -380,15 +415,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
           rs0 = 0.f;
           rs1 = 0.f;
 #pragma unroll
-          for (int cc = 0; cc < 2; ++cc) {
+          for (int c = 0; c < 4; ++c) {
+            uint32_t* dst = &pk[c >> 1][(c & 1) * 16];
+            if (c < live) {  // warp-uniform
 #pragma unroll
-            for (int e = 0; e < 32; e += 2) {
-              const float a0 = ex2(fmaf(__uint_as_float(sr[cc * 2][e]), sc, -m_sub)), a1 = ex2(fmaf(__uint_as_float(sr[cc * 2][e + 1]), sc, -m_sub));
-              const float b0 = ex2(fmaf(__uint_as_float(sr[cc * 2 + 1][e]), sc, -m_sub)), b1 = ex2(fmaf(__uint_as_float(sr[cc * 2 + 1][e + 1]), sc, -m_sub));
-              rs0 += a0 + a1;
-              rs1 += b0 + b1;
-              pk[cc][e >> 1] = pack2<T>(a0, a1);
-              pk[cc][16 + (e >> 1)] = pack2<T>(b0, b1);
+              for (int e = 0; e < 32; e += 4) {
+                const float a0 = ex2(fmaf(__uint_as_float(sr[c][e]), sc, -m_sub)), a1 = ex2(fmaf(__uint_as_float(sr[c][e + 1]), sc, -m_sub));
+                const float a2 = ex2(fmaf(__uint_as_float(sr[c][e + 2]), sc, -m_sub)), a3 = ex2(fmaf(__uint_as_float(sr[c][e + 3]), sc, -m_sub));
+                rs0 += a0 + a1;
+                rs1 += a2 + a3;
+                dst[e >> 1] = pack2<T>(a0, a1);
+                dst[(e >> 1) + 1] = pack2<T>(a2, a3);
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 16; ++e) dst[e] = 0u;
             }
           }
           // every probability is below the row sum: under the limit none of them leaves the 16-bit range
@@ -407,31 +448,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
         if (lane == 0) mbar_arrive(p_ready(s));
       }
       if (!ok) break;
-      // ---- output: O / l, 128 contiguous bytes per row
-      if (!__all_sync(0xffffffffu, mbar_wait(o_done(s), (g - 1) & 1u, abort_flag))) { ok = false; break; }
-      tc_fence_after();
-      const float inv = 1.0f / l_run;
-      T* op = static_cast<T*>(p.out) + (long long)(it.tok0 + qrow) * H + it.head * D;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld32_issue(to + (uint32_t)(c * 32), r);
-        tmem_ld_wait();
-        if (qrow < it.len) {
-#pragma unroll
-          for (int g8 = 0; g8 < 4; ++g8) {
-            uint4 q;
-            q.x = pack2<T>(__uint_as_float(r[g8 * 8 + 0]) * inv, __uint_as_float(r[g8 * 8 + 1]) * inv);
-            q.y = pack2<T>(__uint_as_float(r[g8 * 8 + 2]) * inv, __uint_as_float(r[g8 * 8 + 3]) * inv);
-            q.z = pack2<T>(__uint_as_float(r[g8 * 8 + 4]) * inv, __uint_as_float(r[g8 * 8 + 5]) * inv);
-            q.w = pack2<T>(__uint_as_float(r[g8 * 8 + 6]) * inv, __uint_as_float(r[g8 * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(op + c * 32 + g8 * 8) = q;
-          }
-        }
-      }
-      // The next item's first output MMA (which overwrites O, and reads the P written after these loads) waits for this
-      // warp's next p_ready arrival, which follows these loads in program order.
+      pend = true;
+      pend_store = qrow < it.len;
+      pend_inv = 1.0f / l_run;
+      pend_op = static_cast<T*>(p.out) + (long long)(it.tok0 + qrow) * H + it.head * D;
     }
+    if (ok && pend) flush_output();  // the stream's last item
   }
 
   tc_fence_before();
