@@ -6,6 +6,7 @@
 Outputs (git-ignored, shipped with the tree to GPU machines):
     turbotransformers_b200/libttb.so                          C ABI + CUDA kernels (include/ttb.h)
     turbotransformers_b200/turbo_transformers_cxx*.so         C++ layer classes + pybind11 surface
+    turbotransformers_b200/bert_model_example                 command-line host of the C++ API (npz model, no Python)
 """
 import argparse
 import glob
@@ -90,7 +91,7 @@ def build_cxx_module(force=False, verbose=False):
     import pybind11
     cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall", "-I", os.path.join(ROOT, "include"),
            "-I", host, "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"], *srcs,
-           "-L", PKG, "-l:libttb.so", "-Wl,-rpath,$ORIGIN", "-o", out]
+           "-L", PKG, "-l:libttb.so", "-lz", "-Wl,-rpath,$ORIGIN", "-o", out]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or r.returncode != 0:
         print(r.stdout, r.stderr)
@@ -99,10 +100,32 @@ def build_cxx_module(force=False, verbose=False):
     return out
 
 
+EXAMPLE = os.path.join(PKG, "bert_model_example")
+
+
+def build_example(force=False, verbose=False):
+    """The Python-free command-line host: C++ layer classes + npz loader + BertModel, no pybind, no libpython."""
+    host = os.path.join(CSRC, "host")
+    srcs = [s for s in sorted(glob.glob(os.path.join(host, "*.cpp"))) if os.path.basename(s) != "pybind.cpp"]
+    srcs += sorted(glob.glob(os.path.join(CSRC, "example", "*.cpp")))
+    deps = srcs + glob.glob(os.path.join(host, "*.h")) + glob.glob(os.path.join(ROOT, "include", "*.h"))
+    if not force and not _newer(EXAMPLE, deps):
+        return EXAMPLE
+    cmd = ["g++", "-O2", "-std=c++17", "-Wall", "-pthread", "-I", os.path.join(ROOT, "include"), "-I", host, *srcs,
+           "-L", PKG, "-l:libttb.so", "-lz", "-Wl,-rpath,$ORIGIN", "-o", EXAMPLE]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or r.returncode != 0:
+        print(r.stdout, r.stderr)
+    if r.returncode != 0:
+        raise RuntimeError("building bert_model_example failed")
+    return EXAMPLE
+
+
 def build_all(force=False, verbose=False):
     lib = build_libttb(force, verbose)
     mod = build_cxx_module(force, verbose)
-    return lib, mod
+    exe = build_example(force, verbose)
+    return lib, mod, exe
 
 
 if __name__ == "__main__":

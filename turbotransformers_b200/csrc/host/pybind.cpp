@@ -8,7 +8,9 @@
 
 #include <cstring>
 
+#include "bert_model.h"
 #include "layers.h"
+#include "npz.h"
 
 namespace py = pybind11;
 using namespace turbo_transformers;
@@ -194,6 +196,34 @@ PYBIND11_MODULE(turbo_transformers_cxx, m) {
   py::class_<layers::BertPooler>(m, "BertPooler")
       .def(py::init([](Tensor& w, Tensor& b) { return new layers::BertPooler(std::move(w), std::move(b)); }))
       .def("__call__", &layers::BertPooler::operator());
+
+  // ---- the Python-free model of the C++ API (example/cpp/bert_model.cpp of the reference), reachable from Python for tests
+  m.def("npz_load", [](const std::string& filename) {
+    py::dict d;
+    for (auto& kv : loaders::npz_load(filename)) {
+      d[py::str(kv.first)] = py::make_tuple(kv.second.descr, kv.second.shape,
+                                            py::bytes(reinterpret_cast<const char*>(kv.second.bytes.data()), kv.second.bytes.size()));
+    }
+    return d;
+  }, "Read an .npz archive with the C++ reader: {name: (dtype string, shape, raw bytes)}.");
+  py::class_<BertModel>(m, "NpzBertModel")
+      .def(py::init([](const std::string& filename, size_t n_layers, int64_t n_heads, const std::string& dtype, int device_id) {
+             return new BertModel(filename, kDLCUDA, n_layers, n_heads, dtype, device_id);
+           }),
+           py::arg("filename"), py::arg("n_layers"), py::arg("n_heads"), py::arg("dtype") = "float32", py::arg("device_id") = 0)
+      .def("__call__",
+           [](const BertModel& self, const std::vector<std::vector<int64_t>>& inputs, const std::vector<std::vector<int64_t>>& position_ids,
+              const std::vector<std::vector<int64_t>>& segment_ids, const std::string& pooling, bool use_pooler) {
+             PoolType p = PoolType::kFirst;
+             if (pooling == "Max") p = PoolType::kMax;
+             else if (pooling == "Mean") p = PoolType::kMean;
+             else if (pooling == "Last") p = PoolType::kLast;
+             else if (pooling != "First") TT_THROW("The input pool type (%s) is not supported.", pooling.c_str());
+             return self(inputs, position_ids, segment_ids, p, use_pooler);
+           },
+           py::arg("inputs"), py::arg("position_ids") = std::vector<std::vector<int64_t>>(),
+           py::arg("segment_ids") = std::vector<std::vector<int64_t>>(), py::arg("pooling") = "First", py::arg("use_pooler") = false)
+      .def_property_readonly("hidden_size", &BertModel::hidden_size);
 
   py::class_<layers::PrepareBertMasks>(m, "PrepareBertMasks").def(py::init()).def("__call__", &layers::PrepareBertMasks::operator());
 
