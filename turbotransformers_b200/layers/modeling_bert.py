@@ -268,6 +268,7 @@ class BertModelNoPooler:
                  output_hidden_states: Optional[bool] = None, pooling_type: PoolingType = PoolingType.FIRST,
                  return_type: Optional[ReturnType] = None):
         use_current_stream(inputs if isinstance(inputs, torch.Tensor) else None)
+        no_mask = attention_masks is None
         attention_masks = try_convert(create_empty_if_none(attention_masks))
         token_type_ids = try_convert(create_empty_if_none(token_type_ids))
         position_ids = try_convert(create_empty_if_none(position_ids))
@@ -276,6 +277,10 @@ class BertModelNoPooler:
         self.prepare(inputs, attention_masks, token_type_ids, position_ids, extended_attention_masks)
         hidden_cache = self.embeddings(inputs, position_ids=position_ids, token_type_ids=token_type_ids,
                                        return_type=ReturnType.turbo_transformers)
+        # Without a caller mask the additive mask is all zeros: 16-bit models then run the mask-free attention kernel
+        # (fp32 models keep the reference's sequence, mask included).
+        if no_mask and hidden_cache.dtype() in ("float16", "bfloat16"):
+            extended_attention_masks = None
         return self.encoder(hidden_states=hidden_cache, attention_mask=extended_attention_masks,
                             output_attentions=output_attentions, output_hidden_states=output_hidden_states,
                             return_type=return_type)

@@ -5,6 +5,7 @@
     python -m turbotransformers_b200.model_bench --config c3     # BERT-base int8, batch {1,16,64}, seq 128
     python -m turbotransformers_b200.model_bench --config c4     # BERT-large fp16, 32 sequences of 512 (one GPU's shard of 256)
     python -m turbotransformers_b200.model_bench --config c5     # GPT-2 small fp16, b8 s1024, logits
+    python -m turbotransformers_b200.model_bench --config cpp [--devices N]   # the Python-free C++ host on the headline batch
 
 One JSON line per point: sequences/s, ms per forward (mean and p50 over CUDA-event-timed iterations, inputs resident on
 the device), and the algorithmic TFLOP/s (padding never counts; causal attention counts the lower triangle only).
@@ -46,14 +47,44 @@ def report(name, batch, seq, flops_per_seq, mean_ms, p50_ms, **extra):
                       "tflops": round(batch * flops_per_seq / (mean_ms / 1e3) / 1e12, 1), **extra}), flush=True)
 
 
+def cpp_host(a):
+    """BERT-base fp16 on the headline batch (64 requests U[8,512]) through `bert_model_example`: archive from disk, ids from
+    a text file, one model and one host thread per device; every batch uploads its ids and downloads its pooled output."""
+    import os
+    import re
+    import subprocess
+    import tempfile
+
+    from . import build
+    from .tools.convert_huggingface_bert_pytorch_to_npz import save_bert_npz
+    hf = synthetic.make_hf_bert("bert-base", 0)
+    lens = synthetic.varlen_lengths(64, 8, 512, 0)
+    ids = synthetic.varlen_ids(lens, hf.config.vocab_size, 0)
+    with tempfile.TemporaryDirectory() as d:
+        npz, txt = os.path.join(d, "bert_base.npz"), os.path.join(d, "ids.txt")
+        save_bert_npz(hf, npz, compressed=False)
+        with open(txt, "w") as f:
+            f.write("\n".join(" ".join(str(int(v)) for v in r) for r in ids) + "\n")
+        r = subprocess.run([build.build_example(), npz, "12", "12", "--dtype", "float16", "--ids", txt, "--devices", str(a.devices),
+                            "--requests", str(max(a.iters, 20))], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(r.stderr)
+    m = re.search(r"([0-9.]+) sequences/s \(([0-9.]+) ms per batch per device\)", r.stdout)
+    print(json.dumps({"config": "bert-base fp16, 64 requests U[8,512], C++ host (npz archive, no Python), pooled output to the host",
+                      "devices": a.devices, "sequences_per_s": float(m.group(1)), "ms_per_batch_per_device": float(m.group(2))}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", required=True, choices=["c1", "sweep", "c3", "c4", "c5"])
+    ap.add_argument("--config", required=True, choices=["c1", "sweep", "c3", "c4", "c5", "cpp"])
+    ap.add_argument("--devices", type=int, default=1, help="cpp: GPUs the serving loop drives (one host thread each)")
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     a = ap.parse_args()
     torch.set_grad_enabled(False)
     dev = torch.device("cuda:0")
+    if a.config == "cpp":
+        return cpp_host(a)
     if a.config in ("c1", "sweep", "c3"):
         hf = synthetic.make_hf_bert("bert-base", 0)
         V = hf.config.vocab_size
