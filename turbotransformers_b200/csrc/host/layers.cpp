@@ -392,6 +392,53 @@ void BertOutput::operator()(const Tensor& hidden_states, const Tensor& input_ten
   }
 }
 
+namespace {
+// out = LN(residual + act_in . W2 + b2) with W2's bias and the residual in the GEMM epilogue (16-bit) or in the
+// AddBiasLayerNorm kernel (fp32, the reference's sequence).
+void ProjectAddNorm(const PackedLinear& dense, const Tensor& act_in, const Tensor& residual, const Tensor& gamma, const Tensor& beta,
+                    bool is_trans, Tensor* out, const char* name) {
+  const int dt = FloatType(act_in, name);
+  const int64_t M = act_in.rows(), N = dense.out_dim(is_trans);
+  TT_ENFORCE_EQ(residual.numel(), M * N, "%s: residual shape mismatch", name);
+  ttb_ctx* c = DeviceContext(act_in.device_id());
+  out->Reshape(act_in.dtype(), ShapeOf(residual), kDLCUDA, act_in.device_id(), name);
+  if (dt == TTB_F32) {
+    dense.Forward(act_in, M, TTB_EPI_NONE, nullptr, out->raw_mut(), is_trans, name);
+    Check(ttb_add_bias_layernorm(c, dt, out->raw_mut(), residual.raw(), dense.bias().raw(), gamma.raw(), beta.raw(), M, N, 1e-12f), c, name);
+  } else {
+    dense.Forward(act_in, M, TTB_EPI_BIAS_RESIDUAL, residual.raw(), out->raw_mut(), is_trans, name);
+    Check(ttb_layernorm(c, dt, out->raw(), out->raw_mut(), gamma.raw(), beta.raw(), M, N, 1e-12f), c, name);
+  }
+}
+}  // namespace
+
+void DistrillFFN::operator()(const Tensor& x, Tensor* output, bool is_trans_weight) const {
+  TT_ENFORCE(output, "The output tensor should not be nullptr.");
+  FloatType(x, "DistrillFFN input");
+  SameTypeDevice(x, dense1_.weight(), "DistrillFFN");
+  TT_ENFORCE_EQ(dense1_.in_dim(is_trans_weight), x.shape(-1), "dense weight and input tensor should have the same model_dim.");
+  Tensor inter(nullptr);
+  inter.Reshape(x.dtype(), {x.rows(), dense1_.out_dim(is_trans_weight)}, kDLCUDA, x.device_id(), "FFN/gemm0/Reshape");
+  dense1_.Forward(x, x.rows(), TTB_EPI_BIAS_GELU, nullptr, inter.raw_mut(), is_trans_weight, "FFN/gemm0");
+  ProjectAddNorm(dense2_, inter, x, layer_norm_weight_, layer_norm_bias_, is_trans_weight, output, "FFN/gemm1");
+}
+
+void AlbertLayer::EnforceShapeAndType() const {
+  TT_ENFORCE_EQ(dense_.weight().n_dim(), 2, "dense weight must be matrix");
+  TT_ENFORCE_EQ(dense_.bias().n_dim(), 1, "dense bias must be vector");
+  TT_ENFORCE_EQ(dense_.weight().shape(1), dense_.bias().shape(0), "weight and bias shape mismatch");
+  TT_ENFORCE_EQ(dense_output_.weight().shape(0), dense_.weight().shape(1), "the two dense layers do not chain");
+}
+
+void AlbertLayer::operator()(const Tensor& x, Tensor* hidden_output, Tensor* output) const {
+  TT_ENFORCE(hidden_output && output, "The output tensors should not be nullptr.");
+  FloatType(x, "AlbertLayer input");
+  SameTypeDevice(x, dense_.weight(), "AlbertLayer");
+  hidden_output->Reshape(x.dtype(), WithLast(x, dense_.out_dim(false)), kDLCUDA, x.device_id(), "AlbertLayer/Reshape");
+  dense_.Forward(x, x.rows(), TTB_EPI_BIAS_GELU, nullptr, hidden_output->raw_mut(), false, "AlbertLayer/gemm0");
+  ProjectAddNorm(dense_output_, *hidden_output, x, layer_norm_weight_, layer_norm_bias_, false, output, "AlbertLayer/gemm1");
+}
+
 void BertPooler::EnforceShapeAndType() const {
   TT_ENFORCE_EQ(dense_.weight().n_dim(), 2, "dense weight must be matrix");
   TT_ENFORCE_EQ(dense_.bias().n_dim(), 1, "dense bias must be vector");

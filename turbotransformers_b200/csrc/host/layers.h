@@ -212,6 +212,39 @@ class PositionwiseFeedForward {
   float eps_ = 1e-12f;
 };
 
+// Post-LN feed-forward block of DistilBERT (positionwise_ffn.cpp:79-123): out = LN(x + W2 gelu(W1 x + b1) + b2), eps 1e-12.
+// The same two fused GEMMs and LayerNorm as BertIntermediate + BertOutput.
+class DistrillFFN {
+ public:
+  DistrillFFN(core::Tensor dense_weight_1, core::Tensor dense_bias_1, core::Tensor dense_weight_2, core::Tensor dense_bias_2,
+              core::Tensor layer_norm_weight, core::Tensor layer_norm_bias)
+      : dense1_(std::move(dense_weight_1), std::move(dense_bias_1)), dense2_(std::move(dense_weight_2), std::move(dense_bias_2)),
+        layer_norm_weight_(std::move(layer_norm_weight)), layer_norm_bias_(std::move(layer_norm_bias)) {}
+  void operator()(const core::Tensor& input_tensor, core::Tensor* output, bool is_trans_weight = true) const;
+
+ private:
+  PackedLinear dense1_, dense2_;
+  core::Tensor layer_norm_weight_, layer_norm_bias_;
+};
+
+// Feed-forward half of an ALBERT layer (albert_layer.cpp:31-50): hidden_output = gelu(x W1 + b1),
+// output = LN(x + hidden_output W2 + b2). Weights are [in, out].
+class AlbertLayer {
+ public:
+  AlbertLayer(core::Tensor dense_weight, core::Tensor dense_bias, core::Tensor dense_output_weight, core::Tensor dense_output_bias,
+              core::Tensor layer_norm_weight, core::Tensor layer_norm_bias)
+      : dense_(std::move(dense_weight), std::move(dense_bias)), dense_output_(std::move(dense_output_weight), std::move(dense_output_bias)),
+        layer_norm_weight_(std::move(layer_norm_weight)), layer_norm_bias_(std::move(layer_norm_bias)) {
+    EnforceShapeAndType();
+  }
+  void EnforceShapeAndType() const;
+  void operator()(const core::Tensor& input_tensor, core::Tensor* hidden_output, core::Tensor* output) const;
+
+ private:
+  PackedLinear dense_, dense_output_;
+  core::Tensor layer_norm_weight_, layer_norm_bias_;
+};
+
 // In-place bias + tanh-GELU on a projection computed elsewhere (layers/addbias_act.cpp:20-23).
 class FusedAddBiasGELU {
  public:

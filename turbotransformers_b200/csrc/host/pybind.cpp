@@ -227,6 +227,18 @@ PYBIND11_MODULE(turbo_transformers_cxx, m) {
 
   py::class_<layers::PrepareBertMasks>(m, "PrepareBertMasks").def(py::init()).def("__call__", &layers::PrepareBertMasks::operator());
 
+  py::class_<layers::DistrillFFN>(m, "DistrillFFN")
+      .def(py::init([](Tensor& w1, Tensor& b1, Tensor& w2, Tensor& b2, Tensor& ln_w, Tensor& ln_b) {
+        return new layers::DistrillFFN(std::move(w1), std::move(b1), std::move(w2), std::move(b2), std::move(ln_w), std::move(ln_b));
+      }))
+      .def("__call__", &layers::DistrillFFN::operator(), py::arg("input_tensor"), py::arg("output"), py::arg("is_trans_weight") = true);
+
+  py::class_<layers::AlbertLayer>(m, "AlbertLayer")
+      .def(py::init([](Tensor& w1, Tensor& b1, Tensor& w2, Tensor& b2, Tensor& ln_w, Tensor& ln_b) {
+        return new layers::AlbertLayer(std::move(w1), std::move(b1), std::move(w2), std::move(b2), std::move(ln_w), std::move(ln_b));
+      }))
+      .def("__call__", &layers::AlbertLayer::operator());
+
   py::class_<layers::PositionwiseFeedForward>(m, "PositionwiseFeedForward")
       .def(py::init([](Tensor& w1, Tensor& b1, Tensor& w2, Tensor& b2, Tensor& ln_w, Tensor& ln_b) {
         return new layers::PositionwiseFeedForward(std::move(w1), std::move(b1), std::move(w2), std::move(b2), std::move(ln_w),
