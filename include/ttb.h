@@ -219,6 +219,20 @@ int ttb_attention_fwd(ttb_ctx* ctx, int dtype, const void* qkv, int64_t total_to
                       int64_t max_seqlen, int64_t heads, int64_t d, const float* mask,
                       int64_t mask_batch_stride, int64_t mask_row_stride, int causal, float scale, void* out);
 
+/* Decoder step with a key/value cache: replaces the per-step Concat of the whole cache and the padded attention sequence
+ * of `layer_cache` self-attention (multi_headed_attention.cpp:207-231, 320-354; Concat: kernels/utils.cpp:32-97).
+ *   qkv      : [B * n_new, 3*heads*d], row b*n_new + t, columns q|k|v (bias already added), dtype F16/BF16, d == 64
+ *   k_cache, v_cache : paged [pages, B, 16, heads*d]: token j of sequence b is row (j / 16, b, j % 16); tokens [0, past_len)
+ *              are cached so far. Appending is in place and growth adds pages at the end.
+ * ttb_kv_cache_append files the new keys/values as tokens [past_len, past_len + n_new) (after a prompt that went through
+ * ttb_attention_fwd). ttb_attention_decode does the same append and then attends: query t sees tokens [0, past_len + t].
+ * n_new <= 64 there; out is [B * n_new, heads*d]. Capacity is the caller's business: pages up to token past_len + n_new - 1
+ * are written (ceil((past_len + n_new) / 16) pages). */
+int ttb_kv_cache_append(ttb_ctx* ctx, int dtype, const void* qkv, int64_t B, int64_t n_new, int64_t heads, int64_t d,
+                        void* k_cache, void* v_cache, int64_t past_len);
+int ttb_attention_decode(ttb_ctx* ctx, int dtype, const void* qkv, int64_t B, int64_t n_new, int64_t heads, int64_t d,
+                         void* k_cache, void* v_cache, int64_t past_len, float scale, void* out);
+
 /* BERTEmbedding::operator() (layers/bert_embedding.cpp:24-65) in one pass: three gathers + LayerNorm.
  * ids is [n_tokens]. token_type_ids may be NULL (all 0). position_ids may be NULL: the position of token t is
  * then t - cu_seqlens[b] for the sequence b that owns it (packed batches, B+1 prefix sums), or t % seq_len

@@ -197,6 +197,12 @@ void* Tensor::Reshape(DLDataType dtype, const std::vector<int64_t>& shape, DLDev
   return raw_mut();
 }
 
+size_t Tensor::capacity_bytes() const {
+  if (is_null()) return 0;
+  if (owned_ && owned_->deleter == ManagedDeleter) return static_cast<Managed*>(owned_->manager_ctx)->capacity;
+  return (size_t)numel() * ElemBytes(view_.dtype);
+}
+
 void Tensor::ViewAs(const std::vector<int64_t>& shape) {
   int64_t n = 1;
   for (int64_t d : shape) n *= d;

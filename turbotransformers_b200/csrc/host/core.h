@@ -106,6 +106,7 @@ class Tensor {
   size_t n_dim() const { return is_null() ? 0 : (size_t)view_.ndim; }
   int64_t shape(int pos) const;  // negative positions count from the end
   int64_t numel() const;
+  size_t capacity_bytes() const;  // bytes of the underlying buffer (>= the bytes of the current shape for tensors made by Reshape)
   int64_t rows() const { return n_dim() ? numel() / shape(-1) : 0; }  // product of all but the last dim
   DLDeviceType device_type() const { return view_.device.device_type; }
   int device_id() const { return view_.device.device_id; }

@@ -199,10 +199,44 @@ void MultiHeadedAttention::operator()(const Tensor& key_tensor, const Tensor& va
     if (attn_type == "context") TT_THROW("context (encoder-decoder) attention is outside the scope of this runtime");
     TT_THROW("attn_type should be context or self.");
   }
-  for (auto& kv : layer_cache)
-    if (kv.second && !kv.second->is_null()) TT_THROW("incremental decoding caches (layer_cache) are outside the scope of this runtime");
-  Run(query_tensor, attention_mask, nullptr, output, att_score, pre_layernorm, post_layernorm, post_add_input, is_trans_weight);
+  // Incremental decoding (multi_headed_attention.cpp:207-231): the reference concatenates the step's keys / values to
+  // layer_cache["self_keys" / "self_values"] ([B, heads, T, d] there). Here the two entries are appended in place: their shape
+  // reads [T, B, H] (T = tokens cached), their buffer is paged and opaque to the caller; an entry that is present but still
+  // empty starts the cache.
+  Tensor *cache_k = nullptr, *cache_v = nullptr;
+  for (auto& kv : layer_cache) {
+    if (kv.first == "self_keys") cache_k = kv.second;
+    else if (kv.first == "self_values") cache_v = kv.second;
+    else if (kv.second && !kv.second->is_null()) TT_THROW("layer_cache entry %s (context attention memory) is outside the scope of this runtime", kv.first.c_str());
+  }
+  TT_ENFORCE((cache_k == nullptr) == (cache_v == nullptr), "layer_cache needs both self_keys and self_values");
+  Run(query_tensor, attention_mask, nullptr, output, att_score, pre_layernorm, post_layernorm, post_add_input, is_trans_weight, cache_k,
+      cache_v);
 }
+
+namespace {
+// Makes a cache hold past + n_new tokens, keeping the first `past`. The tensor's shape is the logical [T, B, H]; its buffer is
+// paged ([pages, B, 16, H], see ttb_attention_decode) and reserved ahead (a Tensor keeps its buffer across Reshape calls while
+// it is large enough), so most steps only change the logical shape; when the reserve runs out the pages move to a buffer
+// twice as long.
+void EnsureCacheRows(Tensor* t, DLDataType dtype, int64_t past, int64_t n_new, int64_t B, int64_t H, int dev) {
+  const std::vector<int64_t> want{past + n_new, B, H};
+  auto pages = [](int64_t tokens) { return (tokens + 15) / 16; };
+  const size_t need = (size_t)(pages(past + n_new) * 16 * B * H) * 2;
+  if (past == 0) {
+    t->Reshape(dtype, {16 * pages(std::max<int64_t>(2 * n_new, n_new + 256)), B, H}, kDLCUDA, dev, "layer_cache/reserve");
+  } else if (t->capacity_bytes() < need) {
+    ttb_ctx* c = DeviceContext(dev);
+    Tensor bigger(nullptr);
+    bigger.Reshape(dtype, {16 * pages(2 * (past + n_new)), B, H}, kDLCUDA, dev, "layer_cache/grow");
+    const size_t old_bytes = (size_t)(pages(past) * 16 * B * H) * 2;
+    Check(ttb_copy_2d(c, bigger.raw_mut(), old_bytes, t->raw(), old_bytes, old_bytes, 1), c, "layer_cache/grow");
+    Check(ttb_ctx_sync(c), c, "layer_cache/grow");  // the old buffer is released when `*t` is overwritten
+    *t = std::move(bigger);
+  }
+  t->Reshape(dtype, want, kDLCUDA, dev, "layer_cache");
+}
+}  // namespace
 
 void MultiHeadedAttentionSmartBatch::operator()(const Tensor& key_tensor, const Tensor& value_tensor, const Tensor& query_tensor,
                                                 const Tensor& attention_mask, const std::string& attn_type, Tensor* output,
@@ -234,7 +268,7 @@ void BertAttention::operator()(const Tensor& input_tensor, const Tensor& attenti
 
 void MultiHeadedAttention::Run(const Tensor& x, const Tensor& attention_mask, const std::vector<int64_t>* seq_lens, Tensor* output,
                                Tensor* att_score, bool pre_layernorm, bool post_layernorm, bool post_add_input,
-                               bool is_trans_weight) const {
+                               bool is_trans_weight, Tensor* cache_keys, Tensor* cache_values) const {
   TT_ENFORCE(output, "The output tensor should not be nullptr.");
   const int dt = FloatType(x, "attention input");
   SameTypeDevice(x, qkv_.weight(), "attention");
@@ -282,11 +316,33 @@ void MultiHeadedAttention::Run(const Tensor& x, const Tensor& attention_mask, co
       if (MaskIs2D(attention_mask)) { mbs = Lk; mrs = 0; }
       else { mrs = Lk; mbs = attention_mask.shape(-2) * Lk; }
     }
-    Check(ttb_attention_fwd(c, dt, qkv.raw(), T, cu, B, maxL, heads, d, mask, mbs, mrs, causal_ ? 1 : 0, scale, context.raw_mut()), c,
-          "attention_fwd");
+    if (cache_keys) {
+      TT_ENFORCE(!seq_lens && !mask, "layer_cache decoding takes equal-length batches without a mask tensor");
+      const int64_t past = cache_keys->is_null() ? 0 : cache_keys->shape(0);
+      TT_ENFORCE(cache_values->is_null() ? past == 0 : cache_values->shape(0) == past, "self_keys and self_values disagree on the cached length");
+      if (past > 0) {
+        TT_ENFORCE(cache_keys->shape(1) == B && cache_keys->shape(2) == H && core::SameType(cache_keys->dtype(), x.dtype()),
+                   "layer_cache does not match this batch ([T, %lld, %lld] expected)", (long long)B, (long long)H);
+      }
+      EnsureCacheRows(cache_keys, x.dtype(), past, maxL, B, H, dev);
+      EnsureCacheRows(cache_values, x.dtype(), past, maxL, B, H, dev);
+      if (past == 0) {  // prompt: regular attention over the new tokens, then file their keys / values
+        Check(ttb_attention_fwd(c, dt, qkv.raw(), T, cu, B, maxL, heads, d, nullptr, 0, 0, causal_ ? 1 : 0, scale, context.raw_mut()), c,
+              "attention_fwd");
+        Check(ttb_kv_cache_append(c, dt, qkv.raw(), B, maxL, heads, d, cache_keys->raw_mut(), cache_values->raw_mut(), 0), c, "kv_cache_append");
+      } else {
+        Check(ttb_attention_decode(c, dt, qkv.raw(), B, maxL, heads, d, cache_keys->raw_mut(), cache_values->raw_mut(), past, scale,
+                                   context.raw_mut()),
+              c, "attention_decode");
+      }
+    } else {
+      Check(ttb_attention_fwd(c, dt, qkv.raw(), T, cu, B, maxL, heads, d, mask, mbs, mrs, causal_ ? 1 : 0, scale, context.raw_mut()), c,
+            "attention_fwd");
+    }
     if (att_score) *att_score = Tensor(nullptr);
   } else {
     // The reference's own sequence (multi_headed_attention.cpp:168-232,320-354), scores materialised.
+    TT_ENFORCE(!cache_keys, "layer_cache decoding is provided for 16-bit models with 64-wide heads");
     TT_ENFORCE(!causal_ || !attention_mask.is_null(), "the unfused path needs an explicit mask tensor for causal attention");
     Tensor qkv(nullptr), q(nullptr), k(nullptr), v(nullptr), ctx_heads(nullptr), scores_local(nullptr);
     qkv.Reshape(x.dtype(), {T, 3 * H}, kDLCUDA, dev, "self/qkv_out1/Reshape");
@@ -544,7 +600,7 @@ void LayerNorm::operator()(const Tensor& input, Tensor* output) const {
   Check(ttb_layernorm(c, dt, input.raw(), output->raw_mut(), gamma_.raw(), beta_.raw(), input.rows(), input.shape(-1), eps_), c, "LayerNorm");
 }
 
-void TokenPositionEmbedding::operator()(const Tensor& input_ids, Tensor* output) const {
+void TokenPositionEmbedding::operator()(const Tensor& input_ids, Tensor* output, int64_t position_offset) const {
   TT_ENFORCE_EQ(input_ids.n_dim(), 2, "The input ids should be a matrix with shape [BatchSize, SeqLen].");
   const int dt = FloatType(token_, "token embeddings");
   TT_ENFORCE(input_ids.on_gpu(), "input ids must be on the GPU");
@@ -557,7 +613,10 @@ void TokenPositionEmbedding::operator()(const Tensor& input_ids, Tensor* output)
   output->Reshape(token_.dtype(), {B, L, H}, kDLCUDA, dev, "TokenPositionEmbedding/Reshape");
   Check(ttb_lookup_embedding(c, dt, output->raw_mut(), token_.raw(), input_ids.data<int64_t>(), B * L, H, token_.shape(0), 0), c,
         "TokenPositionEmbedding/token");
-  Check(ttb_lookup_embedding(c, dt, output->raw_mut(), position_.raw(), pos_ids, B * L, H, position_.shape(0), 1), c,
+  TT_ENFORCE(position_offset >= 0 && position_offset + L <= position_.shape(0), "positions %lld..%lld exceed the %lld the model has",
+             (long long)position_offset, (long long)(position_offset + L - 1), (long long)position_.shape(0));
+  const char* table = static_cast<const char*>(position_.raw()) + (size_t)position_offset * (size_t)H * (dt == TTB_F32 ? 4 : 2);
+  Check(ttb_lookup_embedding(c, dt, output->raw_mut(), table, pos_ids, B * L, H, position_.shape(0) - position_offset, 1), c,
         "TokenPositionEmbedding/position");
 }
 

@@ -92,9 +92,12 @@ class MultiHeadedAttention {
 
   // Shared implementation: seq_lens == nullptr means a [B,L,H] batch of equal lengths, otherwise
   // query_tensor is packed [1,sumL,H].
+  // cache_keys / cache_values (both or neither): the decoder's `layer_cache["self_keys" / "self_values"]`: tensors whose shape
+  // reads [T, B, H] (paged buffers underneath) and that this call grows by the query's tokens (16-bit models, equal-length
+  // batches).
   void Run(const core::Tensor& query_tensor, const core::Tensor& attention_mask, const std::vector<int64_t>* seq_lens,
            core::Tensor* output, core::Tensor* att_score, bool pre_layernorm, bool post_layernorm, bool post_add_input,
-           bool is_trans_weight) const;
+           bool is_trans_weight, core::Tensor* cache_keys = nullptr, core::Tensor* cache_values = nullptr) const;
 
   // 16-bit models skip the [B,heads,L,L] score tensor unless asked: it is the largest HBM round trip of
   // the reference path. fp32 models always materialise it, as the reference does.
@@ -283,7 +286,8 @@ class TokenPositionEmbedding {
  public:
   TokenPositionEmbedding(core::Tensor token_table, core::Tensor position_table)
       : token_(std::move(token_table)), position_(std::move(position_table)) {}
-  void operator()(const core::Tensor& input_ids, core::Tensor* output) const;  // ids [B,L] -> [B,L,H], positions 0..L-1
+  // ids [B,L] -> [B,L,H], positions position_offset .. position_offset+L-1 (the offset is the cached length when decoding)
+  void operator()(const core::Tensor& input_ids, core::Tensor* output, int64_t position_offset = 0) const;
 
  private:
   core::Tensor token_, position_;

@@ -264,7 +264,7 @@ PYBIND11_MODULE(turbo_transformers_cxx, m) {
 
   py::class_<layers::TokenPositionEmbedding>(m, "TokenPositionEmbedding")
       .def(py::init([](Tensor& tok, Tensor& pos) { return new layers::TokenPositionEmbedding(std::move(tok), std::move(pos)); }))
-      .def("__call__", &layers::TokenPositionEmbedding::operator());
+      .def("__call__", &layers::TokenPositionEmbedding::operator(), py::arg("input_ids"), py::arg("output"), py::arg("position_offset") = 0);
 
   py::class_<layers::Linear>(m, "Linear")
       .def(py::init([](Tensor& w, Tensor& b, bool is_trans_weight) { return new layers::Linear(std::move(w), std::move(b), is_trans_weight); }))

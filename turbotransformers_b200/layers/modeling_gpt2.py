@@ -1,4 +1,5 @@
-"""GPT-2 decoder stack (full-sequence forward) built from the same layer classes.
+"""GPT-2 decoder stack built from the same layer classes: full-sequence forward, and incremental decoding over a
+key/value cache (`past`), the decoder's `layer_cache` path of the reference's MultiHeadedAttention.
 
 The reference's GPT2Model wraps onnxruntime only and raises for its own "turbo" backend
 (python/turbo_transformers/layers/modeling_gpt2.py:39-40,57-58). This class composes the block the way the
@@ -29,22 +30,37 @@ class GPT2Model:
         self.backend = backend
         self.dtype = config.torch_dtype_of_weights
 
-    def __call__(self, input_ids: AnyTensor, return_logits: bool = True, return_type: Optional[ReturnType] = None):
-        """input_ids int64 [B, L] on the GPU -> (last_hidden_state [B,L,H], logits [B,L,vocab] or None)."""
+    def new_cache(self):
+        """An empty key/value cache for incremental decoding (16-bit models): one `layer_cache` dict per block. Pass it as `past`
+        with the prompt first, then with each new token (or few tokens); it grows in place."""
+        if self.dtype == torch.float32:
+            raise NotImplementedError("incremental decoding is provided for fp16 / bf16 models")
+        return [{"self_keys": _empty(), "self_values": _empty()} for _ in self.blocks]
+
+    @staticmethod
+    def cached_length(past) -> int:
+        k = past[0]["self_keys"]
+        return 0 if k.is_null() else k.shape(0)
+
+    def __call__(self, input_ids: AnyTensor, return_logits: bool = True, return_type: Optional[ReturnType] = None, past=None):
+        """input_ids int64 [B, L] on the GPU -> (last_hidden_state [B,L,H], logits [B,L,vocab] or None).
+        With `past` (from new_cache()), input_ids are the tokens that follow what the cache already holds."""
         if isinstance(input_ids, torch.Tensor):
             use_current_stream(input_ids)
         ids = try_convert(input_ids)
         x = _empty()
-        self.embedding(ids, x)
+        self.embedding(ids, x, self.cached_length(past) if past is not None else 0)
         mask = _empty()
+        if past is not None and self.dtype == torch.float32:
+            raise NotImplementedError("incremental decoding is provided for fp16 / bf16 models")
         if self.dtype == torch.float32:
             # the exact-precision path applies an explicit additive mask, as the reference's kernels do
             B, L = ids.shape(0), ids.shape(1)
             m = torch.triu(torch.full((L, L), -10000.0, dtype=torch.float32, device="cuda"), 1)
             mask = convert2tt_tensor(m.unsqueeze(0).repeat(B, 1, 1).contiguous())
-        for attn, ffn in self.blocks:
+        for i, (attn, ffn) in enumerate(self.blocks):
             a, probs, y = _empty(), _empty(), _empty()
-            attn(x, x, x, mask, "self", a, probs, {}, True, False, True, False)  # pre-LN, + input
+            attn(x, x, x, mask, "self", a, probs, past[i] if past is not None else {}, True, False, True, False)  # pre-LN, + input
             ffn(a, y, False)
             x = y
         h = _empty()

@@ -4,6 +4,7 @@
     python -m turbotransformers_b200.microbench attention --lens varlen64 | --batch 32 --seq 512 [--heads 12] [--causal]
     python -m turbotransformers_b200.microbench layernorm --m 18424 --n 768
     python -m turbotransformers_b200.microbench gelu      --m 18424 --n 3072
+    python -m turbotransformers_b200.microbench decode    --batch 64 --seq 1024 [--heads 12]   # one-token step over a cache
 
 Each run launches the kernel `--warmup` + `--iters` times on synthetic data, writes a >L2 buffer between timed
 launches, times every launch with CUDA events on the launching stream, and prints one JSON line with the
@@ -59,7 +60,7 @@ def timed(fn, warmup, iters, flush=True):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["linear", "attention", "layernorm", "gelu"])
+    ap.add_argument("op", choices=["linear", "attention", "layernorm", "gelu", "decode"])
     ap.add_argument("--m", type=int, default=18424)
     ap.add_argument("--n", type=int, default=2304)
     ap.add_argument("--k", type=int, default=768)
@@ -129,6 +130,19 @@ def main():
         fl = sum((2.0 * H * L * (L + 1)) if a.causal else (4.0 * H * L * L) for L in lens)
         out.update(sequences=len(lens), tokens=T, heads=a.heads, dtype=a.dtype, causal=a.causal, us=round(mean * 1e3, 2),
                    us_median=round(med * 1e3, 2), tflops=round(fl / mean / 1e9, 1))
+    elif a.op == "decode":
+        tdt, code = DT[a.dtype]
+        B, T, H = a.batch, a.seq, a.heads * 64
+        qkv = torch.randn(B, 3 * H, device="cuda", dtype=tdt)
+        pages = (T + 1 + 15) // 16
+        kc = torch.randn(pages, B, 16, H, device="cuda", dtype=tdt)
+        vc = torch.randn(pages, B, 16, H, device="cuda", dtype=tdt)
+        o = torch.empty(B, H, device="cuda", dtype=tdt)
+        fn = lambda: ctx.call("attention_decode", code, qkv, B, 1, a.heads, 64, kc, vc, T, 0.125, o)
+        mean, med, best = timed(fn, a.warmup, a.iters, not a.no_flush)
+        nbytes = 2.0 * (T + 1) * B * H * qkv.element_size()  # K and V read once
+        out.update(batch=B, cached=T, heads=a.heads, dtype=a.dtype, us=round(mean * 1e3, 2), us_median=round(med * 1e3, 2),
+                   gbs=round(nbytes / mean / 1e6, 1))
     else:
         tdt, code = DT[a.dtype]
         M, N = a.m, a.n
