@@ -5,6 +5,7 @@
     python -m turbotransformers_b200.model_bench --config c3     # BERT-base int8, batch {1,16,64}, seq 128
     python -m turbotransformers_b200.model_bench --config c4     # BERT-large fp16, 32 sequences of 512 (one GPU's shard of 256)
     python -m turbotransformers_b200.model_bench --config c5     # GPT-2 small fp16, b8 s1024, logits
+    python -m turbotransformers_b200.model_bench --config c5gen  # GPT-2 small fp16 generation: 512-token prompt, then token by token
     python -m turbotransformers_b200.model_bench --config cpp [--devices N]   # the Python-free C++ host on the headline batch
 
 One JSON line per point: sequences/s, ms per forward (mean and p50 over CUDA-event-timed iterations, inputs resident on
@@ -76,7 +77,7 @@ def cpp_host(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", required=True, choices=["c1", "sweep", "c3", "c4", "c5", "cpp"])
+    ap.add_argument("--config", required=True, choices=["c1", "sweep", "c3", "c4", "c5", "c5gen", "cpp"])
     ap.add_argument("--devices", type=int, default=1, help="cpp: GPUs the serving loop drives (one host thread each)")
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
@@ -107,6 +108,36 @@ def main():
         ids = synthetic.random_ids(32, 512, hf.config.vocab_size, 0).to(dev)
         mean, p50 = timeit(lambda: model(ids), a.warmup, a.iters)
         report("bert-large fp16 (32 of the 256 sequences: one GPU's shard at 8 GPUs)", 32, 512, enc_flops(24, 1024, 512), mean, p50)
+    elif a.config == "c5gen":
+        hf = synthetic.make_hf_gpt2("gpt2-small", 0)
+        model = tt.GPT2Model.from_torch(hf.to(dev).half(), dev)
+        for B in (8, 64):
+            prompt = synthetic.random_ids(B, 512, hf.config.vocab_size, 0).to(dev)
+            nxt = synthetic.random_ids(B, 1, hf.config.vocab_size, 1).to(dev)
+
+            def prefill():
+                past = model.new_cache()
+                model(prompt, return_logits=False, past=past)
+                return past
+            mean, p50 = timeit(prefill, 2, 10)
+            past = prefill()
+            steps = 128
+
+            def decode():
+                model(nxt, return_logits=True, past=past)
+            for _ in range(5):
+                decode()
+            torch.cuda.synchronize()
+            s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            for _ in range(steps):
+                decode()
+            e0.record()
+            torch.cuda.synchronize()
+            ms_tok = s0.elapsed_time(e0) / steps
+            print(json.dumps({"config": "gpt2-small fp16 generation with a key/value cache", "batch": B, "prompt": 512, "prefill_ms": round(mean, 3),
+                              "decode_ms_per_step": round(ms_tok, 4), "decode_tokens_per_s": round(B / (ms_tok / 1e3), 1),
+                              "cached_tokens_at_end": model.cached_length(past)}), flush=True)
     else:
         hf = synthetic.make_hf_gpt2("gpt2-small", 0)
         model = tt.GPT2Model.from_torch(hf.to(dev).half(), dev)
