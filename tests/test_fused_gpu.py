@@ -315,3 +315,31 @@ def test_attention_kernels_agree_on_repeated_launches_at_benchmark_size(ctx, mon
             first = out.clone()
         assert torch.equal(out, first)  # and bit-identical from launch to launch
 
+
+
+@pytest.mark.parametrize("kernel", ["tensor_memory", "mma_sync"])
+@pytest.mark.parametrize("case", ["empty_sequences", "many_sequences", "long_sequence", "long_causal", "beyond_schedule_tables"])
+def test_attention_edge_batches(ctx, kernel, case, monkeypatch):
+    """Shapes at the edges of the tensor-memory kernel's schedule: zero-length sequences inside a batch, more sequences than its
+    length ranking handles (256) and than its tables hold (512: the dispatcher must fall back), and sequences of many key tiles."""
+    monkeypatch.setenv("TTB_ATTN_TC", "2" if kernel == "tensor_memory" else "0")
+    r = rng(len(case))
+    causal = case == "long_causal"
+    if case == "empty_sequences":
+        lens, heads = [0, 37, 0, 0, 130, 1, 0], 2
+    elif case == "many_sequences":
+        lens, heads = [int(v) for v in r.integers(1, 40, 300)], 1
+    elif case == "beyond_schedule_tables":
+        lens, heads = [int(v) for v in r.integers(1, 12, 600)], 1
+    else:
+        lens, heads = [1500, 700], 1
+    H, T = heads * 64, sum(lens)
+    qkv = rounded(r.standard_normal((T, 3 * H)).astype(np.float32), "f16")
+    want = attention_oracle(qkv, [n for n in lens if n > 0], heads, causal=causal)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32).cuda()
+    out = torch.full((T, H), float("nan"), dtype=torch.float16, device="cuda")
+    ctx.call("attention_fwd", _capi.F16, dev(qkv, "f16"), T, cu, len(lens), max(lens), heads, 64, None, 0, 0, int(causal), 0.125, out)
+    assert ctx.device_status() == _capi.OK
+    got = host(out)
+    assert np.isfinite(got).all()
+    assert maxdiff(got, want) < 4e-3
