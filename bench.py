@@ -373,6 +373,25 @@ def run_ours(args):
             lat.append(s.elapsed_time(e))
         lat.sort()
         line["latency_b1_s128_ms"] = {"p50": round(lat[len(lat) // 2], 4), "p90": round(lat[int(len(lat) * 0.9)], 4)}
+        # the same request through a CUDA-graph replay of the forward pass (one graph launch instead of ~90 kernel launches)
+        try:
+            from turbotransformers_b200.graphs import CapturedForward
+            replay = CapturedForward(lambda ids: fixed(ids), one.clone())
+            for _ in range(10):
+                replay(one)
+            glat = []
+            for _ in range(50):
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                replay(one)
+                e.record()
+                e.synchronize()
+                glat.append(s.elapsed_time(e))
+            glat.sort()
+            line["latency_b1_s128_ms"].update({"graph_replay_p50": round(glat[len(glat) // 2], 4),
+                                               "graph_replay_p90": round(glat[int(len(glat) * 0.9)], 4)})
+        except Exception as ex:  # the eager numbers above stand on their own
+            line["latency_b1_s128_ms"]["graph_replay_error"] = str(ex)[:160]
         if world == 1 and not args.no_cpu_baseline:
             try:
                 r = time_reference_cpu(steps=1, warmup=0, budget_s=20.0)

@@ -77,6 +77,17 @@ int ttb_free(ttb_ctx* ctx, void* device_ptr, const char* name);
 int ttb_pool_stats(ttb_ctx* ctx, size_t* in_use, size_t* high_water, uint64_t* n_allocs);
 /* Caps the bytes the pool may hand out (0 = no cap); a request beyond it returns TTB_ERR_OOM. */
 int ttb_pool_set_limit(ttb_ctx* ctx, size_t bytes);
+/* Arena mode: between ttb_arena_begin and ttb_arena_end every ttb_alloc is served from one buffer reserved up front, at
+ * increasing 256-byte-aligned offsets, without any driver call; ttb_free of such a pointer does nothing, then or later. A
+ * forward pass run this way places every temporary and its outputs at fixed addresses, which is what capturing that pass into
+ * a CUDA graph needs (the graph's kernels keep using the arena at every replay, so outputs are valid until the next replay or
+ * ttb_arena_begin). No reference counterpart: the reference's model-aware allocator (allocator_api.cpp:112-125) served the
+ * same purpose of a driver-call-free forward. ttb_arena_begin re-uses the previous arena when it is large enough.
+ * ttb_bytes_allocated_total: sum of all ttb_alloc sizes so far; its increase over one forward pass sizes the arena. */
+int ttb_arena_begin(ttb_ctx* ctx, size_t bytes);
+int ttb_arena_end(ttb_ctx* ctx, size_t* bytes_used);
+int ttb_arena_release(ttb_ctx* ctx);
+int ttb_bytes_allocated_total(ttb_ctx* ctx, uint64_t* bytes);
 /* Model-aware plan: replaces bert_opt_mem_allocate_api (core/allocator/allocator_api.cpp:112-125,
  * bert_config.cpp:43-94): computes one arena size for a BERT forward of this shape and reserves it in the
  * pool so steady-state forwards make no driver calls. Returns the arena bytes. */

@@ -38,6 +38,10 @@ SIGNATURES = {
     "ttb_memcpy_h2d": (i32, [p, p, p, sz]),
     "ttb_memcpy_d2h": (i32, [p, p, p, sz]),
     "ttb_copy_2d": (i32, [p, p, sz, p, sz, sz, sz]),
+    "ttb_arena_begin": (i32, [p, sz]),
+    "ttb_arena_end": (i32, [p, p]),
+    "ttb_arena_release": (i32, [p]),
+    "ttb_bytes_allocated_total": (i32, [p, p]),
     "ttb_kv_cache_append": (i32, [p, i32, p, i64, i64, i64, i64, p, p, i64]),
     "ttb_attention_decode": (i32, [p, i32, p, i64, i64, i64, i64, p, p, i64, f32, p]),
     "ttb_matmul": (i32, [p, i32, p, i32, p, i32, i64, i64, i64, f32, f32, p]),

@@ -21,7 +21,7 @@ def _load():
 cxx = _load()
 
 # classes the Python layer subclasses: a module built from older sources lacks some of them
-_missing = [n for n in ("BertAttention", "DistrillFFN", "AlbertLayer", "NpzBertModel", "npz_load") if not hasattr(cxx, n)]
+_missing = [n for n in ("BertAttention", "DistrillFFN", "AlbertLayer", "NpzBertModel", "npz_load", "arena_begin") if not hasattr(cxx, n)]
 if _missing:
     raise ImportError("turbo_transformers_cxx was built from older sources (no %s): rebuild with `python %s`"
                       % (", ".join(_missing), os.path.join(_HERE, "build.py")))

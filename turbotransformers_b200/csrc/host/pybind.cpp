@@ -94,6 +94,21 @@ PYBIND11_MODULE(turbo_transformers_cxx, m) {
   m.def("device_status", [](int device) { return ttb_device_status(core::DeviceContext(device)); },
         "Synchronise and return the device-side status word (0 = OK), clearing it.");
   m.def("launch_count", [](int device) { return ttb_launch_count(core::DeviceContext(device)); });
+  m.def("arena_begin", [](int device, size_t bytes) { ttb_ctx* c = core::DeviceContext(device); core::Check(ttb_arena_begin(c, bytes), c, "arena_begin"); },
+        "Serve every allocation from one reserved buffer at fixed offsets until arena_end (for CUDA-graph capture of a forward pass).");
+  m.def("arena_end", [](int device) {
+    ttb_ctx* c = core::DeviceContext(device);
+    size_t used = 0;
+    core::Check(ttb_arena_end(c, &used), c, "arena_end");
+    return used;
+  });
+  m.def("arena_release", [](int device) { ttb_ctx* c = core::DeviceContext(device); core::Check(ttb_arena_release(c), c, "arena_release"); });
+  m.def("bytes_allocated_total", [](int device) {
+    ttb_ctx* c = core::DeviceContext(device);
+    uint64_t b = 0;
+    core::Check(ttb_bytes_allocated_total(c, &b), c, "bytes_allocated_total");
+    return b;
+  });
   m.def("pool_stats", [](int device) {
     size_t in_use = 0, high = 0;
     uint64_t n = 0;

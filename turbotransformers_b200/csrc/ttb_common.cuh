@@ -30,6 +30,11 @@ struct ttb_ctx {
   uint64_t n_allocs = 0;
   std::atomic<uint64_t> launches{0};
   std::unordered_map<void*, size_t> live;
+  // arena mode (ttb_arena_begin / ttb_arena_end): allocations at increasing offsets of one reserved buffer
+  char* arena = nullptr;
+  size_t arena_size = 0, arena_off = 0, arena_peak = 0;
+  bool arena_active = false;
+  uint64_t bytes_allocated_total = 0;  // sum of all ttb_alloc sizes so far
 };
 
 namespace ttb {

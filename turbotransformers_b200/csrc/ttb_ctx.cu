@@ -46,6 +46,7 @@ extern "C" int ttb_ctx_destroy(ttb_ctx* c) {
   cudaStreamSynchronize(c->stream);
   for (auto& kv : c->live) cudaFreeAsync(kv.first, c->stream);
   cudaStreamSynchronize(c->stream);
+  if (c->arena) cudaFree(c->arena);
   if (c->d_status) cudaFree(c->d_status);
   if (c->h_status) cudaFreeHost(c->h_status);
   if (c->owns_pool && c->pool) cudaMemPoolDestroy(c->pool);
@@ -134,6 +135,19 @@ extern "C" int ttb_alloc(ttb_ctx* c, size_t bytes, const char* name, void** out)
   if (bytes == 0) return TTB_OK;
   {
     std::lock_guard<std::mutex> g(c->mu);
+    c->bytes_allocated_total += bytes;
+    if (c->arena_active) {  // fixed placement, no driver call: what a CUDA-graph capture of a forward pass needs
+      const size_t off = (c->arena_off + 255) & ~(size_t)255;
+      if (off + bytes > c->arena_size) {
+        c->last_error = std::string("arena exhausted allocating '") + (name ? name : "") + "'";
+        return TTB_ERR_OOM;
+      }
+      c->arena_off = off + bytes;
+      if (c->arena_off > c->arena_peak) c->arena_peak = c->arena_off;
+      c->n_allocs++;
+      *out = c->arena + off;
+      return TTB_OK;
+    }
     if (c->limit && c->in_use + bytes > c->limit) {
       c->last_error = std::string("pool limit exceeded allocating '") + (name ? name : "") + "'";
       return TTB_ERR_OOM;
@@ -168,6 +182,7 @@ extern "C" int ttb_free(ttb_ctx* c, void* p, const char* /*name*/) {
   if (!p) return TTB_OK;
   {
     std::lock_guard<std::mutex> lk(c->mu);
+    if (c->arena && p >= (void*)c->arena && p < (void*)(c->arena + c->arena_size)) return TTB_OK;  // arena memory is not recycled
     auto it = c->live.find(p);
     if (it == c->live.end()) {
       c->last_error = "ttb_free: pointer was not allocated by this context";
@@ -178,6 +193,62 @@ extern "C" int ttb_free(ttb_ctx* c, void* p, const char* /*name*/) {
   }
   DeviceGuard g(c->device);
   TTB_CUDA(c, cudaFreeAsync(p, c->stream));
+  return TTB_OK;
+}
+
+extern "C" int ttb_arena_begin(ttb_ctx* c, size_t bytes) {
+  if (!c) return TTB_ERR_INVALID;
+  TTB_REQUIRE(c, bytes > 0, "arena_begin: zero size");
+  TTB_REQUIRE(c, !c->arena_active, "arena_begin: an arena is already active");
+  DeviceGuard g(c->device);
+  if (c->arena && c->arena_size < bytes) {
+    TTB_CUDA(c, cudaStreamSynchronize(c->stream));
+    TTB_CUDA(c, cudaFree(c->arena));
+    c->arena = nullptr;
+    c->arena_size = 0;
+  }
+  if (!c->arena) {
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(c, e == cudaErrorMemoryAllocation ? TTB_ERR_OOM : TTB_ERR_CUDA, "reserving an arena of %zu bytes: %s", bytes, cudaGetErrorString(e));
+    }
+    c->arena = static_cast<char*>(p);
+    c->arena_size = bytes;
+  }
+  std::lock_guard<std::mutex> lk(c->mu);
+  c->arena_off = 0;
+  c->arena_peak = 0;
+  c->arena_active = true;
+  return TTB_OK;
+}
+
+extern "C" int ttb_arena_end(ttb_ctx* c, size_t* bytes_used) {
+  if (!c) return TTB_ERR_INVALID;
+  std::lock_guard<std::mutex> lk(c->mu);
+  if (bytes_used) *bytes_used = c->arena_peak;
+  c->arena_active = false;
+  return TTB_OK;
+}
+
+extern "C" int ttb_arena_release(ttb_ctx* c) {
+  if (!c) return TTB_ERR_INVALID;
+  TTB_REQUIRE(c, !c->arena_active, "arena_release: the arena is active");
+  if (c->arena) {
+    DeviceGuard g(c->device);
+    TTB_CUDA(c, cudaStreamSynchronize(c->stream));
+    TTB_CUDA(c, cudaFree(c->arena));
+    c->arena = nullptr;
+    c->arena_size = 0;
+  }
+  return TTB_OK;
+}
+
+extern "C" int ttb_bytes_allocated_total(ttb_ctx* c, uint64_t* bytes) {
+  if (!c || !bytes) return TTB_ERR_INVALID;
+  std::lock_guard<std::mutex> lk(c->mu);
+  *bytes = c->bytes_allocated_total;
   return TTB_OK;
 }
 
