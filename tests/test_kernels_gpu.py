@@ -44,6 +44,20 @@ def test_matmul_known_answer(ctx):
     assert host(Cc).reshape(-1).tolist() == [20, 26, 44, 58]
 
 
+@pytest.mark.parametrize("m,n,k", [(70, 100, 37), (1000, 1301, 37), (128, 768, 768)])  # 32 x 32 tiles, 64 x 64 tiles, one request
+@pytest.mark.parametrize("a_trans,b_trans", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_matmul_fp32_both_tile_shapes_ragged_sizes(ctx, m, n, k, a_trans, b_trans):
+    r = rng(11)
+    a = r.standard_normal((k, m) if a_trans else (m, k)).astype(np.float32)
+    b = r.standard_normal((n, k) if b_trans else (k, n)).astype(np.float32)
+    want = (a.T if a_trans else a).astype(np.float64) @ (b.T if b_trans else b).astype(np.float64)
+    A, B, Cc = dev(a), dev(b), dev(np.full((m, n), 7.0, np.float32))
+    ctx.call("matmul", _capi.F32, A, a_trans, B, b_trans, m, n, k, 1.0, 0.0, Cc)
+    assert np.abs(host(Cc).astype(np.float64) - want).max() < 2e-6 * k * 4
+    ctx.call("matmul", _capi.F32, A, a_trans, B, b_trans, m, n, k, 0.5, 2.0, Cc)  # alpha and beta
+    assert np.abs(host(Cc).astype(np.float64) - 2.5 * want).max() < 2e-6 * k * 10
+
+
 @pytest.mark.parametrize("dt", DTS)
 def test_batch_matmul_attention_shapes(ctx, dt):
     r = rng(2)
