@@ -15,7 +15,13 @@ against the stand-in headers under ``oracle/shim`` (abseil, loguru, dlpack's old
 ``oracle/blas_shim.cpp`` (replaces core/blas_openblas.cpp, which needs Eigen) and an OpenBLAS shared
 object found in site-packages.  No ``TT_WITH_CUDA``: this is the fp32 OpenMP + cblas_sgemm path.
 
-Usage:  python oracle/build_ref.py [--reference /path/to/reference] [--force]
+``--cuda`` additionally builds the same translation units with ``-DTT_WITH_CUDA`` plus
+core/cuda_device_context.cpp and layers/kernels/gpu_*.cu (nvcc, sm_100a; cub and thrust come with the
+toolkit) against cuBLAS, into ``oracle/_ref/cuda/``: the reference's own fp32 GPU path, used by one GPU
+test as a second checker and as a second timed baseline.  Both modules export the same C++ types, so a
+process may import only one of them.
+
+Usage:  python oracle/build_ref.py [--reference /path/to/reference] [--force] [--cuda]
 """
 import argparse
 import glob
@@ -115,11 +121,92 @@ def build(reference="/root/reference", force=False, verbose=True):
     return out
 
 
+def cuda_module_path():
+    suffix = sysconfig.get_config_var("EXT_SUFFIX")
+    return os.path.join(OUT_DIR, "cuda", MODULE + suffix)
+
+
+def build_cuda(reference="/root/reference", force=False, verbose=True, cuda_home="/usr/local/cuda"):
+    """Build oracle/_ref/cuda/turbo_transformers_cxx*.so (the reference with TT_WITH_CUDA). Returns its path or None."""
+    import shutil
+    import tempfile
+    out = cuda_module_path()
+    if os.path.exists(out) and not force:
+        return out
+    tt = os.path.join(reference, "turbo_transformers")
+    blas, dlpack = find_openblas(), find_dlpack_header()
+    nvcc = os.path.join(cuda_home, "bin", "nvcc")
+    if not os.path.isdir(tt) or blas is None or dlpack is None or not os.path.exists(nvcc):
+        if verbose:
+            print(f"[oracle] cuda build skipped: reference={os.path.isdir(tt)} openblas={blas} dlpack={dlpack} nvcc={os.path.exists(nvcc)}")
+        return out if os.path.exists(out) else None
+    import pybind11
+    import torch
+    os.makedirs(os.path.dirname(out), exist_ok=True)
+
+    def nontest(pattern):
+        return [f for f in sorted(glob.glob(os.path.join(tt, pattern)))
+                if "_test." not in os.path.basename(f) and "catch2" not in f and "benchmark" not in f]
+
+    core = [os.path.join(tt, "core", f + ".cpp") for f in
+            ("enforce", "memory", "tensor", "config", "profiler", "tensor_copy", "cuda_device_context")]
+    core = [c for c in core if os.path.exists(c)]
+    srcs = (core + nontest("core/allocator/*.cpp") + nontest("layers/kernels/*.cpp") + nontest("layers/*.cpp")
+            + nontest("layers/kernels/*.cu") + [os.path.join(HERE, "blas_shim.cpp"), os.path.join(tt, "python", "pybind.cpp")])
+    torch_inc = os.path.join(os.path.dirname(torch.__file__), "include")
+    common = ["-O2", "-std=c++17", "-w", "-DTT_BLAS_USE_OPENBLAS", "-DTT_WITH_CUDA", f'-DORACLE_DLPACK_HEADER="{dlpack}"',
+              "-include", "functional", "-include", "algorithm", "-include", "numeric", "-include", "sstream",
+              "-I", os.path.join(HERE, "shim"), "-I", reference, "-I", torch_inc, "-I", pybind11.get_include(),
+              "-I", sysconfig.get_paths()["include"], "-I", os.path.join(cuda_home, "include")]
+    if verbose:
+        print("[oracle] compiling the reference GPU path:", len(srcs), "translation units")
+    objdir = tempfile.mkdtemp(prefix="ref_cuda_obj_")
+    try:
+        jobs, objs = [], []
+        for i, src in enumerate(srcs):
+            obj = os.path.join(objdir, f"{i}_{os.path.basename(src)}.o")
+            objs.append(obj)
+            if src.endswith(".cu"):
+                cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC,-fopenmp",
+                       "--expt-relaxed-constexpr", *common, "-c", src, "-o", obj]
+            else:
+                cmd = ["g++", "-fPIC", "-fopenmp", "-march=native", *common, "-c", src, "-o", obj]
+            jobs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+        failed = False
+        for src, job in jobs:
+            log, _ = job.communicate()
+            if job.returncode != 0:
+                failed = True
+                if verbose:
+                    print(f"[oracle] {src} failed:\n{log[-3000:]}", file=sys.stderr)
+        if failed:
+            return None
+        link = ["g++", "-shared", "-fopenmp", *objs, f"-l:{os.path.basename(blas)}", "-L", os.path.dirname(blas),
+                f"-Wl,-rpath,{os.path.dirname(blas)}", "-L", os.path.join(cuda_home, "lib64"),
+                f"-Wl,-rpath,{os.path.join(cuda_home, 'lib64')}", "-lcublas", "-lcudart", "-o", out]
+        r = subprocess.run(link, capture_output=True, text=True)
+        if r.returncode != 0:
+            if verbose:
+                print(r.stderr[-3000:], file=sys.stderr)
+            return None
+    finally:
+        shutil.rmtree(objdir, ignore_errors=True)
+    with open(blas_dir_file(), "w") as f:
+        f.write(os.path.dirname(blas))
+    return out
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
     ap.add_argument("--force", action="store_true")
+    ap.add_argument("--cuda", action="store_true", help="also build the reference's GPU path into oracle/_ref/cuda/")
     a = ap.parse_args()
     p = build(a.reference, a.force)
     print(p if p else "oracle/_ref could not be built")
-    sys.exit(0 if p else 1)
+    ok = bool(p)
+    if a.cuda:
+        q = build_cuda(a.reference, a.force)
+        print(q if q else "oracle/_ref/cuda could not be built")
+        ok = ok and bool(q)
+    sys.exit(0 if ok else 1)

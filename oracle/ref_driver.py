@@ -15,11 +15,30 @@ import torch.utils.dlpack as dlpack
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 _cxx = None
+_device = "cpu"   # where T() puts tensors; "cuda" only after use_cuda_build()
 
 
 def available():
     from . import build_ref
     return os.path.exists(build_ref.module_path())
+
+
+def cuda_build_available():
+    from . import build_ref
+    return os.path.exists(build_ref.cuda_module_path())
+
+
+def use_cuda_build():
+    """Make this process drive the reference's GPU build (oracle/_ref/cuda) with tensors on cuda:0.
+
+    The CPU and GPU builds export the same C++ types, so a process can hold only one of them: call this before
+    anything else here has loaded the CPU build.
+    """
+    global _device
+    if _cxx is not None and _device != "cuda":
+        raise RuntimeError("the reference's CPU build is already loaded in this process")
+    _device = "cuda"
+    return load()
 
 
 def load():
@@ -28,7 +47,10 @@ def load():
     if _cxx is not None:
         return _cxx
     from . import build_ref
-    path = build_ref.build(verbose=False)
+    if _device == "cuda":
+        path = build_ref.build_cuda(verbose=False)
+    else:
+        path = build_ref.build(verbose=False)
     if path is None or not os.path.exists(path):
         raise RuntimeError("oracle/_ref is not built and the reference tree is not available")
     # The OpenBLAS object was linked against a libgfortran that sits beside it but is not on the loader
@@ -55,10 +77,12 @@ def set_num_threads(n):
 
 
 def T(t):
-    """torch CPU tensor (or numpy array) -> reference core::Tensor owning a private copy."""
+    """torch tensor (or numpy array) -> reference core::Tensor owning a private copy on the driver's device."""
     if isinstance(t, np.ndarray):
         t = torch.from_numpy(np.ascontiguousarray(t))
-    return load().Tensor.from_dlpack(dlpack.to_dlpack(t.detach().contiguous().clone()))
+    t = t.detach().contiguous()
+    t = t.clone() if t.device.type == _device else t.to(_device)
+    return load().Tensor.from_dlpack(dlpack.to_dlpack(t))
 
 
 def back(t):
@@ -161,10 +185,14 @@ class RefBert:
         mask = torch.zeros(len(lens), 1, max(lens))
         for b, n in enumerate(lens):
             mask[b, 0, n:] = -1e9
-        h = T(x)
+        return self.smart_batch_layers(x, mask, lens, n_layers)
+
+    def smart_batch_layers(self, x, mask, lens, n_layers=None):
+        """The encoder stack over an already embedded, packed batch x [1,sumL,H] with its additive mask [B,1,maxL]."""
+        h, m = T(x), T(mask)
         for sb, inter, out in self.sb_layers[:n_layers]:
             ao, ap, io, ho = E(), E(), E(), E()
-            sb(h, h, h, T(mask), "self", ao, ap, {}, lens, [], False, True, False, False)
+            sb(h, h, h, m, "self", ao, ap, {}, lens, [], False, True, False, False)
             inter(ao, io)
             out(io, ao, ho)
             h = ho

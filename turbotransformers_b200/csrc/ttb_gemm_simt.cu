@@ -2,11 +2,15 @@
 // primitive MatMul / BatchMatMul entry points. The tensor-core GEMM lives in ttb_gemm_tc.cu.
 #include "ttb_common.cuh"
 
+#include <cstdint>
+#include <type_traits>
+
 using namespace ttb;
 
 namespace {
 
-// Tile shapes (256 threads each): 64 x 64 x 16 with 4 x 4 outputs per thread; 32 x 32 x 64 with 2 x 2 for problems whose
+// Tile shapes (256 threads each): 128 x 128 x 16 with 8 x 8 outputs per thread (gemm_simt_large_kernel below) for problems
+// with at least two waves of such tiles; 64 x 64 x 16 with 4 x 4; 32 x 32 x 64 with 2 x 2 for problems whose
 // 64 x 64 grid would leave most SMs idle (one 128-token request: 24 CTAs), where the long k step keeps 16 loads per thread
 // in flight because there are too few CTAs to hide a load behind another CTA's arithmetic. Every output element sums its k terms in the same order in
 // both, so the two give identical bits.
@@ -15,7 +19,7 @@ namespace {
 // op(A) is M x K: element (m,k) at A[m*K + k] or, transposed storage, A[k*M + m].
 // op(B) is K x N: element (k,n) at B[k*N + n] or, transposed storage, B[n*K + k].
 template <typename T, int BM, int BN, int TM, int TN, int BK>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 gemm_simt_kernel(const T* __restrict__ A, int a_trans, const T* __restrict__ B, int b_trans, T* __restrict__ C, int M,
                  int N, int K, float alpha, float beta, int64_t strideA, int64_t strideB, int64_t strideC) {
   constexpr int kPad = BM == 32 ? 1 : 4;  // odd row pitch: the 32 k values a warp stages for one row land in 32 banks
@@ -29,7 +33,11 @@ gemm_simt_kernel(const T* __restrict__ A, int a_trans, const T* __restrict__ B, 
   const int tid = threadIdx.x;
   static_assert((BM / TM) * (BN / TN) == 256, "256 threads per tile");
   constexpr int EA = BM * BK / 256, EB = BN * BK / 256;  // tile elements per thread
-  const int tx = tid % (BN / TN), ty = tid / (BN / TN);  // thread owns rows ty*TM.., cols tx*TN..
+  const int tx = tid % (BN / TN), ty = tid / (BN / TN);
+  // Rows and columns a thread owns: TM (TN) consecutive ones, or, for 8, two groups of 4 half a tile apart, so that the
+  // 16-byte shared-memory reads of neighbouring threads are contiguous (no bank conflicts).
+  auto row_of = [&](int i) { return TM == 8 ? (i / 4) * (BM / 2) + ty * 4 + (i % 4) : ty * TM + i; };
+  auto col_of = [&](int j) { return TN == 8 ? (j / 4) * (BN / 2) + tx * 4 + (j % 4) : tx * TN + j; };
   float acc[TM][TN];
 #pragma unroll
   for (int i = 0; i < TM; ++i)
@@ -79,9 +87,9 @@ gemm_simt_kernel(const T* __restrict__ A, int a_trans, const T* __restrict__ B, 
     for (int k = 0; k < BK; ++k) {
       float a[TM], b[TN];
 #pragma unroll
-      for (int i = 0; i < TM; ++i) a[i] = As[k][ty * TM + i];
+      for (int i = 0; i < TM; ++i) a[i] = As[k][row_of(i)];
 #pragma unroll
-      for (int j = 0; j < TN; ++j) b[j] = Bs[k][tx * TN + j];
+      for (int j = 0; j < TN; ++j) b[j] = Bs[k][col_of(j)];
 #pragma unroll
       for (int i = 0; i < TM; ++i)
 #pragma unroll
@@ -91,15 +99,171 @@ gemm_simt_kernel(const T* __restrict__ A, int a_trans, const T* __restrict__ B, 
   }
 #pragma unroll
   for (int i = 0; i < TM; ++i) {
-    const int gm = m0 + ty * TM + i;
+    const int gm = m0 + row_of(i);
     if (gm >= M) continue;
 #pragma unroll
     for (int j = 0; j < TN; ++j) {
-      const int gn = n0 + tx * TN + j;
+      const int gn = n0 + col_of(j);
       if (gn >= N) continue;
       float r = alpha * acc[i][j];
       if (beta != 0.f) r += beta * to_f(C[(int64_t)gm * N + gn]);
       C[(int64_t)gm * N + gn] = from_f<T>(r);
+    }
+  }
+}
+
+
+// ---- 128 x 128 x 16 and 64 x 128 x 16 tiles for large and medium problems ---------------------------------------------
+// 256 threads, 8 x 8 outputs per thread as 2 x 2 groups of 4 x 4 half a tile apart (4 x 8 as 1 x 2 groups for the 64-row
+// tile), so a k step is four (three) 16-byte shared-memory reads, contiguous across neighbouring threads, for 64 (32) FMAs. Shared memory is double-buffered (one barrier per
+// k block) and the next k block travels global -> registers while the current one is multiplied. fp32 operands whose rows
+// are 16-byte aligned are fetched as float4; tiles on a ragged edge and other types take checked scalar loads into the
+// same register slots. Every output still sums its k terms in increasing k with one FMA each: same bits as the tiles above.
+constexpr int LBN = 128, LBK = 16;
+
+template <typename T>
+__device__ __forceinline__ float4 fetch4(const T* __restrict__ P, bool vec, bool inside, int r, int k, int R, int K, bool k_major) {
+  // Four consecutive elements of an operand with R rows and K columns. k_major: storage is P[r * K + k] and the four run
+  // along k; otherwise storage is P[k * R + r] and the four run along r.
+  if constexpr (std::is_same<T, float>::value) {
+    if (vec && inside) {
+      const float* q = k_major ? P + (int64_t)r * K + k : P + (int64_t)k * R + r;
+      return *reinterpret_cast<const float4*>(q);
+    }
+  }
+  float v[4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int rr = k_major ? r : r + c, kk = k_major ? k + c : k;
+    v[c] = (rr < R && kk < K) ? to_f(k_major ? P[(int64_t)rr * K + kk] : P[(int64_t)kk * R + rr]) : 0.f;
+  }
+  return make_float4(v[0], v[1], v[2], v[3]);
+}
+
+template <typename T, int LBM>
+__global__ void __launch_bounds__(256, 2)
+gemm_simt_large_kernel(const T* __restrict__ A, int a_trans, const T* __restrict__ B, int b_trans, T* __restrict__ C, int M,
+                       int N, int K, float alpha, float beta, int64_t strideA, int64_t strideB, int64_t strideC, int vec_a,
+                       int vec_b, int vec_c) {
+  static_assert(LBM == 128 || LBM == 64, "row tiles of 128 or 64");
+  constexpr int RG = LBM / 64;       // groups of 4 rows per thread
+  constexpr int TR = 4 * RG;         // rows per thread
+  constexpr int EA = LBM * LBK / 1024;  // float4 slots of the A tile per thread
+  __shared__ __align__(16) float As[2][LBK][LBM + 4];
+  __shared__ __align__(16) float Bs[2][LBK][LBN + 4];
+  const int batch = blockIdx.z;
+  A += batch * strideA;
+  B += batch * strideB;
+  C += batch * strideC;
+  const int m0 = blockIdx.y * LBM, n0 = blockIdx.x * LBN;
+  const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
+  const bool a_kmajor = !a_trans;  // A stored [M, K]
+  const bool b_kmajor = b_trans;   // B stored [N, K]
+  const bool rows_in = m0 + LBM <= M, cols_in = n0 + LBN <= N;
+
+  float acc[TR][8];
+#pragma unroll
+  for (int i = 0; i < TR; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+
+  // Slot e of a thread: f = tid + 256 e. k-major operand: row f / 4, k offset 4 (f % 4), four along k.
+  // Operand stored [K, R] (R = tile rows): k = f / (R / 4), rows 4 (f % (R / 4)) .. +3.
+  float4 ra[EA], rb[2];
+  auto fetch = [&](int k0) {
+    const bool k_in = k0 + LBK <= K;
+#pragma unroll
+    for (int e = 0; e < EA; ++e) {
+      const int f = tid + e * 256;
+      if (a_kmajor) ra[e] = fetch4(A, vec_a, rows_in && k_in, m0 + f / 4, k0 + 4 * (f % 4), M, K, true);
+      else ra[e] = fetch4(A, vec_a, rows_in && k_in, m0 + 4 * (f % (LBM / 4)), k0 + f / (LBM / 4), M, K, false);
+    }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int f = tid + e * 256;
+      if (b_kmajor) rb[e] = fetch4(B, vec_b, cols_in && k_in, n0 + f / 4, k0 + 4 * (f % 4), N, K, true);
+      else rb[e] = fetch4(B, vec_b, cols_in && k_in, n0 + 4 * (f % 32), k0 + f / 32, N, K, false);
+    }
+  };
+  auto stage = [&](int buf) {
+#pragma unroll
+    for (int e = 0; e < EA; ++e) {
+      const int f = tid + e * 256;
+      if (a_kmajor) {
+        const int r = f / 4, k = 4 * (f % 4);
+        As[buf][k][r] = ra[e].x; As[buf][k + 1][r] = ra[e].y; As[buf][k + 2][r] = ra[e].z; As[buf][k + 3][r] = ra[e].w;
+      } else {
+        *reinterpret_cast<float4*>(&As[buf][f / (LBM / 4)][4 * (f % (LBM / 4))]) = ra[e];
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int f = tid + e * 256;
+      if (b_kmajor) {
+        const int r = f / 4, k = 4 * (f % 4);
+        Bs[buf][k][r] = rb[e].x; Bs[buf][k + 1][r] = rb[e].y; Bs[buf][k + 2][r] = rb[e].z; Bs[buf][k + 3][r] = rb[e].w;
+      } else {
+        *reinterpret_cast<float4*>(&Bs[buf][f / 32][4 * (f % 32)]) = rb[e];
+      }
+    }
+  };
+
+  if (K > 0) {
+    fetch(0);
+    stage(0);
+  }
+  __syncthreads();
+  int buf = 0;
+  for (int k0 = 0; k0 < K; k0 += LBK) {
+    const bool more = k0 + LBK < K;
+    if (more) fetch(k0 + LBK);
+#pragma unroll
+    for (int k = 0; k < LBK; ++k) {
+      float a[TR];
+#pragma unroll
+      for (int g = 0; g < RG; ++g) {
+        const float4 v = *reinterpret_cast<const float4*>(&As[buf][k][g * 64 + ty * 4]);
+        a[4 * g] = v.x; a[4 * g + 1] = v.y; a[4 * g + 2] = v.z; a[4 * g + 3] = v.w;
+      }
+      const float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * 4]);
+      const float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][k][64 + tx * 4]);
+      const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+      for (int i = 0; i < TR; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    if (more) stage(buf ^ 1);  // the other buffer was last read before the previous barrier
+    __syncthreads();
+    buf ^= 1;
+  }
+
+#pragma unroll
+  for (int i = 0; i < TR; ++i) {
+    const int gm = m0 + (i / 4) * 64 + ty * 4 + (i % 4);
+    if (gm >= M) continue;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int gn = n0 + h * 64 + tx * 4;
+      T* dst = C + (int64_t)gm * N + gn;
+      if constexpr (std::is_same<T, float>::value) {
+        if (vec_c && gn + 3 < N) {
+          float4 r = make_float4(alpha * acc[i][h * 4], alpha * acc[i][h * 4 + 1], alpha * acc[i][h * 4 + 2], alpha * acc[i][h * 4 + 3]);
+          if (beta != 0.f) {
+            const float4 old = *reinterpret_cast<const float4*>(dst);
+            r.x += beta * old.x; r.y += beta * old.y; r.z += beta * old.z; r.w += beta * old.w;
+          }
+          *reinterpret_cast<float4*>(dst) = r;
+          continue;
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        if (gn + c >= N) continue;
+        float r = alpha * acc[i][h * 4 + c];
+        if (beta != 0.f) r += beta * to_f(dst[c]);
+        dst[c] = from_f<T>(r);
+      }
     }
   }
 }
@@ -113,8 +277,13 @@ int run(ttb_ctx* ctx, int dtype, const void* A, int a_trans, const void* B, int 
   TTB_REQUIRE(ctx, C && (K == 0 || (A && B)), "%s: null pointer", what);
   DeviceGuard g(ctx->device);
   const bool small = ((M + 63) / 64) * ((N + 63) / 64) * batch < 2ll * ctx->sm_count;  // too few 64 x 64 tiles to fill the GPU
-  const int bm = small ? 32 : 64;
-  const int64_t gy = (M + bm - 1) / bm, gx = (N + bm - 1) / bm;
+  // 128 x 128 tiles from two waves of them (two CTAs per SM); 64 x 128 from most of one wave; 64 x 64 below that
+  const int64_t n128 = (N + 127) / 128;
+  const bool wide = N % 128 == 0 || N >= 512;  // a 128-column tile is not mostly padding
+  const bool large = wide && ((M + 127) / 128) * n128 * batch >= 4ll * ctx->sm_count;
+  const bool medium = wide && !large && ((M + 63) / 64) * n128 * batch >= (3ll * ctx->sm_count) / 2;
+  const int bm = small ? 32 : (large ? 128 : 64), bn = small ? 32 : ((large || medium) ? 128 : 64);
+  const int64_t gy = (M + bm - 1) / bm, gx = (N + bn - 1) / bn;
   TTB_REQUIRE(ctx, gy <= 65535, "%s: M too large for this kernel", what);
   for (int64_t b0 = 0; b0 < batch; b0 += 65535) {
     const int nb = (int)(batch - b0 < 65535 ? batch - b0 : 65535);
@@ -124,6 +293,24 @@ int run(ttb_ctx* ctx, int dtype, const void* A, int a_trans, const void* B, int 
                          (gemm_simt_kernel<T, 32, 32, 2, 2, 64><<<grid, 256, 0, ctx->stream>>>((const T*)A + b0 * M * K, a_trans, (const T*)B + b0 * K * N,
                                                                                           b_trans, (T*)C + b0 * M * N, (int)M, (int)N, (int)K,
                                                                                           alpha, beta, M * K, K * N, M * N)));
+    } else if (large || medium) {
+      // float4 access: fp32, 16-byte aligned bases, and every row (and every batch member) starting on a 16-byte boundary
+      auto al16 = [](const void* q) { return reinterpret_cast<uintptr_t>(q) % 16 == 0; };
+      const bool f32 = dtype == TTB_F32;
+      const int vec_a = f32 && al16(A) && (a_trans ? M % 4 == 0 : K % 4 == 0) && (M * K) % 4 == 0;
+      const int vec_b = f32 && al16(B) && (b_trans ? K % 4 == 0 : N % 4 == 0) && (K * N) % 4 == 0;
+      const int vec_c = f32 && al16(C) && N % 4 == 0;
+      if (large) {
+        TTB_DISPATCH_FLOAT(ctx, dtype, T,
+                           (gemm_simt_large_kernel<T, 128><<<grid, 256, 0, ctx->stream>>>((const T*)A + b0 * M * K, a_trans, (const T*)B + b0 * K * N,
+                                                                                         b_trans, (T*)C + b0 * M * N, (int)M, (int)N, (int)K, alpha,
+                                                                                         beta, M * K, K * N, M * N, vec_a, vec_b, vec_c)));
+      } else {
+        TTB_DISPATCH_FLOAT(ctx, dtype, T,
+                           (gemm_simt_large_kernel<T, 64><<<grid, 256, 0, ctx->stream>>>((const T*)A + b0 * M * K, a_trans, (const T*)B + b0 * K * N,
+                                                                                        b_trans, (T*)C + b0 * M * N, (int)M, (int)N, (int)K, alpha,
+                                                                                        beta, M * K, K * N, M * N, vec_a, vec_b, vec_c)));
+      }
     } else {
       TTB_DISPATCH_FLOAT(ctx, dtype, T,
                          (gemm_simt_kernel<T, 64, 64, 4, 4, 16><<<grid, 256, 0, ctx->stream>>>((const T*)A + b0 * M * K, a_trans, (const T*)B + b0 * K * N,
