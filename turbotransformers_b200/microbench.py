@@ -60,7 +60,7 @@ def timed(fn, warmup, iters, flush=True):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["linear", "attention", "layernorm", "gelu", "decode"])
+    ap.add_argument("op", choices=["linear", "matmul", "attention", "layernorm", "gelu", "decode"])
     ap.add_argument("--m", type=int, default=18424)
     ap.add_argument("--n", type=int, default=2304)
     ap.add_argument("--k", type=int, default=768)
@@ -75,6 +75,8 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--burst", type=int, default=0, help="linear/attention: time this many back-to-back launches on rotating buffer sets")
+    ap.add_argument("--b-trans", action="store_true", help="matmul: B is stored [N, K]")
+    ap.add_argument("--yardstick", action="store_true", help="matmul: also time torch.matmul (cuBLAS SGEMM, TF32 off) on the same operands")
     ap.add_argument("--pad-rows", action="store_true", help="linear: output rows padded to a multiple of 8 elements, padding declared scratch")
     a = ap.parse_args()
     ctx = _capi.Context(0)
@@ -111,6 +113,21 @@ def main():
             mean, med, best = timed(fn, a.warmup, a.iters, not a.no_flush)
         out.update(shape=[M, N, K], dtype=a.dtype, epilogue=a.epilogue, us=round(mean * 1e3, 2), us_median=round(med * 1e3, 2),
                    tflops=round(2.0 * M * N * K / mean / 1e9, 1))
+    elif a.op == "matmul":  # the exact fp32 GEMM of the fp32 models: C = A [M,K] x B [K,N] (or B stored [N,K])
+        M, N, K = a.m, a.n, a.k
+        tdt, code = DT[a.dtype]
+        x = torch.randn(M, K, device="cuda", dtype=tdt)
+        w = torch.randn((N, K) if a.b_trans else (K, N), device="cuda", dtype=tdt) * 0.03
+        o = torch.empty(M, N, device="cuda", dtype=tdt)
+        fn = lambda: ctx.call("matmul", code, x, 0, w, int(a.b_trans), M, N, K, 1.0, 0.0, o)
+        mean, med, best = timed(fn, a.warmup, a.iters, not a.no_flush)
+        out.update(shape=[M, N, K], dtype=a.dtype, b_trans=a.b_trans, us=round(mean * 1e3, 2), us_median=round(med * 1e3, 2),
+                   tflops=round(2.0 * M * N * K / mean / 1e9, 1))
+        if a.yardstick:
+            torch.backends.cuda.matmul.allow_tf32 = False
+            wt = w.t() if a.b_trans else w
+            ymean, _, _ = timed(lambda: torch.matmul(x, wt, out=o), a.warmup, a.iters, not a.no_flush)
+            out.update(yardstick_us=round(ymean * 1e3, 2), yardstick_tflops=round(2.0 * M * N * K / ymean / 1e9, 1))
     elif a.op == "attention":
         lens = synthetic.varlen_lengths(64, 8, 512, 0) if a.lens == "varlen64" else [a.seq] * a.batch
         tdt, code = DT[a.dtype]
