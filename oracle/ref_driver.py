@@ -199,6 +199,46 @@ class RefBert:
         return back(h)
 
 
+def context_attention_weights(hidden, seed=0):
+    """Seeded fp32 weights of one attention layer in the layout restate.context_attention takes ([in,out] matrices)."""
+    r = np.random.default_rng(seed)
+    w = {}
+    for n in ("q", "k", "v"):
+        w[n + "_weight"] = (r.standard_normal((hidden, hidden)) * 0.05).astype(np.float32)
+        w[n + "_bias"] = (r.standard_normal(hidden) * 0.02).astype(np.float32)
+    w["dense_weight"] = (r.standard_normal((hidden, hidden)) * 0.05).astype(np.float32)
+    w["dense_bias"] = (r.standard_normal(hidden) * 0.02).astype(np.float32)
+    w["ln_gamma"] = (1.0 + 0.1 * r.standard_normal(hidden)).astype(np.float32)
+    w["ln_beta"] = (0.1 * r.standard_normal(hidden)).astype(np.float32)
+    return w
+
+
+class RefContextAttention:
+    """The reference's MultiHeadedAttention driven with attn_type="context" (multi_headed_attention.cpp:45-167,260-380)."""
+
+    def __init__(self, w, num_heads):
+        cxx = load()
+        qkv_w = np.ascontiguousarray(np.concatenate([w["q_weight"], w["k_weight"], w["v_weight"]], 1))
+        qkv_b = np.concatenate([w["q_bias"], w["k_bias"], w["v_bias"]])
+        self.att = cxx.MultiHeadedAttention(T(w["k_weight"]), T(w["k_bias"]), T(w["v_weight"]), T(w["v_bias"]), T(w["q_weight"]),
+                                            T(w["q_bias"]), T(w["dense_weight"]), T(w["dense_bias"]), T(qkv_w), T(qkv_b),
+                                            T(w["ln_gamma"]), T(w["ln_beta"]), num_heads)
+
+    def __call__(self, query, key, value, mask, memory=None, keep_memory=False, pre_layernorm=False, post_layernorm=False,
+                 post_add_input=False):
+        """-> (output, att_score, (memory_keys, memory_values) or None) as numpy. memory = a pair a previous call returned."""
+        out, score = E(), E()
+        cache = {}
+        if memory is not None:
+            cache = {"memory_keys": T(memory[0]), "memory_values": T(memory[1])}
+        elif keep_memory:
+            cache = {"memory_keys": E(), "memory_values": E()}
+        self.att(T(key), T(value), T(query), T(mask) if mask is not None else E(), "context", out, score, cache, pre_layernorm,
+                 post_layernorm, post_add_input, False)
+        mem = (back(cache["memory_keys"]).cpu().numpy().copy(), back(cache["memory_values"]).cpu().numpy().copy()) if cache else None
+        return back(out).cpu().numpy().copy(), back(score).cpu().numpy().copy(), mem
+
+
 def pack_gpt2_weights(hf_model):
     """HF GPT2Model -> the dict layout oracle/restate.py:gpt2_model takes (Conv1D weights are already [in,out])."""
     def n(p):

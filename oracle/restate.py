@@ -240,6 +240,38 @@ def multi_headed_attention(x, mask, w, num_heads, pre_layernorm=False, post_laye
     return out, prob
 
 
+def context_attention(query, key, value, mask, w, num_heads, memory=None, pre_layernorm=False, post_layernorm=False,
+                      post_add_input=False, pre_ln_eps=1e-6):
+    """Context (encoder-decoder) branch of layers/multi_headed_attention.cpp:45-167,308-380.
+
+    w: q_weight / k_weight / v_weight [H,H] ([in,out]), q_bias / k_bias / v_bias [H], dense_weight, dense_bias, ln_gamma,
+    ln_beta. `memory` = (keys, values) [B,h,Lk,d] as a previous call returned them (layer_cache["memory_keys"/"memory_values"]):
+    given, key / value are not projected again. Returns (output [B,Lq,H], att_score [B,h,Lq,Lk], (keys, values)).
+    """
+    B, Lq, H = query.shape
+    d = H // num_heads
+    q_in = layer_norm(query, w["ln_gamma"], w["ln_beta"], pre_ln_eps) if pre_layernorm else query
+    q = add_bias_transpose_for_score(mat_mul(q_in, False, w["q_weight"], False).reshape(B, Lq, num_heads, d), w["q_bias"])
+    if memory is not None:
+        k, v = memory
+    else:
+        Lk = key.shape[1]
+        k = add_bias_transpose_for_score(mat_mul(key, False, w["k_weight"], False).reshape(B, Lk, num_heads, d), w["k_bias"])
+        v = add_bias_transpose_for_score(mat_mul(value, False, w["v_weight"], False).reshape(B, Lk, num_heads, d), w["v_bias"])
+    score = batch_mat_mul(q, False, k, True, 1.0 / math.sqrt(float(d)))
+    prob = apply_mask_and_softmax(score, mask, 1.0)
+    ctx = transpose_for_score(batch_mat_mul(prob, False, v, False))
+    out = mat_mul(ctx, False, w["dense_weight"], False).reshape(B, Lq, H)
+    if not post_add_input:
+        if not post_layernorm:
+            out = add_bias(out, w["dense_bias"])
+        else:
+            out = add_bias_layer_norm(query, w["dense_bias"], w["ln_gamma"], w["ln_beta"], out, 1e-12)
+    else:
+        out = add_input_bias(out, query, w["dense_bias"])
+    return out, prob, (k, v)
+
+
 def multi_headed_attention_smart_batch(x_packed, seq_list, w, num_heads, mask=None, post_layernorm=True):
     """Self-attention branch of layers/multi_headed_attention_smart_batch.cpp:180-421 on packed [1,sumL,H]."""
     H = x_packed.shape[-1]

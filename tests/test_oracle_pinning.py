@@ -128,6 +128,30 @@ def test_live_reference_agrees_with_restatement():
     assert np.abs(sb - sb2).max() < 1e-5
 
 
+@pytest.mark.skipif(not ref_driver.available(), reason="oracle/_ref is not built on this machine")
+@pytest.mark.parametrize("flags", [(False, False, False), (True, False, True), (False, True, False)])
+def test_live_reference_context_attention_agrees_with_restatement(flags):
+    pre, post, add = flags
+    H, heads, B, Lq, Lk = 64, 4, 2, 5, 9
+    w = ref_driver.context_attention_weights(H, 5)
+    r = np.random.default_rng(6)
+    q = r.standard_normal((B, Lq, H)).astype(np.float32)
+    mem = r.standard_normal((B, Lk, H)).astype(np.float32)
+    mask = np.zeros((B, 1, Lk), np.float32)
+    mask[1, 0, 6:] = -1e18  # the decoder masks the source padding with -1e18
+    ref = ref_driver.RefContextAttention(w, heads)
+    out, score, kept = ref(q, mem, mem, mask, keep_memory=True, pre_layernorm=pre, post_layernorm=post, post_add_input=add)
+    out2, score2, kept2 = restate.context_attention(q, mem, mem, mask, w, heads, None, pre, post, add)
+    assert np.abs(out - out2).max() < 1e-5 and np.abs(score - score2).max() < 1e-6
+    assert np.abs(kept[0] - kept2[0]).max() < 1e-5 and np.abs(kept[1] - kept2[1]).max() < 1e-5
+    # second step: one new query over the kept memory, key / value tensors not consulted
+    q1 = r.standard_normal((B, 1, H)).astype(np.float32)
+    junk = np.zeros((B, Lk, H), np.float32)
+    out_s, _, _ = ref(q1, junk, junk, mask, memory=kept, pre_layernorm=pre, post_layernorm=post, post_add_input=add)
+    out_s2, _, _ = restate.context_attention(q1, None, None, mask, w, heads, kept2, pre, post, add)
+    assert np.abs(out_s - out_s2).max() < 1e-5
+
+
 def test_gpt2_composition_matches_huggingface_fp32():
     hf = synthetic.make_hf_gpt2("gpt2-tiny", 3)
     W = ref_driver.pack_gpt2_weights(hf)

@@ -165,25 +165,31 @@ void BERTEmbedding::Packed(const Tensor& input_ids, const std::vector<int64_t>& 
 // ===================================================================================================
 // MultiHeadedAttention
 // ===================================================================================================
-MultiHeadedAttention::MultiHeadedAttention(Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor dense_weight, Tensor dense_bias,
-                                           Tensor qkv_weight, Tensor qkv_bias, int64_t num_attention_heads)
-    : qkv_(std::move(qkv_weight), std::move(qkv_bias)), dense_(std::move(dense_weight), std::move(dense_bias)),
+MultiHeadedAttention::MultiHeadedAttention(Tensor k_weight, Tensor k_bias, Tensor v_weight, Tensor v_bias, Tensor q_weight,
+                                           Tensor q_bias, Tensor dense_weight, Tensor dense_bias, Tensor qkv_weight, Tensor qkv_bias,
+                                           int64_t num_attention_heads)
+    : k_(std::move(k_weight), std::move(k_bias)), v_(std::move(v_weight), std::move(v_bias)), q_(std::move(q_weight), std::move(q_bias)),
+      qkv_(std::move(qkv_weight), std::move(qkv_bias)), dense_(std::move(dense_weight), std::move(dense_bias)),
       layernorm_gamma_(nullptr), layernorm_beta_(nullptr), num_attention_heads_(num_attention_heads) {
   EnforceShapeAndType();
 }
 
-MultiHeadedAttention::MultiHeadedAttention(Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor dense_weight, Tensor dense_bias,
-                                           Tensor qkv_weight, Tensor qkv_bias, Tensor layernorm_gamma, Tensor layernorm_beta,
-                                           int64_t num_attention_heads)
-    : qkv_(std::move(qkv_weight), std::move(qkv_bias)), dense_(std::move(dense_weight), std::move(dense_bias)),
+MultiHeadedAttention::MultiHeadedAttention(Tensor k_weight, Tensor k_bias, Tensor v_weight, Tensor v_bias, Tensor q_weight,
+                                           Tensor q_bias, Tensor dense_weight, Tensor dense_bias, Tensor qkv_weight, Tensor qkv_bias,
+                                           Tensor layernorm_gamma, Tensor layernorm_beta, int64_t num_attention_heads)
+    : k_(std::move(k_weight), std::move(k_bias)), v_(std::move(v_weight), std::move(v_bias)), q_(std::move(q_weight), std::move(q_bias)),
+      qkv_(std::move(qkv_weight), std::move(qkv_bias)), dense_(std::move(dense_weight), std::move(dense_bias)),
       layernorm_gamma_(std::move(layernorm_gamma)), layernorm_beta_(std::move(layernorm_beta)),
       num_attention_heads_(num_attention_heads) {
   EnforceShapeAndType();
 }
 
 void MultiHeadedAttention::EnforceShapeAndType() const {
-  TT_ENFORCE(!qkv_.weight().is_null() && !qkv_.bias().is_null(), "self attention needs the fused qkv weight and bias");
-  TT_ENFORCE_EQ(qkv_.weight().n_dim(), 2, "qkv weight must be a matrix");
+  const bool has_qkv = !qkv_.weight().is_null() && !qkv_.bias().is_null();
+  const bool has_split = !q_.weight().is_null() && !k_.weight().is_null() && !v_.weight().is_null() && !q_.bias().is_null() &&
+                         !k_.bias().is_null() && !v_.bias().is_null();
+  TT_ENFORCE(has_qkv || has_split, "attention needs the fused qkv weight and bias (self) or separate q, k, v weights and biases (context)");
+  if (has_qkv) TT_ENFORCE_EQ(qkv_.weight().n_dim(), 2, "qkv weight must be a matrix");
   TT_ENFORCE_EQ(dense_.weight().n_dim(), 2, "dense weight must be a matrix");
   TT_ENFORCE(num_attention_heads_ > 0, "number of heads must be positive");
 }
@@ -195,10 +201,20 @@ void MultiHeadedAttention::operator()(const Tensor& key_tensor, const Tensor& va
   TT_ENFORCE_EQ(key_tensor.n_dim(), 3, "The key_tensor should be a matrix with shape [batch_size, key_seq_len, hidden_size].");
   TT_ENFORCE_EQ(value_tensor.n_dim(), 3, "The value_tensor should be a matrix with shape [batch_size, key_seq_len, hidden_size].");
   TT_ENFORCE_EQ(query_tensor.n_dim(), 3, "The query_tensors should be a matrix with shape [batch_size, query_seq_len, hidden_size].");
-  if (attn_type != "self") {
-    if (attn_type == "context") TT_THROW("context (encoder-decoder) attention is outside the scope of this runtime");
-    TT_THROW("attn_type should be context or self.");
+  if (attn_type == "context") {
+    // layer_cache["memory_keys" / "memory_values"]: absent = nothing is kept; present and null = computed by this call and
+    // kept; present and filled = used instead of projecting key_tensor / value_tensor again.
+    Tensor *mem_k = nullptr, *mem_v = nullptr;
+    for (auto& kv : layer_cache) {
+      if (kv.first == "memory_keys") mem_k = kv.second;
+      else if (kv.first == "memory_values") mem_v = kv.second;
+    }
+    TT_ENFORCE((mem_k == nullptr) == (mem_v == nullptr), "layer_cache needs both memory_keys and memory_values");
+    RunContext(key_tensor, value_tensor, query_tensor, attention_mask, output, att_score, mem_k, mem_v, pre_layernorm, post_layernorm,
+               post_add_input, is_trans_weight);
+    return;
   }
+  if (attn_type != "self") TT_THROW("attn_type should be context or self.");
   // Incremental decoding (multi_headed_attention.cpp:207-231): the reference concatenates the step's keys / values to
   // layer_cache["self_keys" / "self_values"] ([B, heads, T, d] there). Here the two entries are appended in place: their shape
   // reads [T, B, H] (T = tokens cached), their buffer is paged and opaque to the caller; an entry that is present but still
@@ -207,7 +223,6 @@ void MultiHeadedAttention::operator()(const Tensor& key_tensor, const Tensor& va
   for (auto& kv : layer_cache) {
     if (kv.first == "self_keys") cache_k = kv.second;
     else if (kv.first == "self_values") cache_v = kv.second;
-    else if (kv.second && !kv.second->is_null()) TT_THROW("layer_cache entry %s (context attention memory) is outside the scope of this runtime", kv.first.c_str());
   }
   TT_ENFORCE((cache_k == nullptr) == (cache_v == nullptr), "layer_cache needs both self_keys and self_values");
   Run(query_tensor, attention_mask, nullptr, output, att_score, pre_layernorm, post_layernorm, post_add_input, is_trans_weight, cache_k,
@@ -270,6 +285,7 @@ void MultiHeadedAttention::Run(const Tensor& x, const Tensor& attention_mask, co
                                Tensor* att_score, bool pre_layernorm, bool post_layernorm, bool post_add_input,
                                bool is_trans_weight, Tensor* cache_keys, Tensor* cache_values) const {
   TT_ENFORCE(output, "The output tensor should not be nullptr.");
+  TT_ENFORCE(!qkv_.weight().is_null(), "self attention needs the fused qkv weight and bias");
   const int dt = FloatType(x, "attention input");
   SameTypeDevice(x, qkv_.weight(), "attention");
   const int dev = x.device_id();
@@ -386,7 +402,16 @@ void MultiHeadedAttention::Run(const Tensor& x, const Tensor& attention_mask, co
   }
 
   // 4) output projection and what follows it
-  output->Reshape(x.dtype(), out_shape, kDLCUDA, dev, "gemm5/Reshape");
+  Finish(context, x, T, output, post_layernorm, post_add_input, is_trans_weight);
+}
+
+void MultiHeadedAttention::Finish(const Tensor& context, const Tensor& x, int64_t T, Tensor* output, bool post_layernorm,
+                                  bool post_add_input, bool is_trans_weight) const {
+  const int dt = FloatType(x, "attention input");
+  const int dev = x.device_id();
+  ttb_ctx* c = DeviceContext(dev);
+  const int64_t H = x.shape(2);
+  output->Reshape(x.dtype(), ShapeOf(x), kDLCUDA, dev, "gemm5/Reshape");
   if (post_add_input) {
     dense_.Forward(context, T, TTB_EPI_BIAS_RESIDUAL, x.raw(), output->raw_mut(), is_trans_weight, "gemm5");
   } else if (!post_layernorm) {
@@ -401,6 +426,102 @@ void MultiHeadedAttention::Run(const Tensor& x, const Tensor& attention_mask, co
     Check(ttb_layernorm(c, dt, output->raw(), output->raw_mut(), layernorm_gamma_.raw(), layernorm_beta_.raw(), T, H, 1e-12f), c,
           "AddBiasLayerNorm");
   }
+}
+
+void MultiHeadedAttention::RunContext(const Tensor& key_tensor, const Tensor& value_tensor, const Tensor& query_tensor,
+                                      const Tensor& attention_mask, Tensor* output, Tensor* att_score, Tensor* memory_keys,
+                                      Tensor* memory_values, bool pre_layernorm, bool post_layernorm, bool post_add_input,
+                                      bool is_trans_weight) const {
+  // The reference's sequence (multi_headed_attention.cpp:45-167, 308-354) on this library's kernels: three separate
+  // projections, AddBiasTransposeForScore into [B, heads, L, d], scores materialised, mask + softmax, weighted values,
+  // transpose back, output projection. The encoder memory's keys / values are projected once per sequence when the caller
+  // passes layer_cache entries, so a decoding step costs one query projection and two small batched products.
+  TT_ENFORCE(output, "The output tensor should not be nullptr.");
+  TT_ENFORCE(!q_.weight().is_null() && !k_.weight().is_null() && !v_.weight().is_null(),
+             "context attention needs the separate q, k, v weights and biases");
+  const Tensor& x = query_tensor;
+  const int dt = FloatType(x, "attention input");
+  SameTypeDevice(x, q_.weight(), "attention");
+  const int dev = x.device_id();
+  ttb_ctx* c = DeviceContext(dev);
+  const int64_t B = x.shape(0), Lq = x.shape(1), H = x.shape(2), heads = num_attention_heads_, d = H / heads, T = B * Lq;
+  TT_ENFORCE_EQ(d * heads, H, "hidden size %lld is not divisible by %lld heads", (long long)H, (long long)heads);
+  TT_ENFORCE_EQ(q_.out_dim(is_trans_weight), H, "q weight does not map hidden -> hidden");
+  if (pre_layernorm || post_layernorm) TT_ENFORCE(!layernorm_gamma_.is_null(), "this attention layer was built without layer norm weights");
+  const float scale = 1.0f / std::sqrt((float)d);
+
+  // 1) queries
+  Tensor normed(nullptr), lin(nullptr), q(nullptr);
+  const Tensor* q_in = &x;
+  if (pre_layernorm) {
+    normed.Reshape(x.dtype(), ShapeOf(x), kDLCUDA, dev, "context/gemm0/q_out2/Reshape");
+    Check(ttb_layernorm(c, dt, x.raw(), normed.raw_mut(), layernorm_gamma_.raw(), layernorm_beta_.raw(), T, H, pre_ln_eps_), c,
+          "context/gemm0/prelayernorm");
+    q_in = &normed;
+  }
+  lin.Reshape(x.dtype(), {T, H}, kDLCUDA, dev, "context/gemm0/q_out1/Reshape");
+  q_.Forward(*q_in, T, TTB_EPI_NONE, nullptr, lin.raw_mut(), is_trans_weight, "context/gemm0");
+  q.Reshape(x.dtype(), {B, heads, Lq, d}, kDLCUDA, dev, "context/AddBiasTransposeForScore/q_out2/Reshape");
+  Check(ttb_add_bias_transpose_for_score(c, dt, lin.raw(), q_.bias().raw(), B, Lq, heads, d, q.raw_mut()), c,
+        "context/AddBiasTransposeForScore");
+
+  // 2) keys / values: from the cache when it is filled, otherwise projected (and filed when a cache entry was passed)
+  Tensor k_local(nullptr), v_local(nullptr);
+  Tensor *k = &k_local, *v = &v_local;
+  const bool memory_filled = memory_keys && !memory_keys->is_null() && !memory_values->is_null();
+  if (memory_filled) {
+    k = memory_keys;
+    v = memory_values;
+    TT_ENFORCE(k->n_dim() == 4 && k->shape(0) == B && k->shape(1) == heads && k->shape(3) == d && core::SameType(k->dtype(), x.dtype()),
+               "layer_cache memory_keys does not match this batch ([%lld, %lld, Lk, %lld] expected)", (long long)B, (long long)heads, (long long)d);
+    TT_ENFORCE(v->n_dim() == 4 && v->shape(0) == B && v->shape(1) == heads && v->shape(2) == k->shape(2) && v->shape(3) == d &&
+                   core::SameType(v->dtype(), x.dtype()),
+               "layer_cache memory_values does not match memory_keys");
+  } else {
+    TT_ENFORCE_EQ(key_tensor.shape(0), B, "key_tensor and query_tensor disagree on the batch size");
+    TT_ENFORCE(key_tensor.shape(1) == value_tensor.shape(1) && key_tensor.shape(2) == H && value_tensor.shape(2) == H &&
+                   value_tensor.shape(0) == B,
+               "key_tensor and value_tensor must both be [batch, key_len, hidden]");
+    SameTypeDevice(key_tensor, k_.weight(), "attention");
+    SameTypeDevice(value_tensor, v_.weight(), "attention");
+    const int64_t Lk = key_tensor.shape(1);
+    if (memory_keys) { k = memory_keys; v = memory_values; }
+    Tensor k_lin(nullptr), v_lin(nullptr);
+    k_lin.Reshape(x.dtype(), {B * Lk, H}, kDLCUDA, dev, "context/gemm2/k_out1/Reshape");
+    v_lin.Reshape(x.dtype(), {B * Lk, H}, kDLCUDA, dev, "context/gemm1/v_out1/Reshape");
+    k_.Forward(key_tensor, B * Lk, TTB_EPI_NONE, nullptr, k_lin.raw_mut(), is_trans_weight, "context/gemm1");
+    v_.Forward(value_tensor, B * Lk, TTB_EPI_NONE, nullptr, v_lin.raw_mut(), is_trans_weight, "context/gemm2");
+    k->Reshape(x.dtype(), {B, heads, Lk, d}, kDLCUDA, dev, "context/keys/AddBiasTransposeForScore/Reshape");
+    v->Reshape(x.dtype(), {B, heads, Lk, d}, kDLCUDA, dev, "context/values/AddBiasTransposeForScore/Reshape");
+    Check(ttb_add_bias_transpose_for_score(c, dt, k_lin.raw(), k_.bias().raw(), B, Lk, heads, d, k->raw_mut()), c,
+          "context/keys/AddBiasTransposeForScore");
+    Check(ttb_add_bias_transpose_for_score(c, dt, v_lin.raw(), v_.bias().raw(), B, Lk, heads, d, v->raw_mut()), c,
+          "context/values/AddBiasTransposeForScore");
+  }
+  const int64_t Lk = k->shape(2);
+
+  // 3) scores, mask + softmax, weighted values
+  Tensor scores_local(nullptr), ctx_heads(nullptr), context(nullptr);
+  Tensor* scores = att_score ? att_score : &scores_local;
+  scores->Reshape(x.dtype(), {B, heads, Lq, Lk}, kDLCUDA, dev, "batch_gemm3/Reshape");
+  Check(ttb_batch_matmul(c, dt, q.raw(), 0, k->raw(), 1, B * heads, Lq, Lk, d, scale, 0.0f, scores->raw_mut()), c, "batch_gemm3");
+  const float* mask = nullptr;
+  int is2d = 1;
+  if (!attention_mask.is_null()) {
+    TT_ENFORCE(attention_mask.on_gpu() && core::SameType(attention_mask.dtype(), core::kFloat32),
+               "the attention mask must be an fp32 tensor on the GPU");
+    TT_ENFORCE_EQ(attention_mask.shape(-1), Lk, "attention mask width must equal the key length");
+    mask = attention_mask.data<float>();
+    is2d = MaskIs2D(attention_mask) ? 1 : 0;
+    if (!is2d) TT_ENFORCE_EQ(attention_mask.shape(-2), Lq, "a [B, Lq, Lk] attention mask must have one row per query");
+  }
+  Check(ttb_mask_softmax(c, dt, scores->raw_mut(), mask, B, heads, Lq, Lk, 1.0f, is2d), c, "ApplyMaskAndSoftmax");
+  ctx_heads.Reshape(x.dtype(), {B, heads, Lq, d}, kDLCUDA, dev, "ApplyMaskAndSoftmax/Reshape");
+  Check(ttb_batch_matmul(c, dt, scores->raw(), 0, v->raw(), 0, B * heads, Lq, d, Lk, 1.0f, 0.0f, ctx_heads.raw_mut()), c, "batch_gemm4");
+  context.Reshape(x.dtype(), {T, H}, kDLCUDA, dev, "batch_gemm4/Reshape");
+  Check(ttb_transpose_for_score(c, dt, ctx_heads.raw(), B, heads, Lq, d, context.raw_mut()), c, "TransposeForScore");
+
+  Finish(context, x, T, output, post_layernorm, post_add_input, is_trans_weight);
 }
 
 // ===================================================================================================

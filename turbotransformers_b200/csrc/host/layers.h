@@ -108,6 +108,18 @@ class MultiHeadedAttention {
   int64_t num_attention_heads() const { return num_attention_heads_; }
 
  private:
+  // attn_type == "context" (encoder-decoder attention, multi_headed_attention.cpp:45-167 of the reference): queries from
+  // query_tensor [B, Lq, H], keys / values from key_tensor / value_tensor [B, Lk, H] or, once computed, from
+  // layer_cache["memory_keys" / "memory_values"] ([B, heads, Lk, d], the reference's layout).
+  void RunContext(const core::Tensor& key_tensor, const core::Tensor& value_tensor, const core::Tensor& query_tensor,
+                  const core::Tensor& attention_mask, core::Tensor* output, core::Tensor* att_score, core::Tensor* memory_keys,
+                  core::Tensor* memory_values, bool pre_layernorm, bool post_layernorm, bool post_add_input,
+                  bool is_trans_weight) const;
+  // Output projection of the token-major attention result [T, H] and what follows it (residual, layer norm).
+  void Finish(const core::Tensor& context, const core::Tensor& x, int64_t T, core::Tensor* output, bool post_layernorm,
+              bool post_add_input, bool is_trans_weight) const;
+
+  PackedLinear k_, v_, q_;  // separate projections: context attention only
   PackedLinear qkv_, dense_;
   core::Tensor layernorm_gamma_, layernorm_beta_;
   int64_t num_attention_heads_;

@@ -1,6 +1,6 @@
 """MultiHeadedAttention and PositionwiseFeedForward with the call signatures of the reference's
-python/turbo_transformers/layers/modules.py:36-243. Only self attention is in scope; the NMT decoder's
-context attention and incremental caches raise."""
+python/turbo_transformers/layers/modules.py:36-243: self attention (with the in-place "self_keys"/"self_values" decoding
+cache for 16-bit models) and context (encoder-decoder) attention with its "memory_keys"/"memory_values" cache."""
 from typing import Optional
 
 import torch
@@ -32,9 +32,42 @@ class MultiHeadedAttention(cxx.MultiHeadedAttention):
         output, attn = create_empty_if_none(output), create_empty_if_none(attn)
         cache = {k: (try_convert(v) if v is not None else _empty()) for k, v in (layer_cache or {}).items()}
         self.set_materialize_scores(bool(output_attentions))
-        super().__call__(key_tensor, value_tensor, query_tensor, mask, attn_type or "self", output, attn, cache, pre_layernorm,
+        attn_type = attn_type or "self"
+        super().__call__(key_tensor, value_tensor, query_tensor, mask, attn_type, output, attn, cache, pre_layernorm,
                          post_layernorm, post_add_input, is_trans_weight)
+        if layer_cache is not None and attn_type == "context":
+            # the projected encoder memory goes back to the caller's dict, as the reference does (modules.py:79-83)
+            for k, v in cache.items():
+                if "memory" in k and not v.is_null():
+                    layer_cache[k] = convert_returns_as_type(v, ReturnType.TORCH)
         return convert_returns_as_type(output, return_type), attn
+
+    @staticmethod
+    def pack_parameter(multi_headed_attn, is_trans_weight: Optional[bool] = False):
+        """The ten weight tensors of an OpenNMT-py style attention module (parameters linear_keys / linear_values /
+        linear_query / final_linear), in the constructor's order (modules.py:90-141 of the reference)."""
+        p = {k: v.detach() for k, v in multi_headed_attn.named_parameters()}
+        if getattr(multi_headed_attn, "max_relative_positions", 0) != 0:
+            raise ValueError("multi_headed_attn's max_relative_positions should be 0!")
+        w = (lambda t: t.contiguous()) if is_trans_weight else (lambda t: torch.t(t).contiguous())
+        qkv_weight = w(torch.cat((p['linear_query.weight'], p['linear_keys.weight'], p['linear_values.weight']), 0))
+        qkv_bias = torch.cat((p['linear_query.bias'], p['linear_keys.bias'], p['linear_values.bias']), 0).contiguous()
+        T = convert2tt_tensor
+        return (T(w(p['linear_keys.weight'])), T(p['linear_keys.bias']), T(w(p['linear_values.weight'])), T(p['linear_values.bias']),
+                T(w(p['linear_query.weight'])), T(p['linear_query.bias']), T(w(p['final_linear.weight'])), T(p['final_linear.bias']),
+                T(qkv_weight), T(qkv_bias))
+
+    @staticmethod
+    def from_onmt(multi_headed_attn, layer_norm=None, is_trans_weight: bool = False):
+        """From an OpenNMT-py style MultiHeadedAttention (any module with linear_keys, linear_values, linear_query,
+        final_linear and head_count), optionally with the block's LayerNorm (modules.py:143-167 of the reference)."""
+        with torch.no_grad():
+            packed = MultiHeadedAttention.pack_parameter(multi_headed_attn, is_trans_weight)
+            if layer_norm is None:
+                return MultiHeadedAttention(*packed, multi_headed_attn.head_count)
+            ln = {k: v.detach() for k, v in layer_norm.named_parameters()}
+            return MultiHeadedAttention(*packed, convert2tt_tensor(ln['weight']), convert2tt_tensor(ln['bias']),
+                                        multi_headed_attn.head_count)
 
     @staticmethod
     def from_torch(attention, layer_norm=None, is_trans_weight: bool = False):
