@@ -239,6 +239,47 @@ class RefContextAttention:
         return back(out).cpu().numpy().copy(), back(score).cpu().numpy().copy(), mem
 
 
+def decoder_layer_weights(hidden, ffn_dim, seed=0):
+    """Seeded fp32 weights of one decoder layer in the layout restate.transformer_decoder_layer takes."""
+    r = np.random.default_rng(seed + 100)
+    ctx = context_attention_weights(hidden, seed)
+    sw = context_attention_weights(hidden, seed + 1)
+    self_w = {"qkv_weight": np.ascontiguousarray(np.concatenate([sw["q_weight"], sw["k_weight"], sw["v_weight"]], 1)),
+              "qkv_bias": np.concatenate([sw["q_bias"], sw["k_bias"], sw["v_bias"]]), "dense_weight": sw["dense_weight"],
+              "dense_bias": sw["dense_bias"], "ln_gamma": sw["ln_gamma"], "ln_beta": sw["ln_beta"], "split": sw}
+    ffn = {"w1_weight": (r.standard_normal((hidden, ffn_dim)) * 0.05).astype(np.float32),
+           "w1_bias": (r.standard_normal(ffn_dim) * 0.02).astype(np.float32),
+           "w2_weight": (r.standard_normal((ffn_dim, hidden)) * 0.05).astype(np.float32),
+           "w2_bias": (r.standard_normal(hidden) * 0.02).astype(np.float32),
+           "ln_gamma": (1.0 + 0.1 * r.standard_normal(hidden)).astype(np.float32),
+           "ln_beta": (0.1 * r.standard_normal(hidden)).astype(np.float32)}
+    return {"self": self_w, "context": ctx, "ffn": ffn}
+
+
+class RefDecoderLayer:
+    """The reference's layer classes composed as python/turbo_transformers/layers/modeling_decoder.py:58-140 composes them."""
+
+    def __init__(self, lw, num_heads):
+        cxx = load()
+        sw = lw["self"]["split"]
+        self.self_attn = cxx.MultiHeadedAttention(T(sw["k_weight"]), T(sw["k_bias"]), T(sw["v_weight"]), T(sw["v_bias"]), T(sw["q_weight"]),
+                                                  T(sw["q_bias"]), T(sw["dense_weight"]), T(sw["dense_bias"]), T(lw["self"]["qkv_weight"]),
+                                                  T(lw["self"]["qkv_bias"]), T(sw["ln_gamma"]), T(sw["ln_beta"]), num_heads)
+        self.context = RefContextAttention(lw["context"], num_heads)
+        f = lw["ffn"]
+        self.ffn = cxx.PositionwiseFeedForward(T(f["w1_weight"]), T(f["w1_bias"]), T(f["w2_weight"]), T(f["w2_bias"]), T(f["ln_gamma"]),
+                                               T(f["ln_beta"]))
+
+    def __call__(self, x, memory_bank, src_mask, dec_mask):
+        query, score = E(), E()
+        xt = T(x)
+        self.self_attn(xt, xt, xt, T(dec_mask) if dec_mask is not None else E(), "self", query, score, {}, True, False, True, False)
+        mid, attn, _ = self.context(back(query).numpy(), memory_bank, memory_bank, src_mask, pre_layernorm=True, post_add_input=True)
+        out = E()
+        self.ffn(T(mid), out, False)
+        return back(out).numpy().copy(), attn[:, 0]
+
+
 def pack_gpt2_weights(hf_model):
     """HF GPT2Model -> the dict layout oracle/restate.py:gpt2_model takes (Conv1D weights are already [in,out])."""
     def n(p):

@@ -272,6 +272,25 @@ def context_attention(query, key, value, mask, w, num_heads, memory=None, pre_la
     return out, prob, (k, v)
 
 
+def positionwise_ffn(x, w, eps=1e-12):
+    """layers/positionwise_ffn.cpp:31-75 -- LayerNorm(eps 1e-12), MatMul, AddBiasAct<Relu>, MatMul, AddInputBias (residual).
+    w: w1_weight [H,F], w1_bias, w2_weight [F,H], w2_bias, ln_gamma, ln_beta ([in,out] matrices)."""
+    hdn = layer_norm(x, w["ln_gamma"], w["ln_beta"], eps)
+    inter = add_bias_act(mat_mul(hdn, False, w["w1_weight"], False), w["w1_bias"], "relu")
+    out = mat_mul(inter, False, w["w2_weight"], False).reshape(x.shape)
+    return add_input_bias(out, x, w["w2_bias"])
+
+
+def transformer_decoder_layer(x, memory_bank, src_mask, dec_mask, lw, num_heads, memory=None):
+    """python/turbo_transformers/layers/modeling_decoder.py:58-140 -- pre-LN self attention + residual, pre-LN context attention
+    + residual, feed-forward. lw: {"self": multi_headed_attention weights, "context": context_attention weights, "ffn": ...};
+    masks are additive (already multiplied by -1e18). Returns (output, context attention of head 0, (memory keys, values))."""
+    query, _ = multi_headed_attention(x, dec_mask, lw["self"], num_heads, pre_layernorm=True, post_add_input=True)
+    mid, attn, mem = context_attention(query, memory_bank, memory_bank, src_mask, lw["context"], num_heads, memory,
+                                       pre_layernorm=True, post_add_input=True)
+    return positionwise_ffn(mid, lw["ffn"]), attn[:, 0], mem
+
+
 def multi_headed_attention_smart_batch(x_packed, seq_list, w, num_heads, mask=None, post_layernorm=True):
     """Self-attention branch of layers/multi_headed_attention_smart_batch.cpp:180-421 on packed [1,sumL,H]."""
     H = x_packed.shape[-1]

@@ -152,6 +152,21 @@ def test_live_reference_context_attention_agrees_with_restatement(flags):
     assert np.abs(out_s - out_s2).max() < 1e-5
 
 
+@pytest.mark.skipif(not ref_driver.available(), reason="oracle/_ref is not built on this machine")
+def test_live_reference_decoder_layer_agrees_with_restatement():
+    H, F, heads, B, Lt, Ls = 64, 160, 4, 2, 6, 9
+    lw = ref_driver.decoder_layer_weights(H, F, 3)
+    r = np.random.default_rng(4)
+    x = r.standard_normal((B, Lt, H)).astype(np.float32)
+    mem = r.standard_normal((B, Ls, H)).astype(np.float32)
+    src_mask = np.zeros((B, 1, Ls), np.float32)
+    src_mask[0, 0, 7:] = -1e18
+    dec_mask = (np.triu(np.ones((Lt, Lt), np.float32), 1)[None] * -1e18).repeat(B, 0)
+    out, attn = ref_driver.RefDecoderLayer(lw, heads)(x, mem, src_mask, dec_mask)
+    out2, attn2, _ = restate.transformer_decoder_layer(x, mem, src_mask, dec_mask, lw, heads)
+    assert np.abs(out - out2).max() < 2e-5 and np.abs(attn - attn2).max() < 1e-6
+
+
 def test_gpt2_composition_matches_huggingface_fp32():
     hf = synthetic.make_hf_gpt2("gpt2-tiny", 3)
     W = ref_driver.pack_gpt2_weights(hf)

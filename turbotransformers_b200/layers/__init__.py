@@ -3,6 +3,7 @@ from .modeling_bert import (BertEmbeddings, BertIntermediate, BertOutput, BertAt
 from .qmodeling_bert import QBertIntermediate, QBertOutput, QBertLayer, QBertEncoder, QBertModel
 from .modules import MultiHeadedAttention, PositionwiseFeedForward
 from .modeling_gpt2 import GPT2Model
+from .modeling_decoder import TransformerDecoderLayer, TransformerDecoder
 from .modeling_smart_pad import (MultiHeadedAttentionSmartBatch, BertLayerSmartBatch, BertEncoderSmartBatch, BertModelSmartBatch,
                                  BertModelNoPoolerSmartBatch)
 from .modeling_distillbert import DistillBertAttention, DistrillFFN, DistrillTransformerBlock, DistrillTransformer, DistilBertModel
@@ -15,4 +16,4 @@ __all__ = ['BertEmbeddings', 'BertIntermediate', 'BertOutput', 'BertAttention', 
            'PositionwiseFeedForward', 'QBertIntermediate', 'QBertOutput', 'QBertLayer', 'QBertEncoder', 'QBertModel', 'GPT2Model',
            'MultiHeadedAttentionSmartBatch', 'BertLayerSmartBatch', 'BertEncoderSmartBatch', 'BertModelSmartBatch',
            'BertModelNoPoolerSmartBatch', 'DistillBertAttention', 'DistrillFFN', 'DistrillTransformerBlock', 'DistrillTransformer',
-           'DistilBertModel', 'RobertaModel', 'AlbertAttention', 'AlbertLayer', 'AlbertLayerGroup', 'AlbertTransformer', 'AlbertModel']
+           'DistilBertModel', 'RobertaModel', 'AlbertAttention', 'AlbertLayer', 'AlbertLayerGroup', 'AlbertTransformer', 'AlbertModel', 'TransformerDecoderLayer', 'TransformerDecoder']

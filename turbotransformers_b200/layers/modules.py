@@ -35,11 +35,17 @@ class MultiHeadedAttention(cxx.MultiHeadedAttention):
         attn_type = attn_type or "self"
         super().__call__(key_tensor, value_tensor, query_tensor, mask, attn_type, output, attn, cache, pre_layernorm,
                          post_layernorm, post_add_input, is_trans_weight)
-        if layer_cache is not None and attn_type == "context":
-            # the projected encoder memory goes back to the caller's dict, as the reference does (modules.py:79-83)
+        if layer_cache is not None:
+            # the caches go back to the caller's dict, as the reference does (modules.py:79-83): the projected encoder memory
+            # as torch tensors [B, heads, Lk, d]; the self-attention cache as the runtime's own tensor (its buffer is paged and
+            # reserved ahead, so it is handed back as it is and passed in again on the next step)
             for k, v in cache.items():
-                if "memory" in k and not v.is_null():
+                if v.is_null():
+                    continue
+                if "memory" in k and attn_type == "context":
                     layer_cache[k] = convert_returns_as_type(v, ReturnType.TORCH)
+                elif "self" in k and attn_type == "self":
+                    layer_cache[k] = v
         return convert_returns_as_type(output, return_type), attn
 
     @staticmethod
@@ -97,3 +103,14 @@ class PositionwiseFeedForward(cxx.PositionwiseFeedForward):
         output = create_empty_if_none(output)
         super().__call__(input_tensor, output, is_trans_weight)
         return convert_returns_as_type(output, return_type)
+
+    @staticmethod
+    def from_onmt(position_wise_ffn, is_trans_weight: Optional[bool] = True):
+        """From an OpenNMT-py style PositionwiseFeedForward (parameters w_1, w_2, layer_norm; modules.py:277-309 of the
+        reference). With is_trans_weight the torch [out, in] matrices are used as they are: call with the same flag."""
+        p = {k: v.detach() for k, v in position_wise_ffn.named_parameters()}
+        w = (lambda t: t.contiguous()) if is_trans_weight else (lambda t: torch.t(t).contiguous())
+        T = convert2tt_tensor
+        with torch.no_grad():
+            return PositionwiseFeedForward(T(w(p['w_1.weight'])), T(p['w_1.bias']), T(w(p['w_2.weight'])), T(p['w_2.bias']),
+                                           T(p['layer_norm.weight']), T(p['layer_norm.bias']))
