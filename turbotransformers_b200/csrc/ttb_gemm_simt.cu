@@ -2,6 +2,7 @@
 // primitive MatMul / BatchMatMul entry points. The tensor-core GEMM lives in ttb_gemm_tc.cu.
 #include "ttb_common.cuh"
 
+#include <algorithm>
 #include <cstdint>
 #include <type_traits>
 
@@ -13,7 +14,8 @@ namespace {
 // with at least two waves of such tiles; 64 x 64 x 16 with 4 x 4; 32 x 32 x 64 with 2 x 2 for problems whose
 // 64 x 64 grid would leave most SMs idle (one 128-token request: 24 CTAs), where the long k step keeps 16 loads per thread
 // in flight because there are too few CTAs to hide a load behind another CTA's arithmetic. Every output element sums its k terms in the same order in
-// both, so the two give identical bits.
+// all of them, so they give identical bits; only the split-K path (small problems with a long k, see run()) adds partial
+// sums of k slices instead, still in a fixed order.
 
 // C[b] = alpha * op(A[b]) * op(B[b]) + beta * C[b]; all row-major.
 // op(A) is M x K: element (m,k) at A[m*K + k] or, transposed storage, A[k*M + m].
@@ -122,9 +124,10 @@ gemm_simt_kernel(const T* __restrict__ A, int a_trans, const T* __restrict__ B, 
 constexpr int LBN = 128, LBK = 16;
 
 template <typename T>
-__device__ __forceinline__ float4 fetch4(const T* __restrict__ P, bool vec, bool inside, int r, int k, int R, int K, bool k_major) {
-  // Four consecutive elements of an operand with R rows and K columns. k_major: storage is P[r * K + k] and the four run
-  // along k; otherwise storage is P[k * R + r] and the four run along r.
+__device__ __forceinline__ float4 fetch4(const T* __restrict__ P, bool vec, bool inside, int r, int k, int R, int K, int k_end,
+                                         bool k_major) {
+  // Four consecutive elements of an operand with R rows and K columns, zero at rows >= R and at k >= k_end. k_major: storage
+  // is P[r * K + k] and the four run along k; otherwise storage is P[k * R + r] and the four run along r.
   if constexpr (std::is_same<T, float>::value) {
     if (vec && inside) {
       const float* q = k_major ? P + (int64_t)r * K + k : P + (int64_t)k * R + r;
@@ -135,7 +138,7 @@ __device__ __forceinline__ float4 fetch4(const T* __restrict__ P, bool vec, bool
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     const int rr = k_major ? r : r + c, kk = k_major ? k + c : k;
-    v[c] = (rr < R && kk < K) ? to_f(k_major ? P[(int64_t)rr * K + kk] : P[(int64_t)kk * R + rr]) : 0.f;
+    v[c] = (rr < R && kk < k_end) ? to_f(k_major ? P[(int64_t)rr * K + kk] : P[(int64_t)kk * R + rr]) : 0.f;
   }
   return make_float4(v[0], v[1], v[2], v[3]);
 }
@@ -144,14 +147,18 @@ template <typename T, int LBM>
 __global__ void __launch_bounds__(256, 2)
 gemm_simt_large_kernel(const T* __restrict__ A, int a_trans, const T* __restrict__ B, int b_trans, T* __restrict__ C, int M,
                        int N, int K, float alpha, float beta, int64_t strideA, int64_t strideB, int64_t strideC, int vec_a,
-                       int vec_b, int vec_c) {
+                       int vec_b, int vec_c, int splits, int k_chunk, float* __restrict__ partial) {
+  // splits > 1 (split-K, for problems with too few tiles to fill the GPU): blockIdx.z = batch * splits + s, this CTA sums
+  // k in [s * k_chunk, (s + 1) * k_chunk) and writes its raw fp32 sums to partial[s][batch][M][N]; splitk_reduce_kernel adds
+  // the slices in increasing s and applies alpha / beta.
   static_assert(LBM == 128 || LBM == 64, "row tiles of 128 or 64");
   constexpr int RG = LBM / 64;       // groups of 4 rows per thread
   constexpr int TR = 4 * RG;         // rows per thread
   constexpr int EA = LBM * LBK / 1024;  // float4 slots of the A tile per thread
   __shared__ __align__(16) float As[2][LBK][LBM + 4];
   __shared__ __align__(16) float Bs[2][LBK][LBN + 4];
-  const int batch = blockIdx.z;
+  const int batch = blockIdx.z / splits, split = blockIdx.z % splits;
+  const int k_begin = split * k_chunk, k_end = min(K, k_begin + k_chunk);
   A += batch * strideA;
   B += batch * strideB;
   C += batch * strideC;
@@ -171,18 +178,18 @@ gemm_simt_large_kernel(const T* __restrict__ A, int a_trans, const T* __restrict
   // Operand stored [K, R] (R = tile rows): k = f / (R / 4), rows 4 (f % (R / 4)) .. +3.
   float4 ra[EA], rb[2];
   auto fetch = [&](int k0) {
-    const bool k_in = k0 + LBK <= K;
+    const bool k_in = k0 + LBK <= k_end;
 #pragma unroll
     for (int e = 0; e < EA; ++e) {
       const int f = tid + e * 256;
-      if (a_kmajor) ra[e] = fetch4(A, vec_a, rows_in && k_in, m0 + f / 4, k0 + 4 * (f % 4), M, K, true);
-      else ra[e] = fetch4(A, vec_a, rows_in && k_in, m0 + 4 * (f % (LBM / 4)), k0 + f / (LBM / 4), M, K, false);
+      if (a_kmajor) ra[e] = fetch4(A, vec_a, rows_in && k_in, m0 + f / 4, k0 + 4 * (f % 4), M, K, k_end, true);
+      else ra[e] = fetch4(A, vec_a, rows_in && k_in, m0 + 4 * (f % (LBM / 4)), k0 + f / (LBM / 4), M, K, k_end, false);
     }
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int f = tid + e * 256;
-      if (b_kmajor) rb[e] = fetch4(B, vec_b, cols_in && k_in, n0 + f / 4, k0 + 4 * (f % 4), N, K, true);
-      else rb[e] = fetch4(B, vec_b, cols_in && k_in, n0 + 4 * (f % 32), k0 + f / 32, N, K, false);
+      if (b_kmajor) rb[e] = fetch4(B, vec_b, cols_in && k_in, n0 + f / 4, k0 + 4 * (f % 4), N, K, k_end, true);
+      else rb[e] = fetch4(B, vec_b, cols_in && k_in, n0 + 4 * (f % 32), k0 + f / 32, N, K, k_end, false);
     }
   };
   auto stage = [&](int buf) {
@@ -208,14 +215,14 @@ gemm_simt_large_kernel(const T* __restrict__ A, int a_trans, const T* __restrict
     }
   };
 
-  if (K > 0) {
-    fetch(0);
+  if (k_begin < k_end) {
+    fetch(k_begin);
     stage(0);
   }
   __syncthreads();
   int buf = 0;
-  for (int k0 = 0; k0 < K; k0 += LBK) {
-    const bool more = k0 + LBK < K;
+  for (int k0 = k_begin; k0 < k_end; k0 += LBK) {
+    const bool more = k0 + LBK < k_end;
     if (more) fetch(k0 + LBK);
 #pragma unroll
     for (int k = 0; k < LBK; ++k) {
@@ -245,6 +252,17 @@ gemm_simt_large_kernel(const T* __restrict__ A, int a_trans, const T* __restrict
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int gn = n0 + h * 64 + tx * 4;
+      if (partial) {
+        float* p = partial + (((int64_t)split * (gridDim.z / splits) + batch) * M + gm) * N + gn;
+        if (N % 4 == 0 && gn + 3 < N) {
+          *reinterpret_cast<float4*>(p) = make_float4(acc[i][h * 4], acc[i][h * 4 + 1], acc[i][h * 4 + 2], acc[i][h * 4 + 3]);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            if (gn + c < N) p[c] = acc[i][h * 4 + c];
+        }
+        continue;
+      }
       T* dst = C + (int64_t)gm * N + gn;
       if constexpr (std::is_same<T, float>::value) {
         if (vec_c && gn + 3 < N) {
@@ -268,6 +286,19 @@ gemm_simt_large_kernel(const T* __restrict__ A, int a_trans, const T* __restrict
   }
 }
 
+// C = alpha * (partial[0] + partial[1] + ... in this order) + beta * C over `total` contiguous elements.
+template <typename T>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ partial, int splits, int64_t total, float alpha, float beta, T* __restrict__ C) {
+  const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (idx >= total) return;
+  float s = 0.f;
+  for (int sp = 0; sp < splits; ++sp) s += partial[(int64_t)sp * total + idx];
+  float r = alpha * s;
+  if (beta != 0.f) r += beta * to_f(C[idx]);
+  C[idx] = from_f<T>(r);
+}
+
 int run(ttb_ctx* ctx, int dtype, const void* A, int a_trans, const void* B, int b_trans, int64_t batch, int64_t M,
         int64_t N, int64_t K, float alpha, float beta, void* C, const char* what) {
   if (!ctx) return TTB_ERR_INVALID;
@@ -282,6 +313,41 @@ int run(ttb_ctx* ctx, int dtype, const void* A, int a_trans, const void* B, int 
   const bool wide = N % 128 == 0 || N >= 512;  // a 128-column tile is not mostly padding
   const bool large = wide && ((M + 127) / 128) * n128 * batch >= 4ll * ctx->sm_count;
   const bool medium = wide && !large && ((M + 63) / 64) * n128 * batch >= (3ll * ctx->sm_count) / 2;
+  // Too few tiles and a long k: split k over CTAs (64 x 128 tiles, k slices of at least 64) and add the slices in a
+  // second pass. Deterministic, but the sum is no longer in plain increasing-k order.
+  int splits = 1, k_chunk = (int)K;
+  if (small && wide && K >= 256) {
+    const int64_t tiles = ((M + 63) / 64) * n128 * batch;
+    int64_t want = std::min<int64_t>((2ll * ctx->sm_count + tiles - 1) / tiles, K / 64);
+    if (want > 1 && want * batch <= 65535) {
+      k_chunk = (int)(((K + want - 1) / want + 15) / 16 * 16);
+      splits = (int)((K + k_chunk - 1) / k_chunk);
+    }
+  }
+  if (splits > 1) {
+    auto al16 = [](const void* q) { return reinterpret_cast<uintptr_t>(q) % 16 == 0; };
+    const bool f32 = dtype == TTB_F32;
+    const int vec_a = f32 && al16(A) && (a_trans ? M % 4 == 0 : K % 4 == 0) && (M * K) % 4 == 0;
+    const int vec_b = f32 && al16(B) && (b_trans ? K % 4 == 0 : N % 4 == 0) && (K * N) % 4 == 0;
+    const int64_t total = batch * M * N;
+    void* ws = nullptr;
+    int s = ttb_alloc(ctx, (size_t)(splits * total) * sizeof(float), "matmul/split_k", &ws);
+    if (s) return s;
+    dim3 grid((unsigned)n128, (unsigned)((M + 63) / 64), (unsigned)(batch * splits));
+    TTB_DISPATCH_FLOAT(ctx, dtype, T,
+                       (gemm_simt_large_kernel<T, 64><<<grid, 256, 0, ctx->stream>>>((const T*)A, a_trans, (const T*)B, b_trans, (T*)C, (int)M, (int)N,
+                                                                                    (int)K, alpha, beta, M * K, K * N, M * N, vec_a, vec_b, 0, splits,
+                                                                                    k_chunk, (float*)ws)));
+    s = launched(ctx, what);
+    if (!s) {
+      TTB_DISPATCH_FLOAT(ctx, dtype, T,
+                         (splitk_reduce_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>((const float*)ws, splits, total, alpha, beta,
+                                                                                                           (T*)C)));
+      s = launched(ctx, what);
+    }
+    const int f = ttb_free(ctx, ws, "matmul/split_k");  // stream-ordered: released after the reduce has run
+    return s ? s : f;
+  }
   const int bm = small ? 32 : (large ? 128 : 64), bn = small ? 32 : ((large || medium) ? 128 : 64);
   const int64_t gy = (M + bm - 1) / bm, gx = (N + bn - 1) / bn;
   TTB_REQUIRE(ctx, gy <= 65535, "%s: M too large for this kernel", what);
@@ -304,12 +370,12 @@ int run(ttb_ctx* ctx, int dtype, const void* A, int a_trans, const void* B, int 
         TTB_DISPATCH_FLOAT(ctx, dtype, T,
                            (gemm_simt_large_kernel<T, 128><<<grid, 256, 0, ctx->stream>>>((const T*)A + b0 * M * K, a_trans, (const T*)B + b0 * K * N,
                                                                                          b_trans, (T*)C + b0 * M * N, (int)M, (int)N, (int)K, alpha,
-                                                                                         beta, M * K, K * N, M * N, vec_a, vec_b, vec_c)));
+                                                                                         beta, M * K, K * N, M * N, vec_a, vec_b, vec_c, 1, (int)K, nullptr)));
       } else {
         TTB_DISPATCH_FLOAT(ctx, dtype, T,
                            (gemm_simt_large_kernel<T, 64><<<grid, 256, 0, ctx->stream>>>((const T*)A + b0 * M * K, a_trans, (const T*)B + b0 * K * N,
                                                                                         b_trans, (T*)C + b0 * M * N, (int)M, (int)N, (int)K, alpha,
-                                                                                        beta, M * K, K * N, M * N, vec_a, vec_b, vec_c)));
+                                                                                        beta, M * K, K * N, M * N, vec_a, vec_b, vec_c, 1, (int)K, nullptr)));
       }
     } else {
       TTB_DISPATCH_FLOAT(ctx, dtype, T,
