@@ -144,7 +144,7 @@ __device__ __forceinline__ float4 fetch4(const T* __restrict__ P, bool vec, bool
 }
 
 template <typename T, int LBM>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(256, LBM == 64 ? 3 : 2)
 gemm_simt_large_kernel(const T* __restrict__ A, int a_trans, const T* __restrict__ B, int b_trans, T* __restrict__ C, int M,
                        int N, int K, float alpha, float beta, int64_t strideA, int64_t strideB, int64_t strideC, int vec_a,
                        int vec_b, int vec_c, int splits, int k_chunk, float* __restrict__ partial) {
