@@ -58,6 +58,17 @@ def test_matmul_fp32_both_tile_shapes_ragged_sizes(ctx, m, n, k, a_trans, b_tran
     assert np.abs(host(Cc).astype(np.float64) - 2.5 * want).max() < 2e-6 * k * 10
 
 
+@pytest.mark.parametrize("batch,L", [(40, 509), (12, 250)])  # 128 x 128 tiles and 64 x 128 tiles with a ragged last tile
+def test_batch_matmul_fp32_ragged_attention_scores_on_the_wide_tiles(ctx, batch, L):
+    r = rng(12)
+    q = r.standard_normal((batch, L, 64)).astype(np.float32)
+    k = r.standard_normal((batch, L, 64)).astype(np.float32)
+    want = np.einsum("bld,bmd->blm", q.astype(np.float64), k.astype(np.float64)) * 0.125
+    Q, K, S = dev(q), dev(k), dev(np.full((batch, L, L), 3.0, np.float32))
+    ctx.call("batch_matmul", _capi.F32, Q, 0, K, 1, batch, L, L, 64, 0.125, 0.0, S)
+    assert np.abs(host(S).astype(np.float64) - want).max() < 2e-5
+
+
 @pytest.mark.parametrize("dt", DTS)
 def test_batch_matmul_attention_shapes(ctx, dt):
     r = rng(2)

@@ -310,7 +310,7 @@ int run(ttb_ctx* ctx, int dtype, const void* A, int a_trans, const void* B, int 
   const bool small = ((M + 63) / 64) * ((N + 63) / 64) * batch < 2ll * ctx->sm_count;  // too few 64 x 64 tiles to fill the GPU
   // 128 x 128 tiles from two waves of them (two CTAs per SM); 64 x 128 from most of one wave; 64 x 64 below that
   const int64_t n128 = (N + 127) / 128;
-  const bool wide = N % 128 == 0 || N >= 512;  // a 128-column tile is not mostly padding
+  const bool wide = n128 * 128 * 4 <= N * 5;  // 128-column tiles carry at most a quarter of padding
   const bool large = wide && ((M + 127) / 128) * n128 * batch >= 4ll * ctx->sm_count;
   const bool medium = wide && !large && ((M + 63) / 64) * n128 * batch >= (3ll * ctx->sm_count) / 2;
   // Too few tiles and a long k: split k over CTAs (64 x 128 tiles, k slices of at least 64) and add the slices in a
