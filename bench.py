@@ -28,8 +28,6 @@ METRIC = "bert_base_fp16_varlen_b64_sequences_per_s"
 UNIT = "sequences/s"
 BATCH, LO, HI, SEED = 64, 8, 512, 0
 LAYERS, HIDDEN, HEADS, FFN = 12, 768, 12, 3072
-# ncu, small case of the same kernel (see profiles/): DRAM bytes per GEMM launch relative to algorithmic bytes
-GEMM_TRAFFIC_NOTE = "profiles/gemm_tc_kernel_bert_base_varlen.md"
 
 
 def workload_config(n_gpus):
@@ -138,8 +136,18 @@ class ClockSampler:
                 "source": "nvml" if self.nvml else "nvidia-smi"}
 
 
-def make_batch(vocab, rank):
-    from turbotransformers_b200 import synthetic
+def load_synthetic():
+    """The seeded-input module loaded from its file, without importing the package around it: the reference arm must not
+    load this repository's native libraries."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("ttb_synthetic", os.path.join(ROOT, "turbotransformers_b200", "synthetic.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def make_batch(vocab, rank, synthetic=None):
+    synthetic = synthetic or load_synthetic()
     lens = synthetic.varlen_lengths(BATCH, LO, HI, SEED + rank)
     ids = synthetic.varlen_ids(lens, vocab, SEED + rank)
     return lens, ids
@@ -151,7 +159,7 @@ def make_batch(vocab, rank):
 def time_reference_cpu(steps, warmup, budget_s, rank0=True):
     import torch
     from oracle import ref_driver
-    from turbotransformers_b200 import synthetic
+    synthetic = load_synthetic()
     torch.set_grad_enabled(False)
     if not ref_driver.available():
         raise RuntimeError("oracle/_ref is not built")
@@ -161,7 +169,7 @@ def time_reference_cpu(steps, warmup, budget_s, rank0=True):
     hf = synthetic.make_hf_bert("bert-base", SEED)
     W = ref_driver.pack_bert_weights(hf)
     ref = ref_driver.RefBert(W, HEADS)
-    lens, ids = make_batch(hf.config.vocab_size, 0)
+    lens, ids = make_batch(hf.config.vocab_size, 0, synthetic)
     # calibrate on one short request, then size the per-step sample to the time budget
     t = time.perf_counter()
     ref.forward_smart_batch(ids[:1])
@@ -204,59 +212,85 @@ def run_reference(args):
 # our arm
 # ----------------------------------------------------------------------------------------------------
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel (the CTA-pair GEMM on the QKV shape,
-# M = 18424, N = 2304, K = 768), from the ncu capture summarised in profiles/gemm_tc_kernel_pair_qkv_shape_m18424.md.
+# M = 18424, N = 2304, K = 768), from an ncu capture of that launch.
 # The algorithmic bytes of that launch are 116.7 MB (A 28.3 + W 3.5 + out 84.9); most of the output is still in L2 when
 # the kernel ends, so the DRAM counter sees less than that.
 QKV_LAUNCH_DRAM_BYTES = 61.5e6
 
 
-def gemm_roofline(torch, ctx_mod, tokens, peaks):
-    """Times the tensor-core GEMM on the four Linear shapes of one BERT-base layer at this batch's token count the way
-    they run inside a step: launches back to back (CUDA events around the run, on the launching stream), each launch on
-    another of eight buffer sets so that no launch finds its activations in L2 (8 x >= 85 MB against 126 MB), long enough
-    for the power cap to act. The roofline object is the QKV-shape launch of the dominant kernel against the sustained
-    cuBLAS figure; the other shapes are listed beside it."""
+def burst_us(torch, fns, rounds):
+    """Mean device time of one launch in a back-to-back run over several buffer sets (CUDA events on the launching
+    stream; the rotating sets keep each launch's activations out of L2)."""
+    for _ in range(2):
+        for f in fns:
+            f()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(rounds):
+        for f in fns:
+            f()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (rounds * len(fns))
+
+
+def gemm_roofline(torch, lens, peaks):
+    """Times the kernels of one encoder layer at this batch's size the way they run inside a step: launches back to back,
+    each on another of eight buffer sets so that no launch finds its activations in L2 (8 x >= 85 MB against 126 MB).
+    Each run lasts a few milliseconds at full clocks, so the denominators are the burst figures. The roofline object
+    is the QKV-shape launch of the dominant kernel; the other GEMM shapes, the attention kernel and the LayerNorm kernel
+    are listed beside it with their own fractions."""
+    import numpy as np
     from turbotransformers_b200 import _capi
+    tokens = sum(lens)
     ctx = _capi.Context(torch.cuda.current_device())
     shapes = [("qkv", HIDDEN, 3 * HIDDEN, _capi.EPI_BIAS), ("attn_out", HIDDEN, HIDDEN, _capi.EPI_BIAS_RESIDUAL),
               ("ffn1", HIDDEN, FFN, _capi.EPI_BIAS_GELU), ("ffn2", FFN, HIDDEN, _capi.EPI_BIAS_RESIDUAL)]
     sets, rounds = 8, 6
-    per_shape, total_ms, total_flops = {}, 0.0, 0.0
+    f16 = torch.float16
+    per_shape, total_us, total_flops = {}, 0.0, 0.0
     for name, K, N, epi in shapes:
-        w = torch.randn(N, K, device="cuda", dtype=torch.float16) * 0.03
-        b = torch.randn(N, device="cuda", dtype=torch.float16)
-        bufs = [(torch.randn(tokens, K, device="cuda", dtype=torch.float16), torch.randn(tokens, N, device="cuda", dtype=torch.float16),
-                 torch.empty(tokens, N, device="cuda", dtype=torch.float16)) for _ in range(sets)]
-
-        def run_all():
-            for a, r, o in bufs:
-                ctx.call("linear", _capi.F16, a, K, w, b, r, N, tokens, N, K, epi, o, N)
-        for _ in range(2):
-            run_all()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(rounds):
-            run_all()
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / (rounds * sets)
+        w = torch.randn(N, K, device="cuda", dtype=f16) * 0.03
+        b = torch.randn(N, device="cuda", dtype=f16)
+        bufs = [(torch.randn(tokens, K, device="cuda", dtype=f16), torch.randn(tokens, N, device="cuda", dtype=f16),
+                 torch.empty(tokens, N, device="cuda", dtype=f16)) for _ in range(sets)]
+        us = burst_us(torch, [lambda a=a, r=r, o=o: ctx.call("linear", _capi.F16, a, K, w, b, r, N, tokens, N, K, epi, o, N)
+                              for a, r, o in bufs], rounds)
         fl = 2.0 * tokens * N * K
-        per_shape[name] = {"us": round(ms * 1e3, 1), "tflops": round(fl / ms / 1e9, 1)}
-        total_ms += ms
+        per_shape[name] = {"us": round(us, 1), "tflops": round(fl / us / 1e6, 1), "frac": round(fl / us / 1e6 / peaks["tflops"], 4)}
+        total_us += us
         total_flops += fl
         del bufs, w, b
+    # attention over the packed batch (tensor bound: 4*H*L^2 FLOPs per sequence, padding never counts)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device="cuda")
+    abufs = [(torch.randn(tokens, 3 * HIDDEN, device="cuda", dtype=f16), torch.empty(tokens, HIDDEN, device="cuda", dtype=f16))
+             for _ in range(sets)]
+    us = burst_us(torch, [lambda q=q, o=o: ctx.call("attention_fwd", _capi.F16, q, tokens, cu, len(lens), max(lens), HEADS, HIDDEN // HEADS,
+                                                    None, 0, 0, 0, 0.125, o) for q, o in abufs], rounds)
+    afl = sum(4.0 * HIDDEN * L * L for L in lens)
+    attention = {"us": round(us, 1), "tflops": round(afl / us / 1e6, 1), "frac": round(afl / us / 1e6 / peaks["tflops"], 4), "bound": "tensor"}
+    del abufs
+    # LayerNorm over the residual sum the GEMM epilogue wrote (HBM bound: read + write of [tokens, H] fp16)
+    g, z = torch.ones(HIDDEN, device="cuda", dtype=f16), torch.zeros(HIDDEN, device="cuda", dtype=f16)
+    lbufs = [(torch.randn(tokens, HIDDEN, device="cuda", dtype=f16), torch.empty(tokens, HIDDEN, device="cuda", dtype=f16)) for _ in range(sets * 4)]
+    us = burst_us(torch, [lambda x=x, o=o: ctx.call("layernorm", _capi.F16, x, o, g, z, tokens, HIDDEN, 1e-12) for x, o in lbufs], rounds)
+    lbytes = 2.0 * tokens * HIDDEN * 2
+    layernorm = {"us": round(us, 1), "gbs": round(lbytes / us / 1e3, 1), "frac": round(lbytes / us / 1e3 / peaks["hbm_gbs"], 4), "bound": "hbm"}
+    del lbufs
     ctx.close()
     qkv_flops = 2.0 * tokens * 3 * HIDDEN * HIDDEN
     achieved = per_shape["qkv"]["tflops"]
-    return {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
-            "frac": round(achieved / peaks["tflops_sustained"], 4), "traffic": QKV_LAUNCH_DRAM_BYTES,
-            "peak_source": peaks["source"] + " (cuBLAS bf16, sustained: the launches are timed back to back under the power cap)",
+    return {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+            "frac": round(achieved / peaks["tflops"], 4), "traffic": QKV_LAUNCH_DRAM_BYTES,
+            "peak_source": peaks["source"] + " (cuBLAS bf16, burst: the kernel is timed in a run of a few milliseconds at full clocks)",
+            "frac_of_sustained_peak": round(achieved / peaks["tflops_sustained"], 4),
             "kernel": "gemm_tc_kernel<256, f16, pair> (tcgen05 cta_group::2 + TMEM + TMA) on the QKV shape "
                       f"[{tokens} x {3 * HIDDEN} x {HIDDEN}]; 36 of the 48 GEMM launches per step run this kernel",
             "avg_launch_us": per_shape["qkv"]["us"], "algorithmic_flops_per_launch": qkv_flops,
             "algorithmic_bytes_per_launch": 2.0 * (tokens * HIDDEN + 3 * HIDDEN * HIDDEN + tokens * 3 * HIDDEN),
-            "per_shape": per_shape, "all_four_shapes_tflops": round(total_flops / total_ms / 1e9, 1)}
+            "per_shape": per_shape, "all_four_shapes_tflops": round(total_flops / total_us / 1e6, 1),
+            "attention_kernel": attention, "layernorm_kernel": layernorm}
 
 
 def run_ours(args):
@@ -280,7 +314,7 @@ def run_ours(args):
     hf = synthetic.make_hf_bert("bert-base", SEED)
     vocab = hf.config.vocab_size
     model = tt.BertModelSmartBatch.from_torch(hf.to(dev).half(), dev)
-    lens, ids = make_batch(vocab, rank)
+    lens, ids = make_batch(vocab, rank, synthetic)
     tokens = sum(lens)
     ids_host = torch.cat(ids).pin_memory()
     ids_dev = ids_host.to(dev)
@@ -357,7 +391,7 @@ def run_ours(args):
         if args.no_extras:
             print(json.dumps(line))
             return
-        line["roofline"] = gemm_roofline(torch, cxx, tokens, peaks)
+        line["roofline"] = gemm_roofline(torch, lens, peaks)
         # p50 latency of one 128-token request (the other half of the headline metric)
         fixed = tt.BertModel.from_torch(hf, dev)
         one = synthetic.random_ids(1, 128, vocab, SEED).to(dev)

@@ -35,6 +35,12 @@ OUT_DIR = os.path.join(HERE, "_ref")
 MODULE = "turbo_transformers_cxx"
 
 
+def default_reference():
+    """Where the reference checkout is looked for when no path is given: $TT_REFERENCE_ROOT, else a directory named
+    `reference` beside this repository."""
+    return os.environ.get("TT_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
 def _site_packages():
     import numpy  # any package that lives in site-packages
     return os.path.dirname(os.path.dirname(numpy.__file__))
@@ -72,8 +78,9 @@ def blas_dir_file():
     return os.path.join(OUT_DIR, "blas_dir.txt")
 
 
-def build(reference="/root/reference", force=False, verbose=True):
+def build(reference=None, force=False, verbose=True):
     """Build oracle/_ref/turbo_transformers_cxx*.so. Returns its path, or None when it cannot be built."""
+    reference = reference or default_reference()
     out = module_path()
     if os.path.exists(out) and not force:
         return out
@@ -126,13 +133,17 @@ def cuda_module_path():
     return os.path.join(OUT_DIR, "cuda", MODULE + suffix)
 
 
-def build_cuda(reference="/root/reference", force=False, verbose=True, cuda_home="/usr/local/cuda"):
+def build_cuda(reference=None, force=False, verbose=True, cuda_home=None):
     """Build oracle/_ref/cuda/turbo_transformers_cxx*.so (the reference with TT_WITH_CUDA). Returns its path or None."""
     import shutil
     import tempfile
     out = cuda_module_path()
     if os.path.exists(out) and not force:
         return out
+    reference = reference or default_reference()
+    if cuda_home is None:  # the toolkit that owns the nvcc on PATH, else $CUDA_HOME
+        nvcc_on_path = shutil.which("nvcc")
+        cuda_home = os.environ.get("CUDA_HOME") or (os.path.dirname(os.path.dirname(os.path.realpath(nvcc_on_path))) if nvcc_on_path else "")
     tt = os.path.join(reference, "turbo_transformers")
     blas, dlpack = find_openblas(), find_dlpack_header()
     nvcc = os.path.join(cuda_home, "bin", "nvcc")
@@ -198,7 +209,7 @@ def build_cuda(reference="/root/reference", force=False, verbose=True, cuda_home
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=None, help="the reference checkout (default: $TT_REFERENCE_ROOT, else ../reference)")
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--cuda", action="store_true", help="also build the reference's GPU path into oracle/_ref/cuda/")
     a = ap.parse_args()

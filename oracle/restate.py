@@ -395,7 +395,8 @@ def q_quantize_rows(x):
 def q_linear(x, wq, w_scale, bias):
     """int8 x int8 -> int32 accumulate, then acc * s_row * s_w + bias (fp32 here; the GPU epilogue rounds to fp16)."""
     xq, xs = q_quantize_rows(x.reshape(-1, x.shape[-1]))
-    acc = xq.astype(np.int32) @ wq.astype(np.int32)
+    # products of int8 values summed over K < 2^53 / 127^2 are exact in float64, and float64 has a BLAS behind it
+    acc = np.rint(xq.astype(np.float64) @ wq.astype(np.float64)).astype(np.int32)
     return (acc.astype(F32) * xs * F32(w_scale) + bias.astype(F32)).astype(F32)
 
 

@@ -310,7 +310,7 @@ void MultiHeadedAttention::Run(const Tensor& x, const Tensor& attention_mask, co
     gemm_in = &normed;
   }
 
-  const bool fused = dt != TTB_F32 && !materialize_scores_ && d == 64;
+  const bool fused = dt != TTB_F32 && att_score == nullptr && d == 64;
   Tensor context(nullptr);  // [T, H] token-major attention output
   context.Reshape(x.dtype(), {T, H}, kDLCUDA, dev, "batch_gemm4/Reshape");
 

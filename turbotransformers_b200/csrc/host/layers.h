@@ -6,8 +6,8 @@
 //   fp16 / bf16   -> tcgen05 GEMMs with fused epilogues + one attention kernel over packed tokens
 //   int8          -> (after QuantizeInt8()) int8 tcgen05 GEMMs with dequantising epilogues
 // The dtype is taken from the weights handed to the constructor; activations must match it.
-// No layer keeps per-call state in members, so one object may be called from several host threads
-// (the reference serialised MultiHeadedAttention behind a global mutex).
+// No layer keeps per-call state in members (what a call does follows from its arguments alone), so one object may be
+// called from several host threads (the reference serialised MultiHeadedAttention behind a global mutex).
 #pragma once
 #include <mutex>
 #include <string>
@@ -99,9 +99,9 @@ class MultiHeadedAttention {
            core::Tensor* output, core::Tensor* att_score, bool pre_layernorm, bool post_layernorm, bool post_add_input,
            bool is_trans_weight, core::Tensor* cache_keys = nullptr, core::Tensor* cache_values = nullptr) const;
 
-  // 16-bit models skip the [B,heads,L,L] score tensor unless asked: it is the largest HBM round trip of
-  // the reference path. fp32 models always materialise it, as the reference does.
-  void set_materialize_scores(bool on) { materialize_scores_ = on; }
+  // `att_score` is a per-call choice: a 16-bit model given nullptr skips the [B,heads,L,L] score tensor (the largest HBM
+  // round trip of the reference path) and runs the fused attention kernel; given a tensor it materialises the scores into
+  // it as the reference does. fp32 models always materialise (into a temporary when att_score is nullptr).
   void set_pre_layernorm_eps(float eps) { pre_ln_eps_ = eps; }  // the reference hard-codes 1e-6
   void set_causal(bool on) { causal_ = on; }                    // decoder-style self-attention without a mask tensor
   void QuantizeInt8() { qkv_.set_int8(true); dense_.set_int8(true); }
@@ -123,7 +123,7 @@ class MultiHeadedAttention {
   PackedLinear qkv_, dense_;
   core::Tensor layernorm_gamma_, layernorm_beta_;
   int64_t num_attention_heads_;
-  bool materialize_scores_ = false, causal_ = false;
+  bool causal_ = false;
   float pre_ln_eps_ = 1e-6f;
 };
 

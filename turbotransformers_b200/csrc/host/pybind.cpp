@@ -153,7 +153,6 @@ PYBIND11_MODULE(turbo_transformers_cxx, m) {
                                          std::move(ln_w), std::move(ln_b), num_attention_heads);
       }))
       .def("__call__", &layers::BertAttention::operator())
-      .def("set_materialize_scores", [](layers::BertAttention& s, bool on) { s.set_materialize_scores(on); })
       .def("quantize_int8", [](layers::BertAttention& s) { s.QuantizeInt8(); });
 
   py::class_<layers::MultiHeadedAttention>(m, "MultiHeadedAttention")
@@ -169,7 +168,6 @@ PYBIND11_MODULE(turbo_transformers_cxx, m) {
                                                 std::move(ln_b), heads);
       }))
       .def("__call__", &layers::MultiHeadedAttention::operator())
-      .def("set_materialize_scores", &layers::MultiHeadedAttention::set_materialize_scores)
       .def("set_pre_layernorm_eps", &layers::MultiHeadedAttention::set_pre_layernorm_eps)
       .def("set_causal", &layers::MultiHeadedAttention::set_causal)
       .def("quantize_int8", &layers::MultiHeadedAttention::QuantizeInt8);
@@ -188,7 +186,6 @@ PYBIND11_MODULE(turbo_transformers_cxx, m) {
                                                           std::move(ln_g), std::move(ln_b), heads);
       }))
       .def("__call__", &layers::MultiHeadedAttentionSmartBatch::operator())
-      .def("set_materialize_scores", [](layers::MultiHeadedAttentionSmartBatch& s, bool on) { s.set_materialize_scores(on); })
       .def("quantize_int8", [](layers::MultiHeadedAttentionSmartBatch& s) { s.QuantizeInt8(); });
 
   py::class_<layers::BertIntermediate>(m, "BertIntermediate")

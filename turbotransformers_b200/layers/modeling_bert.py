@@ -119,7 +119,6 @@ class BertAttention(cxx.BertAttention):
         attention_mask = try_convert(create_empty_if_none(attention_mask))
         context_layer = cxx.Tensor.create_empty()
         attn_probs = cxx.Tensor.create_empty()
-        self.set_materialize_scores(bool(output_attentions))
         super().__call__(input_tensor, attention_mask, context_layer, attn_probs if output_attentions else None, is_trans_weight)
         if output_attentions:
             return (convert_returns_as_type(context_layer, return_type),

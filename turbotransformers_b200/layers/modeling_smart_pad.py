@@ -41,8 +41,7 @@ class MultiHeadedAttentionSmartBatch(cxx.MultiHeadedAttentionSmartBatch):
         mask = try_convert(create_empty_if_none(mask))
         output, attn = create_empty_if_none(output), create_empty_if_none(attn)
         cache = {k: (try_convert(v) if v is not None else _empty()) for k, v in (layer_cache or {}).items()}
-        self.set_materialize_scores(bool(output_attentions))
-        super().__call__(key_tensor, value_tensor, query_tensor, mask, attn_type or "self", output, attn, cache,
+        super().__call__(key_tensor, value_tensor, query_tensor, mask, attn_type or "self", output, attn if output_attentions else None, cache,
                          [int(n) for n in query_seq_len_list], [int(n) for n in key_seq_len_list], pre_layernorm, post_layernorm,
                          post_add_input, is_trans_weight)
         return convert_returns_as_type(output, return_type), attn

@@ -31,9 +31,9 @@ class MultiHeadedAttention(cxx.MultiHeadedAttention):
         mask = try_convert(create_empty_if_none(mask))
         output, attn = create_empty_if_none(output), create_empty_if_none(attn)
         cache = {k: (try_convert(v) if v is not None else _empty()) for k, v in (layer_cache or {}).items()}
-        self.set_materialize_scores(bool(output_attentions))
         attn_type = attn_type or "self"
-        super().__call__(key_tensor, value_tensor, query_tensor, mask, attn_type, output, attn, cache, pre_layernorm,
+        super().__call__(key_tensor, value_tensor, query_tensor, mask, attn_type, output,
+                         attn if (output_attentions or attn_type == "context") else None, cache, pre_layernorm,
                          post_layernorm, post_add_input, is_trans_weight)
         if layer_cache is not None:
             # the caches go back to the caller's dict, as the reference does (modules.py:79-83): the projected encoder memory
