@@ -189,12 +189,60 @@ int ttb_prepack_weight_int8(ttb_ctx* ctx, int src_dtype, const void* src, int sr
 int ttb_linear(ttb_ctx* ctx, int dtype, const void* A, int64_t lda, const void* Wp, const void* bias,
                const void* residual, int64_t ldr, int64_t M, int64_t N, int64_t K, int epilogue, void* out,
                int64_t ldo);
+/* The general form of ttb_linear: operands that carry more precision than one tensor-core format are given as two planes,
+ * and the kernel accumulates one product per pair of planes into the same accumulator:
+ *   dtype F16 / BF16, A2 == NULL           out = epilogue(A . W^T)                                   (what ttb_linear computes)
+ *   dtype F16 / BF16, A2 != NULL           out = epilogue(A . W^T + A2 . W^T): activations kept as a rounded value plus what
+ *                                          the rounding dropped (see out_lo), so a bf16 model's GEMMs see 16 significant bits
+ *   dtype F32 (A, A2, W, W2 all given)     out = epilogue(A . W^T + A2 . W^T + A . W2^T) on tf32 tensor cores: A/A2 and W/W2
+ *                                          are the hi/lo planes ttb_split_tf32 makes; the sum has fp32-level accuracy. This is
+ *                                          the tensor-core route of kernels::MatMul for fp32 models (mat_mul.cpp:81-96, where
+ *                                          the reference selects CUBLAS_GEMM_DEFAULT_TENSOR_OP)
+ * out_dtype is dtype, or F32 for 16-bit operands (an fp32 residual stream); bias and residual are of out_dtype. out_lo
+ * (BF16 outputs only, may be NULL) receives v - round(v) for every output value v, with out's pitch. W and W2 are
+ * K-major [N, K] (ttb_prepack_weight). K % 8 == 0 (16-bit) or K % 4 == 0 (F32); lda likewise. */
+typedef struct ttb_linear_args {
+  int dtype, out_dtype;
+  const void* A;
+  const void* A2;
+  int64_t lda;
+  const void* W;
+  const void* W2;
+  const void* bias;
+  const void* residual;
+  int64_t ldr;
+  int64_t M, N, K;
+  int epilogue;
+  void* out;
+  void* out_lo;
+  int64_t ldo;
+} ttb_linear_args;
+int ttb_linear_ex(ttb_ctx* ctx, const ttb_linear_args* args);
+/* hi[i] = x[i] rounded to tf32 (10 mantissa bits), lo[i] = x[i] - hi[i] rounded likewise; x may be hi (in place).
+ * The operand planes of the F32 form of ttb_linear_ex. 16-byte aligned pointers. */
+int ttb_split_tf32(ttb_ctx* ctx, const float* x, int64_t n, float* hi, float* lo);
+
 /* int8 x int8 -> int32 (tcgen05 kind::i8), out = epilogue(acc * row_scale[m] * *w_scale + bias), out dtype
  * F16/BF16. Replaces the torch dynamic-quantised Linear + FusedAddBiasGELU / FusedAddBiasLayerNorm glue of
  * python/turbo_transformers/layers/qmodeling_bert.py:13-45. K % 16 == 0. */
 int ttb_linear_int8(ttb_ctx* ctx, int out_dtype, const int8_t* Aq, const float* row_scale, const int8_t* Wq,
                     const float* w_scale, const void* bias, const void* residual, int64_t ldr, int64_t M,
                     int64_t N, int64_t K, int epilogue, void* out, int64_t ldo);
+/* The reference's own int8 recipe, python/turbo_transformers/layers/qmodeling_bert.py:13-45: torch dynamic quantisation
+ * (torch.quantization.quantize_dynamic, qint8) of a Linear. Weights: per-tensor symmetric, scale = max|W| / 127.5,
+ * q = clamp(rint(W / scale), -128, 127), plus their per-output-row sums. Activations: per-tensor affine over the whole
+ * [M, K] tensor with the range widened to contain 0, 7-bit levels 0..127 (the x86 engines' reduce_range), zero point from
+ * the end of the range with the smaller rounding error. out = epilogue((sum_k (xq - zp) * wq) * x_scale * w_scale + bias).
+ *   ttb_prepack_weight_int8_affine : dst int8 [N, K], *scale_out (device fp32), col_sum_out int32 [N]
+ *   ttb_quantize_tensor_affine     : xq int8 [M, K] (values 0..127); qparams = device fp32 [4]: scale, zero point, and two
+ *                                    words of scratch (the running minimum and maximum)
+ *   ttb_linear_int8_affine         : the GEMM (tcgen05 kind::i8) with the zero-point correction in its epilogue */
+int ttb_prepack_weight_int8_affine(ttb_ctx* ctx, int src_dtype, const void* src, int src_is_nk, int64_t K, int64_t N,
+                                   int8_t* dst, float* scale_out, int32_t* col_sum_out);
+int ttb_quantize_tensor_affine(ttb_ctx* ctx, int dtype, const void* x, int64_t M, int64_t K, int8_t* xq, float* qparams);
+int ttb_linear_int8_affine(ttb_ctx* ctx, int out_dtype, const int8_t* Aq, const float* act_qparams, const int8_t* Wq,
+                           const float* w_scale, const int32_t* col_sum, const void* bias, const void* residual, int64_t ldr,
+                           int64_t M, int64_t N, int64_t K, int epilogue, void* out, int64_t ldo);
 /* int8 Linear with the activations quantised on the fly, for callers that cannot allocate device memory.
  * This entry point has no counterpart in the reference. It exists for hosts that pass the library only their
  * inputs and outputs: a server whose arena already owns all device memory, code inside a region where the CUDA

@@ -18,6 +18,13 @@ ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_OOM, ERR_DEVICE_WAIT, ERR_BAD_INDEX 
 
 p, i32, i64, f32, sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
 
+class LinearArgs(C.Structure):
+    """ttb_linear_args of include/ttb.h."""
+    _fields_ = [("dtype", i32), ("out_dtype", i32), ("A", p), ("A2", p), ("lda", i64), ("W", p), ("W2", p), ("bias", p),
+                ("residual", p), ("ldr", i64), ("M", i64), ("N", i64), ("K", i64), ("epilogue", i32), ("out", p), ("out_lo", p),
+                ("ldo", i64)]
+
+
 # name -> (restype, argtypes); must list every function declared in include/ttb.h
 SIGNATURES = {
     "ttb_ctx_create": (i32, [i32, p, C.POINTER(p)]),
@@ -65,6 +72,11 @@ SIGNATURES = {
     "ttb_prepack_weight": (i32, [p, i32, p, i32, i64, i64, i32, p]),
     "ttb_prepack_weight_int8": (i32, [p, i32, p, i32, i64, i64, p, p]),
     "ttb_linear": (i32, [p, i32, p, i64, p, p, p, i64, i64, i64, i64, i32, p, i64]),
+    "ttb_linear_ex": (i32, [p, C.POINTER(LinearArgs)]),
+    "ttb_split_tf32": (i32, [p, p, i64, p, p]),
+    "ttb_prepack_weight_int8_affine": (i32, [p, i32, p, i32, i64, i64, p, p, p]),
+    "ttb_quantize_tensor_affine": (i32, [p, i32, p, i64, i64, p, p]),
+    "ttb_linear_int8_affine": (i32, [p, i32, p, p, p, p, p, p, p, i64, i64, i64, i64, i32, p, i64]),
     "ttb_linear_int8": (i32, [p, i32, p, p, p, p, p, p, i64, i64, i64, i64, i32, p, i64]),
     "ttb_linear_int8_dynamic_noalloc": (i32, [p, i32, p, p, p, p, p, i64, i64, i64, i64, i32, p, i64]),
     "ttb_quantize_rows_int8": (i32, [p, i32, p, i64, i64, p, p]),
@@ -135,6 +147,14 @@ class Context:
         """Call ttb_<name>(ctx, *args); torch tensors are passed as their data pointers."""
         conv = [p(a.data_ptr()) if hasattr(a, "data_ptr") else a for a in args]
         self.check(getattr(lib(), "ttb_" + name)(self.h, *conv))
+
+    def linear_ex(self, dtype, out_dtype, A, W, M, N, K, epilogue, out, A2=None, W2=None, bias=None, residual=None, out_lo=None,
+                  lda=None, ldr=None, ldo=None):
+        """ttb_linear_ex with the argument block filled from tensors (None = NULL)."""
+        ptr = lambda t: (t.data_ptr() if t is not None else None)
+        a = LinearArgs(dtype, out_dtype, ptr(A), ptr(A2), lda or K, ptr(W), ptr(W2), ptr(bias), ptr(residual), ldr or N, M, N, K,
+                       epilogue, ptr(out), ptr(out_lo), ldo or N)
+        self.check(lib().ttb_linear_ex(self.h, C.byref(a)))
 
     def device_status(self):
         return lib().ttb_device_status(self.h)

@@ -430,6 +430,61 @@ quantize_rows_kernel(const T* __restrict__ x, int64_t M, int K, int8_t* __restri
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Per-tensor affine 7-bit quantisation of activations (torch's dynamic quantisation with reduce_range): a running
+// minimum / maximum over the whole tensor, then q = clamp(rint(zp + x * (1 / scale)), 0, 127).
+// qparams: [0] scale, [1] zero point (as a float), [2] / [3] minimum / maximum as order-preserving integers.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ int float_to_ordered(float f) {
+  const int i = __float_as_int(f);
+  return i >= 0 ? i : i ^ 0x7fffffff;
+}
+__device__ __forceinline__ float ordered_to_float(int i) { return __int_as_float(i >= 0 ? i : i ^ 0x7fffffff); }
+
+__global__ void affine_range_init_kernel(float* qparams) {
+  // the quantised range always contains zero, so zero is the starting point of both ends
+  reinterpret_cast<int*>(qparams)[2] = float_to_ordered(0.f);
+  reinterpret_cast<int*>(qparams)[3] = float_to_ordered(0.f);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) affine_range_kernel(const T* __restrict__ x, int64_t n, float* qparams) {
+  float mn = 0.f, mx = 0.f;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float v = to_f(x[i]);
+    mn = fminf(mn, v);
+    mx = fmaxf(mx, v);
+  }
+  mx = warp_max(mx);
+  mn = -warp_max(-mn);
+  if ((threadIdx.x & 31) == 0) {
+    atomicMin(reinterpret_cast<int*>(qparams) + 2, float_to_ordered(mn));
+    atomicMax(reinterpret_cast<int*>(qparams) + 3, float_to_ordered(mx));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) affine_quantize_kernel(const T* __restrict__ x, int64_t n, int8_t* __restrict__ xq, float* qparams) {
+  const double mn = (double)ordered_to_float(reinterpret_cast<const int*>(qparams)[2]);
+  const double mx = (double)ordered_to_float(reinterpret_cast<const int*>(qparams)[3]);
+  double scale = (mx - mn) / 127.0;
+  if ((float)scale == 0.f || isinf(1.0f / (float)scale)) scale = 0.1;
+  const double zp_from_min = 0.0 - mn / scale, zp_from_max = 127.0 - mx / scale;
+  const double err_min = 0.0 - fabs(mn / scale), err_max = 127.0 - fabs(mx / scale);
+  double zpd = err_min < err_max ? zp_from_min : zp_from_max;
+  zpd = zpd < 0.0 ? 0.0 : (zpd > 127.0 ? 127.0 : rint(zpd));
+  const float fscale = (float)scale, inv = 1.0f / fscale, zp = (float)zpd;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    qparams[0] = fscale;
+    qparams[1] = zp;
+  }
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    // two separately rounded operations, as the CPU code does them (no fused multiply-add)
+    const float q = rintf(__fadd_rn(zp, __fmul_rn(to_f(x[i]), inv)));
+    xq[i] = (int8_t)fminf(fmaxf(q, 0.f), 127.f);
+  }
+}
+
 }  // namespace
 
 // =================================================================================================
@@ -671,6 +726,24 @@ extern "C" int ttb_quantize_rows_int8(ttb_ctx* ctx, int dtype, const void* x, in
   TTB_DISPATCH_FLOAT(ctx, dtype, T,
                      (quantize_rows_kernel<T><<<grid, kRowsPerBlock * 32, 0, ctx->stream>>>((const T*)x, M, (int)K, xq, row_scale)));
   return launched(ctx, "quantize_rows_int8");
+}
+
+extern "C" int ttb_quantize_tensor_affine(ttb_ctx* ctx, int dtype, const void* x, int64_t M, int64_t K, int8_t* xq, float* qparams) {
+  if (!ctx) return TTB_ERR_INVALID;
+  TTB_REQUIRE(ctx, M >= 0 && K > 0, "quantize_tensor_affine: bad shape");
+  if (M == 0) return TTB_OK;
+  TTB_REQUIRE(ctx, x && xq && qparams, "quantize_tensor_affine: null pointer");
+  DeviceGuard g(ctx->device);
+  const int64_t n = M * K;
+  const int64_t want = (n + 255) / 256;
+  const int grid = (int)(want < (int64_t)ctx->sm_count * 8 ? want : (int64_t)ctx->sm_count * 8);
+  affine_range_init_kernel<<<1, 1, 0, ctx->stream>>>(qparams);
+  TTB_DISPATCH_FLOAT(ctx, dtype, T, {
+    affine_range_kernel<T><<<grid, 256, 0, ctx->stream>>>((const T*)x, n, qparams);
+    affine_quantize_kernel<T><<<grid, 256, 0, ctx->stream>>>((const T*)x, n, xq, qparams);
+  });
+  ctx->launches.fetch_add(2);
+  return launched(ctx, "quantize_tensor_affine");
 }
 
 extern "C" int ttb_build_cu_seqlens(ttb_ctx* ctx, const int64_t* host_seq_lens, int64_t B, int32_t* cu_dev) {

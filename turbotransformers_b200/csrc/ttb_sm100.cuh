@@ -38,14 +38,41 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false (and the CTA-wide abort flag raised) when the limit expires or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// Bounded wait: false (and the CTA-wide abort flag raised) when `limit` SM cycles pass or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, long long limit = kWaitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycles) {
+    if (clock64() - t0 > limit) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+// The same wait with acquire semantics at cluster scope: pairs with release.cluster arrivals of other CTAs of the cluster
+// whose writes into this CTA's shared memory must be visible afterwards.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, long long limit = kWaitCycles) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > limit) {
       *abort_flag = 1;
       return false;
     }
@@ -58,6 +85,53 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
       "l"(map), "r"(bar), "r"(x), "r"(y)
       : "memory");
+}
+
+// TMA store of a [rows x 128 B] swizzled shared-memory tile; rows / columns outside the tensor are clipped by the
+// hardware. Completion is tracked per issuing thread in bulk groups.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
+
+// ---- clusters: CTA pairs (cta_group::2) and shared memory of other CTAs of the cluster ----------------------------
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared-window address: "same offset in CTA 0"
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory offset in CTA `target_rank` of the cluster (shared::cluster window).
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t target_rank) {
+  uint32_t ra;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_addr), "r"(target_rank));
+  return ra;
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t local_bar, uint32_t target_rank) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(map_to_rank(local_bar, target_rank)) : "memory");
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+// Tile load issued by either CTA of a pair into its own shared memory; the bytes are counted on CTA 0's barrier.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(map), "r"(bar & kPeerBitMask), "r"(x), "r"(y)
+      : "memory");
+}
+// Arrives (once the MMAs issued so far have completed) on the barrier at this offset in both CTAs of the pair.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(mask)
+               : "memory");
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -108,6 +182,38 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
 __device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr) { return ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16); }
 
+// Operand kinds of the generic MMA wrapper below.
+enum { KIND_F16 = 0, KIND_BF16 = 1, KIND_I8 = 2, KIND_TF32 = 3 };
+
+// D[tmem] (+)= A[smem] * B[smem] for any kind, by one CTA (TWO = false) or a CTA pair (cta_group::2). Both descriptors are
+// given as their low words; the high word is the constant of the 128-byte-swizzled K-major layout.
+template <int KIND, bool TWO>
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+#define TTB_UMMA_ASM(GROUP, KINDSTR)                                                        \
+  asm volatile(                                                                             \
+      "{\n"                                                                                 \
+      ".reg .pred p;\n"                                                                     \
+      ".reg .b64 da, db;\n"                                                                 \
+      "setp.ne.b32 p, %5, 0;\n"                                                             \
+      "mov.b64 da, {%1, %3};\n"                                                             \
+      "mov.b64 db, {%2, %3};\n"                                                             \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KINDSTR " [%0], da, db, %4, p;\n"           \
+      "}\n" ::"r"(d_tmem),                                                                  \
+      "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(accumulate)                       \
+      : "memory")
+  if (KIND == KIND_I8) {
+    if (TWO) TTB_UMMA_ASM("2", "i8");
+    else TTB_UMMA_ASM("1", "i8");
+  } else if (KIND == KIND_TF32) {
+    if (TWO) TTB_UMMA_ASM("2", "tf32");
+    else TTB_UMMA_ASM("1", "tf32");
+  } else {
+    if (TWO) TTB_UMMA_ASM("2", "f16");
+    else TTB_UMMA_ASM("1", "f16");
+  }
+#undef TTB_UMMA_ASM
+}
+
 // D[tmem] (+)= A[smem] * B[smem], 16-bit inputs, fp32 accumulate; one thread issues.
 __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -154,8 +260,8 @@ __host__ __device__ constexpr uint32_t idesc_f16(int fmt, int M, int N, int b_mn
 namespace ttb {
 namespace sm100 {
 
-// Encodes a 2-D row-major tensor map [rows, cols] of 16-bit (elem_bytes = 2) or 8-bit elements with `ld_elems`
-// between rows, box = [box_rows, 128 bytes], 128-byte swizzle, zero fill outside the tensor. Returns false when
+// Encodes a 2-D row-major tensor map [rows, cols] of 32-bit (elem_bytes = 4, fp32), 16-bit (elem_bytes = 2) or 8-bit
+// elements with `ld_elems` between rows, box = [box_rows, 128 bytes], 128-byte swizzle, zero fill outside the tensor. Returns false when
 // the driver entry point is missing or rejects the arguments.
 inline bool encode_tile_map(CUtensorMap* map, const void* ptr, int elem_bytes, bool bf16, uint64_t rows, uint64_t cols,
                             uint64_t ld_elems, uint32_t box_rows) {
@@ -170,7 +276,8 @@ inline bool encode_tile_map(CUtensorMap* map, const void* ptr, int elem_bytes, b
   }();
   if (!fn) return false;
   const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
-                                                 : (bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+                                 : elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                   : (bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {ld_elems * (uint64_t)elem_bytes};
   cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), box_rows};
