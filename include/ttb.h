@@ -53,6 +53,9 @@ typedef enum {
 int ttb_ctx_create(int device, void* cuda_stream /* cudaStream_t; NULL = the legacy default stream */,
                    ttb_ctx** out);
 int ttb_ctx_destroy(ttb_ctx* ctx);
+/* Work queued after the call runs on `cuda_stream`, ordered after everything queued through the context before it (the new
+ * stream waits for an event on the old one). A context serves one stream at a time: host threads that want different streams
+ * at the same time use one context each. */
 int ttb_ctx_set_stream(ttb_ctx* ctx, void* cuda_stream);
 void* ttb_ctx_stream(ttb_ctx* ctx);
 int ttb_ctx_device(ttb_ctx* ctx);
@@ -80,13 +83,15 @@ int ttb_pool_set_limit(ttb_ctx* ctx, size_t bytes);
 /* Arena mode: between ttb_arena_begin and ttb_arena_end every ttb_alloc is served from one buffer reserved up front, at
  * increasing 256-byte-aligned offsets, without any driver call; ttb_free of such a pointer does nothing, then or later. A
  * forward pass run this way places every temporary and its outputs at fixed addresses, which is what capturing that pass into
- * a CUDA graph needs (the graph's kernels keep using the arena at every replay, so outputs are valid until the next replay or
- * ttb_arena_begin). No reference counterpart: the reference's model-aware allocator (allocator_api.cpp:112-125) served the
- * same purpose of a driver-call-free forward. ttb_arena_begin re-uses the previous arena when it is large enough.
+ * a CUDA graph needs (the graph's kernels keep using the arena at every replay, so outputs are valid until the next replay).
+ * Every ttb_arena_begin reserves a buffer of its own, so graphs captured earlier keep theirs. ttb_arena_end hands the buffer
+ * to the caller (*arena_out, may be NULL to leave it with the context until ttb_ctx_destroy); ttb_arena_release frees it once
+ * nothing replays over it any more (it waits for the device first). No reference counterpart: the reference's model-aware
+ * allocator (allocator_api.cpp:112-125) served the same purpose of a driver-call-free forward.
  * ttb_bytes_allocated_total: sum of all ttb_alloc sizes so far; its increase over one forward pass sizes the arena. */
 int ttb_arena_begin(ttb_ctx* ctx, size_t bytes);
-int ttb_arena_end(ttb_ctx* ctx, size_t* bytes_used);
-int ttb_arena_release(ttb_ctx* ctx);
+int ttb_arena_end(ttb_ctx* ctx, size_t* bytes_used, void** arena_out);
+int ttb_arena_release(ttb_ctx* ctx, void* arena);
 int ttb_bytes_allocated_total(ttb_ctx* ctx, uint64_t* bytes);
 /* Model-aware plan: replaces bert_opt_mem_allocate_api (core/allocator/allocator_api.cpp:112-125,
  * bert_config.cpp:43-94): computes one arena size for a BERT forward of this shape and reserves it in the
@@ -148,6 +153,12 @@ int ttb_add_bias_layernorm(ttb_ctx* ctx, int dtype, void* out, const void* input
 /* ---- A7: kernels::LayerNorm (layer_norm.cpp:32-91): in place. `in` may equal `out`. ---- */
 int ttb_layernorm(ttb_ctx* ctx, int dtype, const void* in, void* out, const void* gamma, const void* beta,
                   int64_t M, int64_t N, float eps);
+/* LayerNorm for models that keep more precision between layers than their 16-bit dtype holds (no reference counterpart:
+ * the reference is fp32 throughout). `in` is of out_dtype or F32 (an fp32 residual stream); out (out_dtype) is the
+ * operand of the next GEMM; out_lo (out_dtype, may be NULL) receives y - round(y), the second activation plane of
+ * ttb_linear_ex; out_f32 (may be NULL) the unrounded value, the residual of the next block. */
+int ttb_layernorm_planes(ttb_ctx* ctx, int in_dtype, int out_dtype, const void* in, void* out, void* out_lo, float* out_f32,
+                         const void* gamma, const void* beta, int64_t M, int64_t N, float eps);
 /* ---- A8: kernels::AddBiasAct (activation.cpp:90-119): in-place act(out + bias). ---- */
 int ttb_add_bias_act(ttb_ctx* ctx, int dtype, void* out, const void* bias, int64_t M, int64_t N, int act);
 /* ---- A9: kernels::LookupEmbedding (embedding.cpp:28-85): out[i,:] (=|+=) table[ids[i],:]. An id outside
@@ -302,9 +313,26 @@ int ttb_embedding_ln(ttb_ctx* ctx, int dtype, const int64_t* ids, const int64_t*
                      const void* gamma, const void* beta, int64_t hidden, int64_t vocab, int64_t n_positions,
                      int64_t n_types, float eps, void* out);
 
+/* ttb_embedding_ln with the two extra outputs of ttb_layernorm_planes (either may be NULL). */
+int ttb_embedding_ln_planes(ttb_ctx* ctx, int dtype, const int64_t* ids, const int64_t* position_ids,
+                            const int64_t* token_type_ids, const int32_t* cu_seqlens, int64_t B, int64_t seq_len,
+                            int64_t n_tokens, const void* word, const void* position, const void* token_type,
+                            const void* gamma, const void* beta, int64_t hidden, int64_t vocab, int64_t n_positions,
+                            int64_t n_types, float eps, void* out, void* out_lo, float* out_f32);
+
 /* cu_seqlens (device int32 [B+1]) from host sequence lengths; a helper for callers that hold the
- * reference's `query_seq_len_list` host vector (multi_headed_attention_smart_batch.h:60-75). */
+ * reference's `query_seq_len_list` host vector (multi_headed_attention_smart_batch.h:60-75). Asynchronous on the
+ * context's stream for B <= 960 (the lengths ride in the kernel's parameters); larger batches take a staging copy that the
+ * call waits for. */
 int ttb_build_cu_seqlens(ttb_ctx* ctx, const int64_t* host_seq_lens, int64_t B, int32_t* cu_seqlens_device);
+
+/* Self-test of the bounded device-side waits that every tensor-core kernel's hang safety rests on (no reference
+ * counterpart). Launches one small kernel in which a thread waits, for at most `limit_cycles` SM cycles (<= 1e8, a
+ * twentieth of a second), on a barrier that nothing arrives at. The wait gives up by itself; the kernel then records
+ * TTB_ERR_DEVICE_WAIT in the status word, which the next ttb_device_status returns (and clears).
+ * observed (device int32 [3]): whether the wait reported completion (0 expected), the abort flag (1 expected), and the
+ * time the wait took in units of 1024 cycles. */
+int ttb_selftest_bounded_wait(ttb_ctx* ctx, int64_t limit_cycles, int32_t* observed_device);
 
 #ifdef __cplusplus
 }

@@ -199,6 +199,55 @@ class RefBert:
         return back(h)
 
 
+class RefQBertRecipe:
+    """The reference's int8 recipe, layer by layer (python/turbo_transformers/layers/qmodeling_bert.py:13-45,158-192):
+    torch dynamic quantisation of the two feed-forward Linears with the bias stripped, the bias re-applied by the compiled
+    reference's FusedAddBiasGELU / FusedAddBiasLayerNorm, attention through its fp32 BertAttention."""
+
+    def __init__(self, hf_model):
+        import warnings
+        cxx = load()
+        W = pack_bert_weights(hf_model)
+        self.ref = RefBert(W, hf_model.config.num_attention_heads)
+        self.layers = []
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            for l in hf_model.encoder.layer:
+                qi = torch.quantization.quantize_dynamic(l.intermediate, {torch.nn.Linear}, dtype=torch.qint8)
+                qo = torch.quantization.quantize_dynamic(l.output, {torch.nn.Linear}, dtype=torch.qint8)
+                wi, _ = qi.dense._weight_bias()
+                qi.dense.set_weight_bias(wi, None)
+                wo, _ = qo.dense._weight_bias()
+                qo.dense.set_weight_bias(wo, None)
+                gelu = cxx.FusedAddBiasGELU(T(l.intermediate.dense.bias))
+                lnorm = cxx.FusedAddBiasLayerNorm(T(l.output.dense.bias), T(l.output.LayerNorm.weight), T(l.output.LayerNorm.bias))
+                self.layers.append((qi.dense, qo.dense, gelu, lnorm))
+
+    def embed(self, ids):
+        """int64 ids [B, L] -> (embedding output as torch fp32 [B, L, H], the additive mask tensor for layer())."""
+        h, ext = self.ref.embed(torch.as_tensor(ids, dtype=torch.int64))
+        return back(h).clone(), ext
+
+    def layer(self, i, h, ext):
+        """One encoder layer of the recipe on the torch fp32 hidden states h."""
+        att = self.ref.layers[i][0]
+        qi, qo, gelu, lnorm = self.layers[i]
+        ao, ap = E(), E()
+        att(T(h), ext, ao, ap, False)
+        a = back(ao).clone()
+        inter = T(qi(a))
+        gelu(inter)
+        out = T(qo(back(inter).clone()))
+        lnorm(T(a), out)
+        return back(out).clone()
+
+    def forward(self, ids):
+        h, ext = self.embed(ids)
+        for i in range(len(self.layers)):
+            h = self.layer(i, h, ext)
+        return h
+
+
 def context_attention_weights(hidden, seed=0):
     """Seeded fp32 weights of one attention layer in the layout restate.context_attention takes ([in,out] matrices)."""
     r = np.random.default_rng(seed)

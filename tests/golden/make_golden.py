@@ -78,32 +78,10 @@ def qbert_reference_recipe(name, model_name, seed, batch, seq_len):
     """The reference's own int8 recipe (python/turbo_transformers/layers/qmodeling_bert.py:13-45,158-192):
     torch dynamic quantisation of the two feed-forward Linears with the bias stripped, the bias re-applied by
     the reference's native FusedAddBiasGELU / FusedAddBiasLayerNorm, fp32 attention."""
-    import torch.utils.dlpack as dlpack
     hf = synthetic.make_hf_bert(model_name, seed)
-    W = ref_driver.pack_bert_weights(hf)
-    cxx = ref_driver.load()
-    T, E, back = ref_driver.T, ref_driver.E, ref_driver.back
-    ref = ref_driver.RefBert(W, hf.config.num_attention_heads)
     ids = synthetic.random_ids(batch, seq_len, hf.config.vocab_size, seed)
-    h, ext = ref.embed(ids)
-    for (att, _, _), l in zip(ref.layers, hf.encoder.layer):
-        qi = torch.quantization.quantize_dynamic(l.intermediate, {torch.nn.Linear}, dtype=torch.qint8)
-        qo = torch.quantization.quantize_dynamic(l.output, {torch.nn.Linear}, dtype=torch.qint8)
-        wi, _ = qi.dense._weight_bias()
-        qi.dense.set_weight_bias(wi, None)
-        wo, _ = qo.dense._weight_bias()
-        qo.dense.set_weight_bias(wo, None)
-        gelu = cxx.FusedAddBiasGELU(T(l.intermediate.dense.bias))
-        lnorm = cxx.FusedAddBiasLayerNorm(T(l.output.dense.bias), T(l.output.LayerNorm.weight), T(l.output.LayerNorm.bias))
-        ao, ap = E(), E()
-        att(h, ext, ao, ap, False)
-        a = back(ao).clone()
-        inter = T(qi.dense(a))
-        gelu(inter)
-        out = T(qo.dense(back(inter)))
-        lnorm(T(a), out)
-        h = out
-    save(name, model=model_name, seed=seed, ids=ids.numpy(), sequence_output=back(h).numpy())
+    h = ref_driver.RefQBertRecipe(hf).forward(ids)
+    save(name, model=model_name, seed=seed, ids=ids.numpy(), sequence_output=h.numpy())
 
 
 if __name__ == "__main__":

@@ -107,7 +107,9 @@ def test_stepwise_decoding_reproduces_the_full_sequence_pass_fp16():
         h = x[:, t:t + 1].contiguous()
         for layer, cache in zip(layers, caches):
             h, attn, _ = layer(h, mem, src_pad, tgt_pad[:, :, t:t + 1], layer_cache=cache, step=t)
-        assert (h[:, 0].float() - full[:, t].float()).abs().max().item() < 2e-2, t
+        # the pre-LN residual stream is not normalised: its values reach ten and more, where an fp16 step is 0.008, and the
+        # one-token GEMMs (split along K over a cluster) round in another order than the full-sequence ones
+        assert (h[:, 0].float() - full[:, t].float()).abs().max().item() < 4e-2, t
         assert (attn[:, 0].float() - full_attn[:, t].float()).abs().max().item() < 1e-2
     assert tuple(caches[0]["memory_keys"].shape) == (B, heads, Ls, H // heads)
     assert caches[0]["self_keys"].shape(0) == Lt  # the in-place cache holds every decoded position

@@ -328,3 +328,25 @@ def test_allocator_pool_contract(ctx):
     arena = C.c_size_t()
     assert lib.ttb_plan_activations(ctx.h, 1, 128, 12, 768, 3072, 12, _capi.F16, C.byref(arena)) == _capi.OK
     assert arena.value >= 128 * (7 * 768 + 3072) * 2
+
+
+def test_bounded_device_wait_gives_up_and_is_reported(ctx):
+    """The mbarrier waits of the tensor-core kernels are bounded; here one is made to run out (a barrier nothing arrives
+    at, a limit of about a millisecond). It must return by itself with the abort flag set, and the status word must carry
+    TTB_ERR_DEVICE_WAIT until it is read."""
+    assert ctx.device_status() == _capi.OK
+    observed = torch.full((3,), -1, dtype=torch.int32, device="cuda")
+    limit = 1_000_000
+    ctx.call("selftest_bounded_wait", limit, observed)
+    status = ctx.device_status()           # synchronises: the kernel has returned
+    completed, aborted, kcycles = observed.cpu().tolist()
+    assert completed == 0 and aborted == 1
+    assert limit // 1024 <= kcycles < 50 * limit // 1024   # it waited out its limit and not much more
+    assert status == _capi.ERR_DEVICE_WAIT
+    assert b"bounded device-side wait" in _capi.lib().ttb_last_error(ctx.h)
+    assert ctx.device_status() == _capi.OK  # reading the status cleared it; the context stays usable
+    x = torch.ones(4, 8, device="cuda", dtype=torch.float16)
+    ctx.call("add_bias", _capi.F16, x, torch.ones(8, device="cuda", dtype=torch.float16), 4, 8)
+    assert float(x.sum().item()) == 64.0
+    with pytest.raises(_capi.TTBError):
+        ctx.call("selftest_bounded_wait", 10**10, observed)  # limits beyond a twentieth of a second are refused

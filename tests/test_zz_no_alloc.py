@@ -70,4 +70,13 @@ def test_noalloc_rejects_problems_beyond_its_scratch(ctx):
     assert lib.ttb_linear_int8_dynamic_noalloc(ctx.h, _capi.F16, P(x), P(x), P(x), None, None, 0, 70000, 768, 16, 0, P(x), 768) \
         == _capi.ERR_INVALID
     assert ctx.launches() == before
+    # every other invalid argument is also refused before the quantising kernel could overwrite the shared array:
+    # K not a multiple of 16, an fp32 activation dtype, an epilogue without its bias, an output pitch below N, a null weight
+    for args in ((_capi.F16, P(x), P(x), P(x), None, None, 0, 8, 8, 24, 0, P(x), 8),
+                 (_capi.F32, P(x), P(x), P(x), None, None, 0, 8, 8, 16, 0, P(x), 8),
+                 (_capi.F16, P(x), P(x), P(x), None, None, 0, 8, 8, 16, _capi.EPI_BIAS, P(x), 8),
+                 (_capi.F16, P(x), P(x), P(x), None, None, 0, 8, 16, 16, 0, P(x), 8),
+                 (_capi.F16, P(x), None, P(x), None, None, 0, 8, 8, 16, 0, P(x), 8)):
+        assert lib.ttb_linear_int8_dynamic_noalloc(ctx.h, *args) == _capi.ERR_INVALID
+    assert ctx.launches() == before
     assert lib.ttb_linear_int8_dynamic_noalloc(ctx.h, _capi.F16, P(x), P(x), P(x), None, None, 0, 0, 768, 16, 0, P(x), 768) == _capi.OK

@@ -46,8 +46,8 @@ SIGNATURES = {
     "ttb_memcpy_d2h": (i32, [p, p, p, sz]),
     "ttb_copy_2d": (i32, [p, p, sz, p, sz, sz, sz]),
     "ttb_arena_begin": (i32, [p, sz]),
-    "ttb_arena_end": (i32, [p, p]),
-    "ttb_arena_release": (i32, [p]),
+    "ttb_arena_end": (i32, [p, p, p]),
+    "ttb_arena_release": (i32, [p, p]),
     "ttb_bytes_allocated_total": (i32, [p, p]),
     "ttb_kv_cache_append": (i32, [p, i32, p, i64, i64, i64, i64, p, p, i64]),
     "ttb_attention_decode": (i32, [p, i32, p, i64, i64, i64, i64, p, p, i64, f32, p]),
@@ -62,6 +62,8 @@ SIGNATURES = {
     "ttb_mask_softmax": (i32, [p, i32, p, p, i64, i64, i64, i64, f32, i32]),
     "ttb_add_bias_layernorm": (i32, [p, i32, p, p, p, p, p, i64, i64, f32]),
     "ttb_layernorm": (i32, [p, i32, p, p, p, p, i64, i64, f32]),
+    "ttb_layernorm_planes": (i32, [p, i32, i32, p, p, p, p, p, p, i64, i64, f32]),
+    "ttb_embedding_ln_planes": (i32, [p, i32, p, p, p, p, i64, i64, i64, p, p, p, p, p, i64, i64, i64, i64, f32, p, p, p]),
     "ttb_add_bias_act": (i32, [p, i32, p, p, i64, i64, i32]),
     "ttb_lookup_embedding": (i32, [p, i32, p, p, p, i64, i64, i64, i32]),
     "ttb_add_bias": (i32, [p, i32, p, p, i64, i64]),
@@ -83,6 +85,7 @@ SIGNATURES = {
     "ttb_attention_fwd": (i32, [p, i32, p, i64, p, i64, i64, i64, i64, p, i64, i64, i32, f32, p]),
     "ttb_embedding_ln": (i32, [p, i32, p, p, p, p, i64, i64, i64, p, p, p, p, p, i64, i64, i64, i64, f32, p]),
     "ttb_build_cu_seqlens": (i32, [p, p, i64, p]),
+    "ttb_selftest_bounded_wait": (i32, [p, i64, p]),
 }
 
 _lib = None

@@ -15,7 +15,7 @@ namespace {
 constexpr int kMaxDevices = 64;
 std::mutex g_mu;
 ttb_ctx* g_ctx[kMaxDevices] = {};
-std::map<std::vector<int64_t>, int32_t*> g_cu_cache[kMaxDevices];
+std::map<std::vector<int64_t>, CuSeqlensHandle> g_cu_cache[kMaxDevices];
 int g_num_threads = 1;
 
 struct Managed {
@@ -60,24 +60,29 @@ void Check(int status, ttb_ctx* ctx, const char* what) {
   TT_THROW("%s failed with status %d: %s", what, status, ctx ? ttb_last_error(ctx) : "");
 }
 
-const int32_t* CuSeqlens(int device_id, const std::vector<int64_t>& seq_lens) {
+CuSeqlensHandle CuSeqlens(int device_id, const std::vector<int64_t>& seq_lens) {
   ttb_ctx* c = DeviceContext(device_id);
-  std::lock_guard<std::mutex> g(g_mu);
-  auto& cache = g_cu_cache[device_id];
-  auto it = cache.find(seq_lens);
-  if (it != cache.end()) return it->second;
-  if (cache.size() >= 256) {  // stream-ordered frees: kernels already queued keep their arrays
-    for (auto& kv : cache) ttb_free(c, kv.second, "cu_seqlens");
-    cache.clear();
+  std::vector<CuSeqlensHandle> evicted;  // released after the lock is dropped (the last release frees device memory)
+  CuSeqlensHandle h;
+  {
+    std::lock_guard<std::mutex> g(g_mu);
+    auto& cache = g_cu_cache[device_id];
+    auto it = cache.find(seq_lens);
+    if (it != cache.end()) return it->second;
+    if (cache.size() >= 256) {  // arrays still held by a caller outlive this: only the cache's references go
+      for (auto& kv : cache) evicted.push_back(std::move(kv.second));
+      cache.clear();
+    }
+    void* p = nullptr;
+    Check(ttb_alloc(c, (seq_lens.size() + 1) * sizeof(int32_t), "cu_seqlens", &p), c, "alloc cu_seqlens");
+    h = CuSeqlensHandle(static_cast<const int32_t*>(p), [c](const int32_t* q) { ttb_free(c, const_cast<int32_t*>(q), "cu_seqlens"); });
+    Check(ttb_build_cu_seqlens(c, seq_lens.data(), (int64_t)seq_lens.size(), static_cast<int32_t*>(p)), c, "build_cu_seqlens");
+    cache[seq_lens] = h;
   }
-  void* p = nullptr;
-  Check(ttb_alloc(c, (seq_lens.size() + 1) * sizeof(int32_t), "cu_seqlens", &p), c, "alloc cu_seqlens");
-  Check(ttb_build_cu_seqlens(c, seq_lens.data(), (int64_t)seq_lens.size(), static_cast<int32_t*>(p)), c, "build_cu_seqlens");
-  cache[seq_lens] = static_cast<int32_t*>(p);
-  return static_cast<int32_t*>(p);
+  return h;
 }
 
-const int32_t* UniformCuSeqlens(int device_id, int64_t B, int64_t L) {
+CuSeqlensHandle UniformCuSeqlens(int device_id, int64_t B, int64_t L) {
   return CuSeqlens(device_id, std::vector<int64_t>((size_t)B, L));
 }
 
@@ -134,6 +139,7 @@ DLManagedTensor* NewDLPackTensor(const std::vector<int64_t>& shape, DLDeviceType
 }
 
 void Tensor::Release() {
+  extras_.reset();
   if (owned_ && owned_->deleter) owned_->deleter(owned_);
   owned_ = nullptr;
   is_view_ = false;
@@ -148,6 +154,7 @@ void Tensor::MoveFrom(Tensor& o) {
   const bool own_shape = !o.view_shape_.empty() && o.view_.shape == o.view_shape_.data();
   view_shape_ = std::move(o.view_shape_);
   if (own_shape) view_.shape = view_shape_.data();
+  extras_ = std::move(o.extras_);
   o.owned_ = nullptr;
   o.is_view_ = false;
   o.view_ = DLTensor{};
@@ -180,6 +187,7 @@ void* Tensor::Reshape(DLDataType dtype, const std::vector<int64_t>& shape, DLDev
   int64_t n = 1;
   for (int64_t d : shape) n *= d;
   const size_t need = (size_t)n * ElemBytes(dtype);
+  extras_.reset();  // the contents are about to be replaced
   if (owned_ && owned_->deleter == ManagedDeleter) {
     auto* m = static_cast<Managed*>(owned_->manager_ctx);
     if (m->capacity >= need && view_.device.device_type == dev && view_.device.device_id == dev_id) {
@@ -234,6 +242,29 @@ Tensor Tensor::operator[](int64_t n) const {
   t.view_.byte_offset = view_.byte_offset + (uint64_t)(n * inner) * ElemBytes(view_.dtype);
   return t;
 }
+
+// ---------------------------------------------------------------------------------------------------
+// precision switches
+// ---------------------------------------------------------------------------------------------------
+namespace {
+int g_precise_bf16 = -1, g_fp32_tc = -1;  // -1: not decided yet (environment)
+}
+bool PreciseBF16() {
+  if (g_precise_bf16 < 0) {
+    const char* e = std::getenv("TTB_BF16_PRECISE");
+    g_precise_bf16 = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_precise_bf16 != 0;
+}
+void SetPreciseBF16(bool on) { g_precise_bf16 = on ? 1 : 0; }
+bool Fp32TensorCores() {
+  if (g_fp32_tc < 0) {
+    const char* e = std::getenv("TTB_FP32_GEMM");
+    g_fp32_tc = (e && std::string(e) == "simt") ? 0 : 1;
+  }
+  return g_fp32_tc != 0;
+}
+void SetFp32TensorCores(bool on) { g_fp32_tc = on ? 1 : 0; }
 
 // ---------------------------------------------------------------------------------------------------
 // module-level API

@@ -61,10 +61,13 @@ void SetDeviceStream(int device_id, void* cuda_stream);
 // Throws EnforceNotMet carrying ttb_last_error when `status` is not TTB_OK.
 void Check(int status, ttb_ctx* ctx, const char* what);
 // A device int32 [B+1] prefix-sum array for these sequence lengths; cached per device, so the 12 layers
-// of one forward (and repeated shapes) share one upload.
-const int32_t* CuSeqlens(int device_id, const std::vector<int64_t>& seq_lens);
+// of one forward (and repeated shapes) share one table. The caller holds the handle until it has queued the last kernel
+// that reads the array: eviction from the cache only drops the cache's own reference, and the array goes back to the
+// pool (stream ordered) when the last holder lets go.
+using CuSeqlensHandle = std::shared_ptr<const int32_t>;
+CuSeqlensHandle CuSeqlens(int device_id, const std::vector<int64_t>& seq_lens);
 // Same for B equal sequences of length L.
-const int32_t* UniformCuSeqlens(int device_id, int64_t B, int64_t L);
+CuSeqlensHandle UniformCuSeqlens(int device_id, int64_t B, int64_t L);
 
 // ---- dtype helpers --------------------------------------------------------------------------------
 template <typename T> struct DataTypeTrait;
@@ -80,6 +83,17 @@ int ToTTBDtype(DLDataType dt);
 
 DLManagedTensor* NewDLPackTensor(const std::vector<int64_t>& shape, DLDeviceType device, int device_id, DLDataType dtype,
                                  const std::string& name);
+
+// Whether bf16 models keep an fp32 residual stream and hi + lo activation planes between their layers (default on;
+// TTB_BF16_PRECISE=0 or SetPreciseBF16(false) selects plain bf16 storage, which is faster and 8 bits accurate).
+bool PreciseBF16();
+void SetPreciseBF16(bool on);
+// Whether fp32 models run their Linears on the tensor cores as three tf32 products (default on; TTB_FP32_GEMM=simt or
+// SetFp32TensorCores(false) selects the exact-order CUDA-core GEMM).
+bool Fp32TensorCores();
+void SetFp32TensorCores(bool on);
+
+struct TensorExtras;
 
 class Tensor {
  public:
@@ -136,6 +150,15 @@ class Tensor {
   // Non-owning view of sub-tensor n along the first axis.
   Tensor operator[](int64_t n) const;
 
+  // Companion planes a layer may attach to a 16-bit activation it produced, for the next layer to use (they travel with
+  // the tensor through moves, and are dropped when it is reshaped or exported):
+  //   lo  : same shape and dtype, what rounding to the 16-bit type dropped (value = this + lo to 16 significant bits)
+  //   f32 : same shape in fp32, the unrounded value (the residual stream of a bf16 model)
+  const Tensor* lo() const;
+  const Tensor* f32() const;
+  TensorExtras& NewExtras();
+  void DropExtras() { extras_.reset(); }
+
  private:
   void Release();
   void MoveFrom(Tensor& o);
@@ -143,7 +166,19 @@ class Tensor {
   DLTensor view_{};      // what the accessors read; for an owning tensor a copy of owned_->dl_tensor
   bool is_view_ = false;
   std::vector<int64_t> view_shape_;  // backing store of view_.shape for views and re-shaped tensors
+  std::shared_ptr<TensorExtras> extras_;
 };
+
+struct TensorExtras {
+  Tensor lo{nullptr};
+  Tensor f32{nullptr};
+};
+inline const Tensor* Tensor::lo() const { return extras_ && !extras_->lo.is_null() ? &extras_->lo : nullptr; }
+inline const Tensor* Tensor::f32() const { return extras_ && !extras_->f32.is_null() ? &extras_->f32 : nullptr; }
+inline TensorExtras& Tensor::NewExtras() {
+  extras_ = std::make_shared<TensorExtras>();
+  return *extras_;
+}
 
 // ---- module-level API of the reference kept for scripts that call it --------------------------------
 void SetNumThreads(int n);  // host threads are not used by the device path; recorded only

@@ -38,6 +38,28 @@ std::vector<int64_t> WithLast(const Tensor& t, int64_t last) {
   return s;
 }
 
+// bf16 models in their precise mode: activations travel as a bf16 value plus a lo plane (what the rounding dropped) and,
+// for the residual stream, an fp32 copy; see core::Tensor::lo() / f32().
+bool PreciseMode(int dt) { return dt == TTB_BF16 && core::PreciseBF16(); }
+
+// out = LN(in) with the companion planes attached to `out` (already reshaped to its 16-bit shape). `in` is fp32 when
+// in_f32, else of out's dtype.
+void LayerNormPlanes(ttb_ctx* c, bool in_f32, const void* in, Tensor* out, const Tensor& gamma, const Tensor& beta, int64_t M, int64_t N,
+                     float eps, bool want_f32, const char* name) {
+  const int dt = core::ToTTBDtype(out->dtype());
+  const auto shape = ShapeOf(*out);
+  void* out_ptr = out->raw_mut();
+  core::TensorExtras& ex = out->NewExtras();
+  void* lo = ex.lo.Reshape(out->dtype(), shape, kDLCUDA, out->device_id(), "precise/lo_plane");
+  float* f32 = want_f32 ? ex.f32.Reshape<float>(shape, kDLCUDA, out->device_id(), "precise/residual_stream") : nullptr;
+  Check(ttb_layernorm_planes(c, in_f32 ? TTB_F32 : dt, dt, in, out_ptr, lo, f32, gamma.raw(), beta.raw(), M, N, eps), c, name);
+}
+
+// dst (16-bit, [M, N]) = src (fp32): the re-layout kernel with an already K-major source is a plain conversion.
+void CastFromF32(ttb_ctx* c, const float* src, int dst_dt, void* dst, int64_t M, int64_t N, const char* name) {
+  Check(ttb_prepack_weight(c, TTB_F32, src, 1, N, M, dst_dt, dst), c, name);
+}
+
 // Which of the reference's two mask forms a tensor is (softmax.cpp:93-102): one row per batch or per query.
 bool MaskIs2D(const Tensor& m) {
   return m.n_dim() == 2 || (m.n_dim() == 3 && m.shape(1) == 1) || (m.n_dim() == 4 && m.shape(2) == 1);
@@ -61,9 +83,53 @@ const void* PackedLinear::Packed(bool is_trans) const {
   return p.raw();
 }
 
-void PackedLinear::Int8(bool is_trans, const int8_t** wq, const float** scale) const {
+const float* PackedLinear::PackedTf32(bool is_trans) const {
+  std::lock_guard<std::mutex> g(cache_->mu);
+  Tensor& p = cache_->tf32[is_trans ? 1 : 0];
+  if (p.is_null()) {
+    const int64_t K = in_dim(is_trans), N = out_dim(is_trans);
+    ttb_ctx* c = DeviceContext(weight_.device_id());
+    float* planes = p.Reshape<float>({2, N, K}, kDLCUDA, weight_.device_id(), "linear/tf32_weight_planes");
+    Check(ttb_prepack_weight(c, TTB_F32, weight_.raw(), is_trans ? 1 : 0, K, N, TTB_F32, planes), c, "prepack_weight");
+    Check(ttb_split_tf32(c, planes, N * K, planes, planes + N * K), c, "split_tf32");
+  }
+  return p.data<float>();
+}
+
+const float* PackedLinear::BiasF32() const {
+  if (bias_.is_null()) return nullptr;
+  std::lock_guard<std::mutex> g(cache_->mu);
+  Tensor& b = cache_->bias_f32;
+  if (b.is_null()) {
+    // a [K=N, N=1] "weight" re-laid out is a plain dtype conversion of the vector
+    const int dt = FloatType(bias_, "linear bias");
+    ttb_ctx* c = DeviceContext(bias_.device_id());
+    float* dst = b.Reshape<float>({bias_.numel()}, kDLCUDA, bias_.device_id(), "linear/bias_f32");
+    Check(ttb_prepack_weight(c, dt, bias_.raw(), 1, bias_.numel(), 1, TTB_F32, dst), c, "bias to fp32");
+  }
+  return b.data<float>();
+}
+
+void PackedLinear::Int8(bool is_trans, const int8_t** wq, const float** scale, const int32_t** col_sum) const {
   std::lock_guard<std::mutex> g(cache_->mu);
   const int i = is_trans ? 1 : 0;
+  if (col_sum) {  // the reference recipe's quantiser
+    if (cache_->qref[i].is_null()) {
+      const int dt = FloatType(weight_, "linear weight");
+      const int64_t K = in_dim(is_trans), N = out_dim(is_trans);
+      ttb_ctx* c = DeviceContext(weight_.device_id());
+      cache_->qref[i].Reshape(core::kInt8, {N, K}, kDLCUDA, weight_.device_id(), "linear/int8_weight");
+      cache_->qref_scale[i].Reshape(core::kFloat32, {1}, kDLCUDA, weight_.device_id(), "linear/int8_scale");
+      cache_->qref_colsum[i].Reshape(core::kInt32, {N}, kDLCUDA, weight_.device_id(), "linear/int8_col_sum");
+      Check(ttb_prepack_weight_int8_affine(c, dt, weight_.raw(), i, K, N, cache_->qref[i].mutableData<int8_t>(),
+                                           cache_->qref_scale[i].mutableData<float>(), cache_->qref_colsum[i].mutableData<int32_t>()),
+            c, "prepack_weight_int8_affine");
+    }
+    *wq = cache_->qref[i].data<int8_t>();
+    *scale = cache_->qref_scale[i].data<float>();
+    *col_sum = cache_->qref_colsum[i].data<int32_t>();
+    return;
+  }
   if (cache_->q[i].is_null()) {
     const int dt = FloatType(weight_, "linear weight");
     const int64_t K = in_dim(is_trans), N = out_dim(is_trans);
@@ -79,7 +145,7 @@ void PackedLinear::Int8(bool is_trans, const int8_t** wq, const float** scale) c
 }
 
 void PackedLinear::Forward(const Tensor& x, int64_t M, int epilogue, const void* residual, void* out, bool is_trans,
-                           const char* name, int64_t ldo) const {
+                           const char* name, int64_t ldo, void* out_lo, bool f32_out) const {
   const int dt = FloatType(x, name);
   SameTypeDevice(x, weight_, name);
   const int64_t K = in_dim(is_trans), N = out_dim(is_trans);
@@ -88,7 +154,26 @@ void PackedLinear::Forward(const Tensor& x, int64_t M, int epilogue, const void*
   const void* bias = bias_.is_null() ? nullptr : bias_.raw();
   if (!bias && epilogue == TTB_EPI_BIAS) epilogue = TTB_EPI_NONE;
   if (ldo == 0) ldo = N;
-  TT_ENFORCE(ldo == N || (dt != TTB_F32 && !use_int8_), "%s: a padded output pitch is only supported on the 16-bit path", name);
+  TT_ENFORCE(ldo == N || (dt != TTB_F32 && !use_int8()), "%s: a padded output pitch is only supported on the 16-bit path", name);
+  TT_ENFORCE((!out_lo && !f32_out) || (dt == TTB_BF16 && !use_int8()), "%s: two-plane and fp32 outputs belong to the bf16 path", name);
+  if (dt == TTB_F32 && core::Fp32TensorCores() && K % 4 == 0 && M > 0) {
+    // fp32 on the tensor cores: activations split into two tf32 planes, weights kept as two planes, three products
+    // accumulated in one GEMM with the elementwise kernel that followed MatMul in the reference as its epilogue
+    // (mat_mul.cpp:81-96 selects tensor-op math for the same product)
+    Tensor planes(nullptr);
+    float* a = planes.Reshape<float>({2, M, K}, kDLCUDA, x.device_id(), "linear/tf32_activation_planes");
+    Check(ttb_split_tf32(c, x.data<float>(), M * K, a, a + M * K), c, name);
+    const float* w = PackedTf32(is_trans);
+    ttb_linear_args args{};
+    args.dtype = TTB_F32; args.out_dtype = TTB_F32;
+    args.A = a; args.A2 = a + M * K; args.lda = K;
+    args.W = w; args.W2 = w + N * K;
+    args.bias = bias; args.residual = residual; args.ldr = N;
+    args.M = M; args.N = N; args.K = K; args.epilogue = epilogue;
+    args.out = out; args.ldo = N;
+    Check(ttb_linear_ex(c, &args), c, name);
+    return;
+  }
   if (dt == TTB_F32) {
     // exact path: the reference's sequence MatMul -> elementwise kernel
     Check(ttb_matmul(c, dt, x.raw(), 0, weight_.raw(), is_trans ? 1 : 0, M, N, K, 1.0f, 0.0f, out), c, name);
@@ -102,7 +187,19 @@ void PackedLinear::Forward(const Tensor& x, int64_t M, int epilogue, const void*
     }
     return;
   }
-  if (use_int8_) {
+  if (int8_mode_ == kInt8Reference) {
+    const int8_t* wq;
+    const float* ws;
+    const int32_t* cs;
+    Int8(is_trans, &wq, &ws, &cs);
+    Tensor xq(nullptr), qp(nullptr);
+    xq.Reshape(core::kInt8, {M, K}, kDLCUDA, x.device_id(), "linear/int8_activations");
+    qp.Reshape(core::kFloat32, {4}, kDLCUDA, x.device_id(), "linear/int8_qparams");
+    Check(ttb_quantize_tensor_affine(c, dt, x.raw(), M, K, xq.mutableData<int8_t>(), qp.mutableData<float>()), c, name);
+    Check(ttb_linear_int8_affine(c, dt, xq.data<int8_t>(), qp.data<float>(), wq, ws, cs, bias, residual, N, M, N, K, epilogue, out, N), c, name);
+    return;
+  }
+  if (use_int8()) {
     const int8_t* wq;
     const float* ws;
     Int8(is_trans, &wq, &ws);
@@ -114,7 +211,17 @@ void PackedLinear::Forward(const Tensor& x, int64_t M, int epilogue, const void*
     return;
   }
   if (ldo != N) epilogue |= TTB_EPI_FLAG_ROW_PADDING_IS_SCRATCH;  // only Linear's own row-padded scratch gets here
-  Check(ttb_linear(c, dt, x.raw(), K, Packed(is_trans), bias, residual, N, M, N, K, epilogue, out, ldo), c, name);
+  ttb_linear_args args{};
+  args.dtype = dt; args.out_dtype = f32_out ? TTB_F32 : dt;
+  args.A = x.raw(); args.lda = K;
+  // a bf16 activation that carries what its rounding dropped is used whole: A . W + A_lo . W
+  if (dt == TTB_BF16 && x.lo() && core::PreciseBF16()) args.A2 = x.lo()->raw();
+  args.W = Packed(is_trans);
+  args.bias = f32_out ? static_cast<const void*>(BiasF32()) : bias;
+  args.residual = residual; args.ldr = N;
+  args.M = M; args.N = N; args.K = K; args.epilogue = epilogue;
+  args.out = out; args.out_lo = out_lo; args.ldo = ldo;
+  Check(ttb_linear_ex(c, &args), c, name);
 }
 
 // ===================================================================================================
@@ -138,27 +245,47 @@ void BERTEmbedding::operator()(const Tensor& input_ids, const Tensor& position_i
   const int dev = input_ids.device_id();
   ttb_ctx* c = DeviceContext(dev);
   output_tensor->Reshape(word_embedings_.dtype(), {B, L, H}, kDLCUDA, dev, "BERTEmbedding/Reshape");
-  Check(ttb_embedding_ln(c, dt, input_ids.data<int64_t>(), position_ids.is_null() ? nullptr : position_ids.data<int64_t>(),
-                         token_type_ids.is_null() ? nullptr : token_type_ids.data<int64_t>(), nullptr, B, L, B * L,
-                         word_embedings_.raw(), position_embeddings_.raw(), token_type_embeddings_.raw(),
-                         layer_norm_weights_.raw(), layer_norm_bias_.raw(), H, word_embedings_.shape(0),
-                         position_embeddings_.shape(0), token_type_embeddings_.shape(0), 1e-12f, output_tensor->raw_mut()),
+  void* out = output_tensor->raw_mut();
+  void* lo = nullptr;
+  float* f32 = nullptr;
+  if (PreciseMode(dt)) {
+    core::TensorExtras& ex = output_tensor->NewExtras();
+    lo = ex.lo.Reshape(word_embedings_.dtype(), {B, L, H}, kDLCUDA, dev, "precise/lo_plane");
+    f32 = ex.f32.Reshape<float>({B, L, H}, kDLCUDA, dev, "precise/residual_stream");
+  }
+  Check(ttb_embedding_ln_planes(c, dt, input_ids.data<int64_t>(), position_ids.is_null() ? nullptr : position_ids.data<int64_t>(),
+                                token_type_ids.is_null() ? nullptr : token_type_ids.data<int64_t>(), nullptr, B, L, B * L,
+                                word_embedings_.raw(), position_embeddings_.raw(), token_type_embeddings_.raw(),
+                                layer_norm_weights_.raw(), layer_norm_bias_.raw(), H, word_embedings_.shape(0),
+                                position_embeddings_.shape(0), token_type_embeddings_.shape(0), 1e-12f, out, lo, f32),
         c, "BERTEmbedding");
 }
 
-void BERTEmbedding::Packed(const Tensor& input_ids, const std::vector<int64_t>& seq_lens, Tensor* output_tensor) const {
+void BERTEmbedding::Packed(const Tensor& input_ids, const std::vector<int64_t>& seq_lens, Tensor* output_tensor,
+                           const Tensor& position_ids, const Tensor& token_type_ids) const {
   const int dt = FloatType(word_embedings_, "word embeddings");
   TT_ENFORCE(input_ids.on_gpu(), "input ids must be on the GPU");
   const int64_t T = input_ids.numel(), H = word_embedings_.shape(1);
   TT_ENFORCE_EQ(T, std::accumulate(seq_lens.begin(), seq_lens.end(), (int64_t)0), "ids do not match the sequence lengths");
+  TT_ENFORCE(position_ids.is_null() || (position_ids.on_gpu() && position_ids.numel() == T), "packed position ids must be %lld ids on the GPU", (long long)T);
+  TT_ENFORCE(token_type_ids.is_null() || (token_type_ids.on_gpu() && token_type_ids.numel() == T), "packed token type ids must be %lld ids on the GPU", (long long)T);
   const int dev = input_ids.device_id();
   ttb_ctx* c = DeviceContext(dev);
   output_tensor->Reshape(word_embedings_.dtype(), {1, T, H}, kDLCUDA, dev, "BERTEmbedding/Reshape");
-  Check(ttb_embedding_ln(c, dt, input_ids.data<int64_t>(), nullptr, nullptr, core::CuSeqlens(dev, seq_lens),
-                         (int64_t)seq_lens.size(), 0, T, word_embedings_.raw(), position_embeddings_.raw(),
-                         token_type_embeddings_.raw(), layer_norm_weights_.raw(), layer_norm_bias_.raw(), H,
-                         word_embedings_.shape(0), position_embeddings_.shape(0), token_type_embeddings_.shape(0), 1e-12f,
-                         output_tensor->raw_mut()),
+  void* out = output_tensor->raw_mut();
+  void* lo = nullptr;
+  float* f32 = nullptr;
+  if (PreciseMode(dt)) {
+    core::TensorExtras& ex = output_tensor->NewExtras();
+    lo = ex.lo.Reshape(word_embedings_.dtype(), {1, T, H}, kDLCUDA, dev, "precise/lo_plane");
+    f32 = ex.f32.Reshape<float>({1, T, H}, kDLCUDA, dev, "precise/residual_stream");
+  }
+  const core::CuSeqlensHandle cu = core::CuSeqlens(dev, seq_lens);
+  Check(ttb_embedding_ln_planes(c, dt, input_ids.data<int64_t>(), position_ids.is_null() ? nullptr : position_ids.data<int64_t>(),
+                                token_type_ids.is_null() ? nullptr : token_type_ids.data<int64_t>(), cu.get(), (int64_t)seq_lens.size(), 0, T,
+                                word_embedings_.raw(), position_embeddings_.raw(), token_type_embeddings_.raw(), layer_norm_weights_.raw(),
+                                layer_norm_bias_.raw(), H, word_embedings_.shape(0), position_embeddings_.shape(0),
+                                token_type_embeddings_.shape(0), 1e-12f, out, lo, f32),
         c, "BERTEmbedding/packed");
 }
 
@@ -305,8 +432,13 @@ void MultiHeadedAttention::Run(const Tensor& x, const Tensor& attention_mask, co
   const Tensor* gemm_in = &x;
   if (pre_layernorm) {
     normed.Reshape(x.dtype(), out_shape, kDLCUDA, dev, "self/layernorm/Reshape");
-    Check(ttb_layernorm(c, dt, x.raw(), normed.raw_mut(), layernorm_gamma_.raw(), layernorm_beta_.raw(), T, H, pre_ln_eps_), c,
-          "self/layernorm");
+    if (PreciseMode(dt)) {
+      LayerNormPlanes(c, x.f32() != nullptr, x.f32() ? x.f32()->raw() : x.raw(), &normed, layernorm_gamma_, layernorm_beta_, T, H, pre_ln_eps_,
+                      false, "self/layernorm");
+    } else {
+      Check(ttb_layernorm(c, dt, x.raw(), normed.raw_mut(), layernorm_gamma_.raw(), layernorm_beta_.raw(), T, H, pre_ln_eps_), c,
+            "self/layernorm");
+    }
     gemm_in = &normed;
   }
 
@@ -320,7 +452,8 @@ void MultiHeadedAttention::Run(const Tensor& x, const Tensor& attention_mask, co
     qkv.Reshape(x.dtype(), {T, 3 * H}, kDLCUDA, dev, "self/qkv_out1/Reshape");
     qkv_.Forward(*gemm_in, T, TTB_EPI_BIAS, nullptr, qkv.raw_mut(), is_trans_weight, "self/gemm012_fused");
     // 3) attention over packed tokens; the mask tensor (if any) is applied as the reference does
-    const int32_t* cu = seq_lens ? core::CuSeqlens(dev, *seq_lens) : core::UniformCuSeqlens(dev, B, maxL);
+    const core::CuSeqlensHandle cu_handle = seq_lens ? core::CuSeqlens(dev, *seq_lens) : core::UniformCuSeqlens(dev, B, maxL);
+    const int32_t* cu = cu_handle.get();
     const float* mask = nullptr;
     int64_t mbs = 0, mrs = 0;
     if (!attention_mask.is_null()) {
@@ -367,7 +500,8 @@ void MultiHeadedAttention::Run(const Tensor& x, const Tensor& attention_mask, co
     q.Reshape(x.dtype(), head_shape, kDLCUDA, dev, "self/q/Reshape");
     k.Reshape(x.dtype(), head_shape, kDLCUDA, dev, "self/k/Reshape");
     v.Reshape(x.dtype(), head_shape, kDLCUDA, dev, "self/v/Reshape");
-    const int32_t* cu = seq_lens ? core::CuSeqlens(dev, *seq_lens) : nullptr;
+    const core::CuSeqlensHandle cu_handle = seq_lens ? core::CuSeqlens(dev, *seq_lens) : core::CuSeqlensHandle();
+    const int32_t* cu = cu_handle.get();
     Check(ttb_split_add_bias_transpose_pad(c, dt, qkv.raw(), qkv_.bias().raw(), cu, B, maxL, heads, d, q.raw_mut(), k.raw_mut(),
                                            v.raw_mut()),
           c, "self/SplitAddBiasTransposeForScore");
@@ -412,6 +546,24 @@ void MultiHeadedAttention::Finish(const Tensor& context, const Tensor& x, int64_
   ttb_ctx* c = DeviceContext(dev);
   const int64_t H = x.shape(2);
   output->Reshape(x.dtype(), ShapeOf(x), kDLCUDA, dev, "gemm5/Reshape");
+  const bool precise = PreciseMode(dt) && x.f32() != nullptr && !dense_.use_int8();
+  if (precise && (post_add_input || post_layernorm)) {
+    // the residual stream stays fp32: out-projection + bias + fp32 residual -> fp32, then either the layer norm that
+    // writes the next GEMM's two operand planes, or (pre-LN models) the 16-bit copy the caller sees
+    if (post_layernorm) {
+      Tensor sum(nullptr);
+      float* s = sum.Reshape<float>(ShapeOf(x), kDLCUDA, dev, "gemm5/fp32_sum");
+      dense_.Forward(context, T, TTB_EPI_BIAS_RESIDUAL, x.f32()->raw(), s, is_trans_weight, "gemm5", 0, nullptr, true);
+      LayerNormPlanes(c, true, s, output, layernorm_gamma_, layernorm_beta_, T, H, 1e-12f, true, "AddBiasLayerNorm");
+    } else {
+      void* pub = output->raw_mut();
+      core::TensorExtras& ex = output->NewExtras();
+      float* s = ex.f32.Reshape<float>(ShapeOf(x), kDLCUDA, dev, "precise/residual_stream");
+      dense_.Forward(context, T, TTB_EPI_BIAS_RESIDUAL, x.f32()->raw(), s, is_trans_weight, "gemm5", 0, nullptr, true);
+      CastFromF32(c, s, dt, pub, T, H, "gemm5/public_copy");
+    }
+    return;
+  }
   if (post_add_input) {
     dense_.Forward(context, T, TTB_EPI_BIAS_RESIDUAL, x.raw(), output->raw_mut(), is_trans_weight, "gemm5");
   } else if (!post_layernorm) {
@@ -536,9 +688,14 @@ void BertIntermediate::EnforceShapeAndType() const {
 void BertIntermediate::operator()(const Tensor& input_tensor, Tensor* output_tensor) const {
   TT_ENFORCE(output_tensor, "The output tensor should not be nullptr.");
   FloatType(input_tensor, "BertIntermediate input");
-  output_tensor->Reshape(input_tensor.dtype(), WithLast(input_tensor, dense_.out_dim(false)), kDLCUDA, input_tensor.device_id(),
-                         "BertIntermediate/Reshape");
-  dense_.Forward(input_tensor, input_tensor.rows(), TTB_EPI_BIAS_GELU, nullptr, output_tensor->raw_mut(), false, "BertIntermediate");
+  const int dt = core::ToTTBDtype(input_tensor.dtype());
+  const auto shape = WithLast(input_tensor, dense_.out_dim(false));
+  output_tensor->Reshape(input_tensor.dtype(), shape, kDLCUDA, input_tensor.device_id(), "BertIntermediate/Reshape");
+  void* out = output_tensor->raw_mut();
+  void* lo = nullptr;
+  if (PreciseMode(dt) && input_tensor.lo() && !dense_.use_int8())  // the activation leaves as two planes, like it came
+    lo = output_tensor->NewExtras().lo.Reshape(input_tensor.dtype(), shape, kDLCUDA, input_tensor.device_id(), "precise/lo_plane");
+  dense_.Forward(input_tensor, input_tensor.rows(), TTB_EPI_BIAS_GELU, nullptr, out, false, "BertIntermediate", 0, lo);
 }
 
 void BertOutput::EnforceShapeAndType() const {
@@ -561,6 +718,11 @@ void BertOutput::operator()(const Tensor& hidden_states, const Tensor& input_ten
     Check(ttb_add_bias_layernorm(c, dt, output_tensor->raw_mut(), input_tensor.raw(), dense_.bias().raw(), layer_norm_weight_.raw(),
                                  layer_norm_bias_.raw(), M, N, 1e-12f),
           c, "BertOutput/AddBiasLayerNorm");
+  } else if (PreciseMode(dt) && input_tensor.f32() && !dense_.use_int8()) {
+    Tensor sum(nullptr);
+    float* s = sum.Reshape<float>({M, N}, kDLCUDA, hidden_states.device_id(), "BertOutput/fp32_sum");
+    dense_.Forward(hidden_states, M, TTB_EPI_BIAS_RESIDUAL, input_tensor.f32()->raw(), s, false, "BertOutput/MatMul", 0, nullptr, true);
+    LayerNormPlanes(c, true, s, output_tensor, layer_norm_weight_, layer_norm_bias_, M, N, 1e-12f, true, "BertOutput/AddBiasLayerNorm");
   } else {
     dense_.Forward(hidden_states, M, TTB_EPI_BIAS_RESIDUAL, input_tensor.raw(), output_tensor->raw_mut(), false, "BertOutput/MatMul");
     Check(ttb_layernorm(c, dt, output_tensor->raw(), output_tensor->raw_mut(), layer_norm_weight_.raw(), layer_norm_bias_.raw(), M, N,
@@ -582,6 +744,11 @@ void ProjectAddNorm(const PackedLinear& dense, const Tensor& act_in, const Tenso
   if (dt == TTB_F32) {
     dense.Forward(act_in, M, TTB_EPI_NONE, nullptr, out->raw_mut(), is_trans, name);
     Check(ttb_add_bias_layernorm(c, dt, out->raw_mut(), residual.raw(), dense.bias().raw(), gamma.raw(), beta.raw(), M, N, 1e-12f), c, name);
+  } else if (PreciseMode(dt) && residual.f32() && !dense.use_int8()) {
+    Tensor sum(nullptr);
+    float* s = sum.Reshape<float>({M, N}, kDLCUDA, act_in.device_id(), "fp32_sum");
+    dense.Forward(act_in, M, TTB_EPI_BIAS_RESIDUAL, residual.f32()->raw(), s, is_trans, name, 0, nullptr, true);
+    LayerNormPlanes(c, true, s, out, gamma, beta, M, N, 1e-12f, true, name);
   } else {
     dense.Forward(act_in, M, TTB_EPI_BIAS_RESIDUAL, residual.raw(), out->raw_mut(), is_trans, name);
     Check(ttb_layernorm(c, dt, out->raw(), out->raw_mut(), gamma.raw(), beta.raw(), M, N, 1e-12f), c, name);
@@ -596,7 +763,11 @@ void DistrillFFN::operator()(const Tensor& x, Tensor* output, bool is_trans_weig
   TT_ENFORCE_EQ(dense1_.in_dim(is_trans_weight), x.shape(-1), "dense weight and input tensor should have the same model_dim.");
   Tensor inter(nullptr);
   inter.Reshape(x.dtype(), {x.rows(), dense1_.out_dim(is_trans_weight)}, kDLCUDA, x.device_id(), "FFN/gemm0/Reshape");
-  dense1_.Forward(x, x.rows(), TTB_EPI_BIAS_GELU, nullptr, inter.raw_mut(), is_trans_weight, "FFN/gemm0");
+  void* inter_ptr = inter.raw_mut();
+  void* inter_lo = nullptr;
+  if (PreciseMode(core::ToTTBDtype(x.dtype())) && x.lo())
+    inter_lo = inter.NewExtras().lo.Reshape(x.dtype(), ShapeOf(inter), kDLCUDA, x.device_id(), "precise/lo_plane");
+  dense1_.Forward(x, x.rows(), TTB_EPI_BIAS_GELU, nullptr, inter_ptr, is_trans_weight, "FFN/gemm0", 0, inter_lo);
   ProjectAddNorm(dense2_, inter, x, layer_norm_weight_, layer_norm_bias_, is_trans_weight, output, "FFN/gemm1");
 }
 
@@ -612,7 +783,11 @@ void AlbertLayer::operator()(const Tensor& x, Tensor* hidden_output, Tensor* out
   FloatType(x, "AlbertLayer input");
   SameTypeDevice(x, dense_.weight(), "AlbertLayer");
   hidden_output->Reshape(x.dtype(), WithLast(x, dense_.out_dim(false)), kDLCUDA, x.device_id(), "AlbertLayer/Reshape");
-  dense_.Forward(x, x.rows(), TTB_EPI_BIAS_GELU, nullptr, hidden_output->raw_mut(), false, "AlbertLayer/gemm0");
+  void* hid_ptr = hidden_output->raw_mut();
+  void* hid_lo = nullptr;
+  if (PreciseMode(core::ToTTBDtype(x.dtype())) && x.lo())
+    hid_lo = hidden_output->NewExtras().lo.Reshape(x.dtype(), ShapeOf(*hidden_output), kDLCUDA, x.device_id(), "precise/lo_plane");
+  dense_.Forward(x, x.rows(), TTB_EPI_BIAS_GELU, nullptr, hid_ptr, false, "AlbertLayer/gemm0", 0, hid_lo);
   ProjectAddNorm(dense_output_, *hidden_output, x, layer_norm_weight_, layer_norm_bias_, false, output, "AlbertLayer/gemm1");
 }
 
@@ -653,7 +828,8 @@ void SequencePool::Packed(const Tensor& input, const std::vector<int64_t>& seq_l
   ttb_ctx* c = DeviceContext(dev);
   const int64_t B = (int64_t)seq_lens.size(), H = input.shape(-1);
   output->Reshape(input.dtype(), {B, H}, kDLCUDA, dev, "SequencePool/Reshape");
-  Check(ttb_seq_pool_varlen(c, dt, input.raw(), core::CuSeqlens(dev, seq_lens), B, H, pool_type_, output->raw_mut()), c, "SeqPool/packed");
+  const core::CuSeqlensHandle cu = core::CuSeqlens(dev, seq_lens);
+  Check(ttb_seq_pool_varlen(c, dt, input.raw(), cu.get(), B, H, pool_type_, output->raw_mut()), c, "SeqPool/packed");
 }
 
 void PrepareBertMasks::operator()(const Tensor& inputs, Tensor* att_mask, Tensor* seq_type, Tensor* position_ids,
@@ -687,8 +863,27 @@ void PositionwiseFeedForward::operator()(const Tensor& x, Tensor* output, bool i
   TT_ENFORCE_EQ(dense1_.in_dim(is_trans_weight), H, "dense weight and input tensor should have the same model_dim.");
   Tensor normed(nullptr), inter(nullptr);
   normed.Reshape(x.dtype(), ShapeOf(x), kDLCUDA, dev, "FFN/LayerNorm/Reshape");
-  Check(ttb_layernorm(c, dt, x.raw(), normed.raw_mut(), layer_norm_weight_.raw(), layer_norm_bias_.raw(), M, H, eps_), c, "FFN/LayerNorm");
   inter.Reshape(x.dtype(), {M, F}, kDLCUDA, dev, "FFN/inter/Reshape");
+  if (PreciseMode(dt) && act_ == TTB_ACT_GELU) {
+    // pre-LN block of a bf16 model: normalise the fp32 stream into two operand planes, keep the GELU output as two
+    // planes, add into the fp32 stream and leave its 16-bit copy for the caller
+    LayerNormPlanes(c, x.f32() != nullptr, x.f32() ? x.f32()->raw() : x.raw(), &normed, layer_norm_weight_, layer_norm_bias_, M, H, eps_, false,
+                    "FFN/LayerNorm");
+    void* inter_ptr = inter.raw_mut();
+    void* inter_lo = inter.NewExtras().lo.Reshape(x.dtype(), {M, F}, kDLCUDA, dev, "precise/lo_plane");
+    dense1_.Forward(normed, M, TTB_EPI_BIAS_GELU, nullptr, inter_ptr, is_trans_weight, "FFN/gemm0", 0, inter_lo);
+    output->Reshape(x.dtype(), ShapeOf(x), kDLCUDA, dev, "FFN/Reshape");
+    if (x.f32()) {
+      void* pub = output->raw_mut();
+      float* s = output->NewExtras().f32.Reshape<float>(ShapeOf(x), kDLCUDA, dev, "precise/residual_stream");
+      dense2_.Forward(inter, M, TTB_EPI_BIAS_RESIDUAL, x.f32()->raw(), s, is_trans_weight, "FFN/gemm1", 0, nullptr, true);
+      CastFromF32(c, s, dt, pub, M, H, "FFN/public_copy");
+    } else {
+      dense2_.Forward(inter, M, TTB_EPI_BIAS_RESIDUAL, x.raw(), output->raw_mut(), is_trans_weight, "FFN/gemm1");
+    }
+    return;
+  }
+  Check(ttb_layernorm(c, dt, x.raw(), normed.raw_mut(), layer_norm_weight_.raw(), layer_norm_bias_.raw(), M, H, eps_), c, "FFN/LayerNorm");
   if (act_ == TTB_ACT_GELU) {
     dense1_.Forward(normed, M, TTB_EPI_BIAS_GELU, nullptr, inter.raw_mut(), is_trans_weight, "FFN/gemm0");
   } else {
@@ -717,6 +912,15 @@ void FusedAddBiasLayerNorm::operator()(const Tensor& input_tensor, Tensor* outpu
 void LayerNorm::operator()(const Tensor& input, Tensor* output) const {
   const int dt = FloatType(input, "LayerNorm input");
   ttb_ctx* c = DeviceContext(input.device_id());
+  if (PreciseMode(dt) && output != &input) {  // the final norm of a pre-LN bf16 model reads the fp32 stream when there is one
+    const bool f = input.f32() != nullptr;
+    const void* in = f ? input.f32()->raw() : input.raw();
+    const int64_t rows = input.rows(), width = input.shape(-1);
+    const auto shape = ShapeOf(input);
+    output->Reshape(input.dtype(), shape, kDLCUDA, input.device_id(), "LayerNorm/Reshape");
+    LayerNormPlanes(c, f, in, output, gamma_, beta_, rows, width, eps_, false, "LayerNorm");
+    return;
+  }
   output->Reshape(input.dtype(), ShapeOf(input), kDLCUDA, input.device_id(), "LayerNorm/Reshape");
   Check(ttb_layernorm(c, dt, input.raw(), output->raw_mut(), gamma_.raw(), beta_.raw(), input.rows(), input.shape(-1), eps_), c, "LayerNorm");
 }
@@ -739,6 +943,13 @@ void TokenPositionEmbedding::operator()(const Tensor& input_ids, Tensor* output,
   const char* table = static_cast<const char*>(position_.raw()) + (size_t)position_offset * (size_t)H * (dt == TTB_F32 ? 4 : 2);
   Check(ttb_lookup_embedding(c, dt, output->raw_mut(), table, pos_ids, B * L, H, position_.shape(0) - position_offset, 1), c,
         "TokenPositionEmbedding/position");
+  if (PreciseMode(dt)) {
+    // start the fp32 residual stream of a bf16 model from the embedding sum (its one rounding is 2^-9 of a value of the
+    // embeddings' size, far below what the blocks add)
+    const void* pub = output->raw();
+    float* f = output->NewExtras().f32.Reshape<float>({B, L, H}, kDLCUDA, dev, "precise/residual_stream");
+    Check(ttb_prepack_weight(c, dt, pub, 1, H, B * L, TTB_F32, f), c, "TokenPositionEmbedding/residual_stream");
+  }
 }
 
 void Linear::operator()(const Tensor& input, Tensor* output) const {

@@ -32,24 +32,40 @@ class PackedLinear {
   int64_t out_dim(bool is_trans) const { return weight_.shape(is_trans ? 0 : 1); }
   // K-major [N,K] copy in the weight's own 16-bit dtype (built on first use).
   const void* Packed(bool is_trans) const;
-  // int8 [N,K] copy + device scale (built on first use).
-  void Int8(bool is_trans, const int8_t** wq, const float** scale) const;
-  void set_int8(bool on) { use_int8_ = on; }
-  bool use_int8() const { return use_int8_; }
+  // fp32 weights as two tf32 planes [2][N,K] (hi, then lo), for the three-product tensor-core GEMM.
+  const float* PackedTf32(bool is_trans) const;
+  // int8 [N,K] copy + device scale (built on first use); `col_sum` (may be null) selects the reference recipe's
+  // quantiser (torch's per-tensor rule) and receives the per-output-row sums its zero-point correction needs.
+  void Int8(bool is_trans, const int8_t** wq, const float** scale, const int32_t** col_sum = nullptr) const;
+  // The bias as fp32 (for GEMMs that write an fp32 residual stream).
+  const float* BiasF32() const;
+  // kInt8PerRow: the benchmark's scheme (per-row symmetric activations); kInt8Reference: the reference's recipe
+  // (qmodeling_bert.py:13-45: torch dynamic quantisation, per-tensor affine 7-bit activations).
+  enum Int8Mode { kInt8Off = 0, kInt8PerRow = 1, kInt8Reference = 2 };
+  void set_int8(bool on) { int8_mode_ = on ? kInt8PerRow : kInt8Off; }
+  void set_int8_mode(int mode) { int8_mode_ = mode; }
+  bool use_int8() const { return int8_mode_ != kInt8Off; }
 
-  // out[M,N] = epilogue(x[M,K] . W + bias); picks the kernel by dtype / int8 flag.
-  // `ldo` (elements between output rows) defaults to N.
+  // out[M,N] = epilogue(x[M,K] . W + bias); picks the kernel by dtype / int8 mode.
+  // `ldo` (elements between output rows) defaults to N. A bf16 x that carries a lo plane is used at full precision
+  // (two passes). out_lo (bf16 only) receives the second plane of the output. f32_out: `out` and `residual` are fp32
+  // (the residual stream of a bf16 model in its precise mode).
   void Forward(const core::Tensor& x, int64_t M, int epilogue, const void* residual, void* out, bool is_trans,
-               const char* name, int64_t ldo = 0) const;
+               const char* name, int64_t ldo = 0, void* out_lo = nullptr, bool f32_out = false) const;
 
  private:
   core::Tensor weight_, bias_;
-  bool use_int8_ = false;
+  int int8_mode_ = kInt8Off;
   struct Cache {
     std::mutex mu;
     core::Tensor packed[2]{core::Tensor(nullptr), core::Tensor(nullptr)};
+    core::Tensor tf32[2]{core::Tensor(nullptr), core::Tensor(nullptr)};
     core::Tensor q[2]{core::Tensor(nullptr), core::Tensor(nullptr)};
     core::Tensor qscale[2]{core::Tensor(nullptr), core::Tensor(nullptr)};
+    core::Tensor qref[2]{core::Tensor(nullptr), core::Tensor(nullptr)};
+    core::Tensor qref_scale[2]{core::Tensor(nullptr), core::Tensor(nullptr)};
+    core::Tensor qref_colsum[2]{core::Tensor(nullptr), core::Tensor(nullptr)};
+    core::Tensor bias_f32{nullptr};
   };
   std::unique_ptr<Cache> cache_{new Cache()};
 };
@@ -66,8 +82,10 @@ class BERTEmbedding {
   void EnforceShapeAndType() const;
   void operator()(const core::Tensor& input_ids, const core::Tensor& position_ids, const core::Tensor& token_type_ids,
                   core::Tensor* output_tensor) const;
-  // Packed variable-length form: ids [sumL], positions restart at 0 per sequence, types 0.
-  void Packed(const core::Tensor& input_ids, const std::vector<int64_t>& seq_lens, core::Tensor* output_tensor) const;
+  // Packed variable-length form: ids [sumL]; positions restart at 0 per sequence and types are 0 unless packed
+  // position_ids / token_type_ids ([sumL], null tensors = defaults) are given.
+  void Packed(const core::Tensor& input_ids, const std::vector<int64_t>& seq_lens, core::Tensor* output_tensor,
+              const core::Tensor& position_ids = core::Tensor(nullptr), const core::Tensor& token_type_ids = core::Tensor(nullptr)) const;
 
  private:
   core::Tensor word_embedings_, position_embeddings_, token_type_embeddings_, layer_norm_weights_, layer_norm_bias_;
@@ -157,7 +175,7 @@ class BertIntermediate {
   }
   void EnforceShapeAndType() const;
   void operator()(const core::Tensor& input_tensor, core::Tensor* output_tensor) const;
-  void QuantizeInt8() { dense_.set_int8(true); }
+  void QuantizeInt8(int mode = PackedLinear::kInt8PerRow) { dense_.set_int8_mode(mode); }
 
  private:
   PackedLinear dense_;
@@ -172,7 +190,7 @@ class BertOutput {
   }
   void EnforceShapeAndType() const;
   void operator()(const core::Tensor& hidden_states, const core::Tensor& input_tensor, core::Tensor* output_tensor) const;
-  void QuantizeInt8() { dense_.set_int8(true); }
+  void QuantizeInt8(int mode = PackedLinear::kInt8PerRow) { dense_.set_int8_mode(mode); }
 
  private:
   PackedLinear dense_;

@@ -99,10 +99,20 @@ PYBIND11_MODULE(turbo_transformers_cxx, m) {
   m.def("arena_end", [](int device) {
     ttb_ctx* c = core::DeviceContext(device);
     size_t used = 0;
-    core::Check(ttb_arena_end(c, &used), c, "arena_end");
-    return used;
+    void* arena = nullptr;
+    core::Check(ttb_arena_end(c, &used, &arena), c, "arena_end");
+    return std::make_pair(used, reinterpret_cast<uintptr_t>(arena));
+  }, "End arena mode; returns (bytes used, arena handle). The buffer stays reserved until arena_release(device, handle).");
+  m.def("arena_release", [](int device, uintptr_t arena) {
+    ttb_ctx* c = core::DeviceContext(device);
+    core::Check(ttb_arena_release(c, reinterpret_cast<void*>(arena)), c, "arena_release");
   });
-  m.def("arena_release", [](int device) { ttb_ctx* c = core::DeviceContext(device); core::Check(ttb_arena_release(c), c, "arena_release"); });
+  m.def("set_bf16_precise", [](bool on) { core::SetPreciseBF16(on); },
+        "bf16 models: keep an fp32 residual stream and hi + lo activation planes between layers (default on).");
+  m.def("bf16_precise", []() { return core::PreciseBF16(); });
+  m.def("set_fp32_tensor_cores", [](bool on) { core::SetFp32TensorCores(on); },
+        "fp32 models: run Linears on the tensor cores as three tf32 products (default on); off = exact-order CUDA-core GEMM.");
+  m.def("fp32_tensor_cores", []() { return core::Fp32TensorCores(); });
   m.def("bytes_allocated_total", [](int device) {
     ttb_ctx* c = core::DeviceContext(device);
     uint64_t b = 0;
@@ -144,7 +154,11 @@ PYBIND11_MODULE(turbo_transformers_cxx, m) {
         return new layers::BERTEmbedding(std::move(word), std::move(position), std::move(token_type), std::move(ln_w), std::move(ln_b));
       }))
       .def("__call__", &layers::BERTEmbedding::operator())
-      .def("packed", &layers::BERTEmbedding::Packed);
+      .def("packed", [](const layers::BERTEmbedding& self, const Tensor& ids, const std::vector<int64_t>& lens, Tensor* out,
+                        const Tensor* position_ids, const Tensor* token_type_ids) {
+        const Tensor none(nullptr);
+        self.Packed(ids, lens, out, position_ids ? *position_ids : none, token_type_ids ? *token_type_ids : none);
+      }, py::arg("input_ids"), py::arg("seq_lens"), py::arg("output"), py::arg("position_ids") = nullptr, py::arg("token_type_ids") = nullptr);
 
   py::class_<layers::BertAttention>(m, "BertAttention")
       .def(py::init([](Tensor& qkv_weight, Tensor& qkv_bias, Tensor& dense_weight, Tensor& dense_bias, Tensor& ln_w, Tensor& ln_b,
@@ -191,14 +205,14 @@ PYBIND11_MODULE(turbo_transformers_cxx, m) {
   py::class_<layers::BertIntermediate>(m, "BertIntermediate")
       .def(py::init([](Tensor& w, Tensor& b) { return new layers::BertIntermediate(std::move(w), std::move(b)); }))
       .def("__call__", &layers::BertIntermediate::operator())
-      .def("quantize_int8", &layers::BertIntermediate::QuantizeInt8);
+      .def("quantize_int8", &layers::BertIntermediate::QuantizeInt8, py::arg("mode") = 1);
 
   py::class_<layers::BertOutput>(m, "BertOutput")
       .def(py::init([](Tensor& w, Tensor& b, Tensor& ln_w, Tensor& ln_b) {
         return new layers::BertOutput(std::move(w), std::move(b), std::move(ln_w), std::move(ln_b));
       }))
       .def("__call__", &layers::BertOutput::operator())
-      .def("quantize_int8", &layers::BertOutput::QuantizeInt8);
+      .def("quantize_int8", &layers::BertOutput::QuantizeInt8, py::arg("mode") = 1);
 
   py::class_<layers::SequencePool>(m, "SequencePool")
       .def(py::init([](const std::string& pool_type) { return new layers::SequencePool(pool_type); }))

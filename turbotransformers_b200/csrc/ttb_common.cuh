@@ -12,6 +12,8 @@
 #include <mutex>
 #include <string>
 #include <unordered_map>
+#include <utility>
+#include <vector>
 
 #include "ttb.h"
 
@@ -30,10 +32,12 @@ struct ttb_ctx {
   uint64_t n_allocs = 0;
   std::atomic<uint64_t> launches{0};
   std::unordered_map<void*, size_t> live;
-  // arena mode (ttb_arena_begin / ttb_arena_end): allocations at increasing offsets of one reserved buffer
-  char* arena = nullptr;
+  // arena mode (ttb_arena_begin / ttb_arena_end): allocations at increasing offsets of one reserved buffer. Every
+  // begin reserves a buffer of its own; after end it belongs to the caller until ttb_arena_release.
+  char* arena = nullptr;  // the active arena
   size_t arena_size = 0, arena_off = 0, arena_peak = 0;
   bool arena_active = false;
+  std::vector<std::pair<char*, size_t>> arenas;  // every reserved buffer not yet released (the active one included)
   uint64_t bytes_allocated_total = 0;  // sum of all ttb_alloc sizes so far
 };
 

@@ -46,7 +46,7 @@ extern "C" int ttb_ctx_destroy(ttb_ctx* c) {
   cudaStreamSynchronize(c->stream);
   for (auto& kv : c->live) cudaFreeAsync(kv.first, c->stream);
   cudaStreamSynchronize(c->stream);
-  if (c->arena) cudaFree(c->arena);
+  for (auto& a : c->arenas) cudaFree(a.first);
   if (c->d_status) cudaFree(c->d_status);
   if (c->h_status) cudaFreeHost(c->h_status);
   if (c->owns_pool && c->pool) cudaMemPoolDestroy(c->pool);
@@ -63,7 +63,26 @@ extern "C" int ttb_ctx_set_stream(ttb_ctx* c, void* s) {
     cudaStreamDestroy(c->stream);
     c->owns_stream = false;
   }
-  c->stream = s ? static_cast<cudaStream_t>(s) : cudaStreamLegacy;
+  cudaStream_t next = s ? static_cast<cudaStream_t>(s) : cudaStreamLegacy;
+  if (next != c->stream) {
+    // Work already queued through this context (kernels, and the stream-ordered frees of its buffers) stays ahead of
+    // whatever is queued next: the new stream waits for an event recorded on the old one. While either stream is being
+    // captured into a graph the event cannot be recorded; the capture code orders its streams itself.
+    DeviceGuard g(c->device);
+    cudaStreamCaptureStatus a = cudaStreamCaptureStatusNone, b = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(c->stream, &a);
+    cudaStreamIsCapturing(next, &b);
+    cudaGetLastError();
+    if (a == cudaStreamCaptureStatusNone && b == cudaStreamCaptureStatusNone) {
+      cudaEvent_t ev = nullptr;
+      if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) == cudaSuccess) {
+        if (cudaEventRecord(ev, c->stream) == cudaSuccess) cudaStreamWaitEvent(next, ev, 0);
+        cudaEventDestroy(ev);
+      }
+      cudaGetLastError();
+    }
+    c->stream = next;
+  }
   return TTB_OK;
 }
 
@@ -182,7 +201,8 @@ extern "C" int ttb_free(ttb_ctx* c, void* p, const char* /*name*/) {
   if (!p) return TTB_OK;
   {
     std::lock_guard<std::mutex> lk(c->mu);
-    if (c->arena && p >= (void*)c->arena && p < (void*)(c->arena + c->arena_size)) return TTB_OK;  // arena memory is not recycled
+    for (auto& a : c->arenas)
+      if (p >= (void*)a.first && p < (void*)(a.first + a.second)) return TTB_OK;  // arena memory is not recycled
     auto it = c->live.find(p);
     if (it == c->live.end()) {
       c->last_error = "ttb_free: pointer was not allocated by this context";
@@ -201,47 +221,58 @@ extern "C" int ttb_arena_begin(ttb_ctx* c, size_t bytes) {
   TTB_REQUIRE(c, bytes > 0, "arena_begin: zero size");
   TTB_REQUIRE(c, !c->arena_active, "arena_begin: an arena is already active");
   DeviceGuard g(c->device);
-  if (c->arena && c->arena_size < bytes) {
-    TTB_CUDA(c, cudaStreamSynchronize(c->stream));
-    TTB_CUDA(c, cudaFree(c->arena));
-    c->arena = nullptr;
-    c->arena_size = 0;
-  }
-  if (!c->arena) {
-    void* p = nullptr;
-    cudaError_t e = cudaMalloc(&p, bytes);
-    if (e != cudaSuccess) {
-      cudaGetLastError();
-      return fail(c, e == cudaErrorMemoryAllocation ? TTB_ERR_OOM : TTB_ERR_CUDA, "reserving an arena of %zu bytes: %s", bytes, cudaGetErrorString(e));
-    }
-    c->arena = static_cast<char*>(p);
-    c->arena_size = bytes;
+  // a buffer of its own for every begin: buffers of earlier arenas may be in use by graphs that were captured over them
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(c, e == cudaErrorMemoryAllocation ? TTB_ERR_OOM : TTB_ERR_CUDA, "reserving an arena of %zu bytes: %s", bytes, cudaGetErrorString(e));
   }
   std::lock_guard<std::mutex> lk(c->mu);
+  c->arena = static_cast<char*>(p);
+  c->arena_size = bytes;
+  c->arenas.emplace_back(c->arena, bytes);
   c->arena_off = 0;
   c->arena_peak = 0;
   c->arena_active = true;
   return TTB_OK;
 }
 
-extern "C" int ttb_arena_end(ttb_ctx* c, size_t* bytes_used) {
+extern "C" int ttb_arena_end(ttb_ctx* c, size_t* bytes_used, void** arena_out) {
   if (!c) return TTB_ERR_INVALID;
   std::lock_guard<std::mutex> lk(c->mu);
+  if (!c->arena_active) {
+    c->last_error = "arena_end: no arena is active";
+    return TTB_ERR_INVALID;
+  }
   if (bytes_used) *bytes_used = c->arena_peak;
+  if (arena_out) *arena_out = c->arena;
   c->arena_active = false;
+  c->arena = nullptr;
+  c->arena_size = 0;
   return TTB_OK;
 }
 
-extern "C" int ttb_arena_release(ttb_ctx* c) {
+extern "C" int ttb_arena_release(ttb_ctx* c, void* arena) {
   if (!c) return TTB_ERR_INVALID;
-  TTB_REQUIRE(c, !c->arena_active, "arena_release: the arena is active");
-  if (c->arena) {
-    DeviceGuard g(c->device);
-    TTB_CUDA(c, cudaStreamSynchronize(c->stream));
-    TTB_CUDA(c, cudaFree(c->arena));
-    c->arena = nullptr;
-    c->arena_size = 0;
+  if (!arena) return TTB_OK;
+  {
+    std::lock_guard<std::mutex> lk(c->mu);
+    size_t i = 0;
+    while (i < c->arenas.size() && c->arenas[i].first != arena) ++i;
+    if (i == c->arenas.size()) {
+      c->last_error = "arena_release: not an arena of this context";
+      return TTB_ERR_INVALID;
+    }
+    if (c->arena_active && c->arena == arena) {
+      c->last_error = "arena_release: the arena is active";
+      return TTB_ERR_INVALID;
+    }
+    c->arenas.erase(c->arenas.begin() + (long)i);
   }
+  DeviceGuard g(c->device);
+  TTB_CUDA(c, cudaDeviceSynchronize());  // graphs replayed on any stream may still be using the buffer
+  TTB_CUDA(c, cudaFree(arena));
   return TTB_OK;
 }
 

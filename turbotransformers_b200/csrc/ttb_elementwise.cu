@@ -1,5 +1,6 @@
 // Bandwidth-bound kernels: layer norm, bias/activation, embedding, pooling, transposes, softmax, quantise.
 // All are warp-per-row or 16-byte-vector grid-stride kernels; reductions use warp shuffles and fp32 math.
+#include <type_traits>
 #include <vector>
 
 #include "ttb_common.cuh"
@@ -17,73 +18,201 @@ inline int grid_for(int64_t work, int per_block, int sm_count) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// LayerNorm: out = LN(x [+ residual + bias]) * gamma + beta. One warp per row, row cached in registers.
-// ITERS vectors of 8 elements per lane: N % 8 == 0 and N <= 256*ITERS.
+// LayerNorm: out = LN(x [+ residual + bias]) * gamma + beta. One warp per pair of rows, both rows cached in registers
+// and all of their loads issued before the first reduction, so that a warp keeps 2 x N elements in flight.
+// ITERS vectors of 8 elements per lane and row: N % 8 == 0 and N <= 256*ITERS. x may be out (no __restrict__ on them).
+// TIn is the type of x / residual, TOut of gamma / beta / bias / out. EXTRA adds two optional outputs for models that
+// carry more precision than TOut between layers: out_lo = what rounding to TOut dropped, out_f32 = the fp32 value.
 // ------------------------------------------------------------------------------------------------
-template <typename T, int ITERS, bool ADD>
-__global__ void __launch_bounds__(kRowsPerBlock * 32)
-layernorm_rows_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ bias,
-                      const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ out, int64_t M, int N,
+constexpr int kLnWarps = 8;
+constexpr int kLnRows = 2;
+
+template <typename TIn, typename TOut, int ITERS, bool ADD, bool EXTRA>
+__global__ void __launch_bounds__(kLnWarps * 32)
+layernorm_rows_kernel(const TIn* x, const TIn* __restrict__ residual, const TOut* __restrict__ bias, const TOut* __restrict__ gamma,
+                      const TOut* __restrict__ beta, TOut* out, TOut* __restrict__ out_lo, float* __restrict__ out_f32, int64_t M, int N,
                       float eps) {
   pdl_trigger();
   pdl_wait();
   const int lane = threadIdx.x & 31;
-  const int warps_total = gridDim.x * kRowsPerBlock;
-  for (int64_t row = (int64_t)blockIdx.x * kRowsPerBlock + (threadIdx.x >> 5); row < M; row += warps_total) {
-    const T* xr = x + row * N;
-    float v[ITERS][8];
-    float sum = 0.f;
+  const int64_t warps_total = (int64_t)gridDim.x * kLnWarps;
+  for (int64_t row0 = ((int64_t)blockIdx.x * kLnWarps + (threadIdx.x >> 5)) * kLnRows; row0 < M; row0 += warps_total * kLnRows) {
+    float v[kLnRows][ITERS][8];
+    float sum[kLnRows];
 #pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-      const int col = (it * 32 + lane) * 8;
-      if (col < N) {
-        Vec8<T> a;
-        a.load(xr + col);
-        if (ADD) {
-          Vec8<T> r, b;
-          r.load(residual + row * N + col);
-          b.load(bias + col);
+    for (int r = 0; r < kLnRows; ++r) {
+      sum[r] = 0.f;
+      const int64_t row = row0 + r;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) a.v[j] = a.v[j] + r.v[j] + b.v[j];
+      for (int it = 0; it < ITERS; ++it) {
+        const int col = (it * 32 + lane) * 8;
+        if (row < M && col < N) {
+          Vec8<TIn> a;
+          a.load(x + row * N + col);
+          if (ADD) {
+            Vec8<TIn> rs;
+            Vec8<TOut> b;
+            rs.load(residual + row * N + col);
+            b.load(bias + col);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a.v[j] = a.v[j] + rs.v[j] + b.v[j];
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { v[r][it][j] = a.v[j]; sum[r] += a.v[j]; }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[r][it][j] = 0.f;
         }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) { v[it][j] = a.v[j]; sum += a.v[j]; }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[it][j] = 0.f;
       }
     }
-    const float mean = warp_sum(sum) / (float)N;
-    float sq = 0.f;
+    float mean[kLnRows], sq[kLnRows];
+#pragma unroll
+    for (int r = 0; r < kLnRows; ++r) mean[r] = warp_sum(sum[r]) / (float)N;
+#pragma unroll
+    for (int r = 0; r < kLnRows; ++r) {
+      sq[r] = 0.f;
+#pragma unroll
+      for (int it = 0; it < ITERS; ++it) {
+        const int col = (it * 32 + lane) * 8;
+        if (col < N) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { float d = v[r][it][j] - mean[r]; sq[r] += d * d; }
+        }
+      }
+    }
+    float rstd[kLnRows];
+#pragma unroll
+    for (int r = 0; r < kLnRows; ++r) rstd[r] = rsqrtf(warp_sum(sq[r]) / (float)N + eps);
 #pragma unroll
     for (int it = 0; it < ITERS; ++it) {
       const int col = (it * 32 + lane) * 8;
       if (col < N) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) { float d = v[it][j] - mean; sq += d * d; }
-      }
-    }
-    const float rstd = rsqrtf(warp_sum(sq) / (float)N + eps);
-#pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-      const int col = (it * 32 + lane) * 8;
-      if (col < N) {
-        Vec8<T> g, b, o;
+        Vec8<TOut> g, b;
         g.load(gamma + col);
         b.load(beta + col);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o.v[j] = b.v[j] + g.v[j] * rstd * (v[it][j] - mean);
-        o.store(out + row * N + col);
+        for (int r = 0; r < kLnRows; ++r) {
+          const int64_t row = row0 + r;
+          if (row < M) {
+            Vec8<TOut> o;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o.v[j] = b.v[j] + g.v[j] * rstd[r] * (v[r][it][j] - mean[r]);
+            o.store(out + row * N + col);
+            if (EXTRA) {
+              if (out_f32) {
+                Vec8<float> f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f.v[j] = o.v[j];
+                f.store(out_f32 + row * N + col);
+              }
+              if (out_lo) {
+                Vec8<TOut> l;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) l.v[j] = o.v[j] - to_f(from_f<TOut>(o.v[j]));
+                l.store(out_lo + row * N + col);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+}
+
+// The same for 16-bit rows without the residual form (the 16-bit models' hot case): the rows stay in registers as they
+// were loaded (packed 16-bit, half the registers of the fp32 form), so a warp holds four rows and two or three CTAs fit
+// an SM: 8 warps x 2..3 x 4 rows x N x 2 bytes in flight per SM.
+constexpr int kLn16Rows = 4;
+
+template <typename T, int ITERS, bool EXTRA>
+__global__ void __launch_bounds__(kLnWarps * 32, ITERS <= 2 ? 3 : 2)
+layernorm16_rows_kernel(const T* x, const T* __restrict__ gamma, const T* __restrict__ beta, T* out, T* __restrict__ out_lo,
+                        float* __restrict__ out_f32, int64_t M, int N, float eps) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_total = (int64_t)gridDim.x * kLnWarps;
+  for (int64_t row0 = ((int64_t)blockIdx.x * kLnWarps + (threadIdx.x >> 5)) * kLn16Rows; row0 < M; row0 += warps_total * kLn16Rows) {
+    uint4 raw[kLn16Rows][ITERS];
+#pragma unroll
+    for (int r = 0; r < kLn16Rows; ++r) {
+#pragma unroll
+      for (int it = 0; it < ITERS; ++it) {
+        const int col = (it * 32 + lane) * 8;
+        raw[r][it] = (row0 + r < M && col < N) ? *reinterpret_cast<const uint4*>(x + (row0 + r) * N + col) : make_uint4(0, 0, 0, 0);
+      }
+    }
+    auto unpack = [](const uint4& q, float (&f)[8]) {
+      const T* h = reinterpret_cast<const T*>(&q);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = to_f(h[j]);
+    };
+    // one pass for both moments, var = E[x^2] - mean^2 as the reference's CPU kernel computes it (layer_norm.cpp:58-66)
+    float mean[kLn16Rows], rstd[kLn16Rows];
+#pragma unroll
+    for (int r = 0; r < kLn16Rows; ++r) {
+      float sum = 0.f, sq = 0.f;
+#pragma unroll
+      for (int it = 0; it < ITERS; ++it) {
+        float f[8];
+        unpack(raw[r][it], f);   // lanes beyond N hold zeros
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { sum += f[j]; sq = fmaf(f[j], f[j], sq); }
+        // the packed words stay the only live copy of the row: the second pass converts them again
+        asm volatile("" : "+r"(raw[r][it].x), "+r"(raw[r][it].y), "+r"(raw[r][it].z), "+r"(raw[r][it].w));
+      }
+      mean[r] = sum;
+      rstd[r] = sq;
+    }
+#pragma unroll
+    for (int r = 0; r < kLn16Rows; ++r) {
+      mean[r] = warp_sum(mean[r]) / (float)N;
+      const float var = fmaxf(warp_sum(rstd[r]) / (float)N - mean[r] * mean[r], 0.f);
+      rstd[r] = rsqrtf(var + eps);
+    }
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int col = (it * 32 + lane) * 8;
+      if (col < N) {
+        const uint4 gq = *reinterpret_cast<const uint4*>(gamma + col), bq = *reinterpret_cast<const uint4*>(beta + col);
+#pragma unroll
+        for (int r = 0; r < kLn16Rows; ++r) {
+          const int64_t row = row0 + r;
+          if (row < M) {
+            float f[8], g[8], b[8];
+            unpack(raw[r][it], f);
+            unpack(gq, g);
+            unpack(bq, b);
+            Vec8<T> o;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o.v[j] = b[j] + g[j] * rstd[r] * (f[j] - mean[r]);
+            o.store(out + row * N + col);
+            if (EXTRA) {
+              if (out_f32) {
+                Vec8<float> w;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) w.v[j] = o.v[j];
+                w.store(out_f32 + row * N + col);
+              }
+              if (out_lo) {
+                Vec8<T> l;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) l.v[j] = o.v[j] - to_f(from_f<T>(o.v[j]));
+                l.store(out_lo + row * N + col);
+              }
+            }
+          }
+        }
       }
     }
   }
 }
 
 // Any N: one warp per row, three passes over the row (the re-reads hit L1/L2).
-template <typename T, bool ADD>
+template <typename TIn, typename TOut, bool ADD>
 __global__ void __launch_bounds__(kRowsPerBlock * 32)
-layernorm_rows_generic_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ bias,
-                              const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ out, int64_t M,
+layernorm_rows_generic_kernel(const TIn* x, const TIn* __restrict__ residual, const TOut* __restrict__ bias, const TOut* __restrict__ gamma,
+                              const TOut* __restrict__ beta, TOut* out, TOut* __restrict__ out_lo, float* __restrict__ out_f32, int64_t M,
                               int N, float eps) {
   const int lane = threadIdx.x & 31;
   const int warps_total = gridDim.x * kRowsPerBlock;
@@ -101,31 +230,64 @@ layernorm_rows_generic_kernel(const T* __restrict__ x, const T* __restrict__ res
     const float rstd = rsqrtf(warp_sum(sq) / (float)N + eps);
     // x may alias out: every lane reads only the columns it then writes.
     for (int c = lane; c < N; c += 32) {
-      float a = val(c);
-      out[row * N + c] = from_f<T>(to_f(beta[c]) + to_f(gamma[c]) * rstd * (a - mean));
+      const float y = to_f(beta[c]) + to_f(gamma[c]) * rstd * (val(c) - mean);
+      out[row * N + c] = from_f<TOut>(y);
+      if (out_f32) out_f32[row * N + c] = y;
+      if (out_lo) out_lo[row * N + c] = from_f<TOut>(y - to_f(from_f<TOut>(y)));
     }
   }
 }
 
-template <typename T, bool ADD>
-int launch_layernorm(ttb_ctx* ctx, const T* x, const T* residual, const T* bias, const T* gamma, const T* beta, T* out,
-                     int64_t M, int64_t N, float eps) {
+template <typename TIn, typename TOut, bool ADD>
+int launch_layernorm(ttb_ctx* ctx, const TIn* x, const TIn* residual, const TOut* bias, const TOut* gamma, const TOut* beta, TOut* out,
+                     TOut* out_lo, float* out_f32, int64_t M, int64_t N, float eps) {
   if (M == 0) return TTB_OK;
-  const int grid = grid_for(M, kRowsPerBlock, ctx->sm_count);
-  const int block = kRowsPerBlock * 32;
-#define LN_CASE(IT)                                                                                             \
-  launch_pdl(layernorm_rows_kernel<T, IT, ADD>, dim3(grid), dim3(block), 0, ctx->stream, x, residual, bias, gamma, beta, out, M, (int)N, eps)
-  const bool aligned = (N % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) |
-                                         reinterpret_cast<uintptr_t>(gamma) | reinterpret_cast<uintptr_t>(beta) |
+  const int64_t pair_warps = (M + kLnRows - 1) / kLnRows;
+  const int grid = grid_for(pair_warps, kLnWarps, ctx->sm_count);
+  const int block = kLnWarps * 32;
+  const bool extra = out_lo != nullptr || out_f32 != nullptr;
+#define LN_CASE(IT)                                                                                                              \
+  do {                                                                                                                           \
+    if (extra)                                                                                                                   \
+      launch_pdl(layernorm_rows_kernel<TIn, TOut, IT, ADD, true>, dim3(grid), dim3(block), 0, ctx->stream, x, residual, bias, gamma, beta, \
+                 out, out_lo, out_f32, M, (int)N, eps);                                                                          \
+    else                                                                                                                         \
+      launch_pdl(layernorm_rows_kernel<TIn, TOut, IT, ADD, false>, dim3(grid), dim3(block), 0, ctx->stream, x, residual, bias, gamma, beta, \
+                 out, out_lo, out_f32, M, (int)N, eps);                                                                          \
+  } while (0)
+  const bool aligned = (N % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(out_lo) |
+                                         reinterpret_cast<uintptr_t>(out_f32) | reinterpret_cast<uintptr_t>(gamma) |
+                                         reinterpret_cast<uintptr_t>(beta) |
                                          (ADD ? (reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(bias)) : 0)) %
                                             16 == 0);
+  if constexpr (!ADD && std::is_same<TIn, TOut>::value && sizeof(TIn) == 2) {
+    if (aligned && N <= 1024) {
+      const int grid16 = grid_for((M + kLn16Rows - 1) / kLn16Rows, kLnWarps, ctx->sm_count);
+#define LN16_CASE(IT)                                                                                                                  \
+  do {                                                                                                                                 \
+    if (extra)                                                                                                                         \
+      launch_pdl(layernorm16_rows_kernel<TOut, IT, true>, dim3(grid16), dim3(block), 0, ctx->stream, x, gamma, beta, out, out_lo, out_f32, M, \
+                 (int)N, eps);                                                                                                         \
+    else                                                                                                                               \
+      launch_pdl(layernorm16_rows_kernel<TOut, IT, false>, dim3(grid16), dim3(block), 0, ctx->stream, x, gamma, beta, out, out_lo, out_f32, M, \
+                 (int)N, eps);                                                                                                         \
+  } while (0)
+      if (N <= 256) LN16_CASE(1);
+      else if (N <= 512) LN16_CASE(2);
+      else if (N <= 768) LN16_CASE(3);
+      else LN16_CASE(4);
+#undef LN16_CASE
+      return launched(ctx, "layernorm");
+    }
+  }
   if (aligned && N <= 256) LN_CASE(1);
   else if (aligned && N <= 512) LN_CASE(2);
   else if (aligned && N <= 768) LN_CASE(3);
   else if (aligned && N <= 1024) LN_CASE(4);
   else if (aligned && N <= 2048) LN_CASE(8);
   else
-    layernorm_rows_generic_kernel<T, ADD><<<grid, block, 0, ctx->stream>>>(x, residual, bias, gamma, beta, out, M, (int)N, eps);
+    layernorm_rows_generic_kernel<TIn, TOut, ADD><<<grid_for(M, kRowsPerBlock, ctx->sm_count), kRowsPerBlock * 32, 0, ctx->stream>>>(
+        x, residual, bias, gamma, beta, out, out_lo, out_f32, M, (int)N, eps);
 #undef LN_CASE
   return launched(ctx, "layernorm");
 }
@@ -211,7 +373,7 @@ embedding_ln_kernel(const int64_t* __restrict__ ids, const int64_t* __restrict__
                     int64_t n_tokens, const T* __restrict__ word, const T* __restrict__ position,
                     const T* __restrict__ token_type, const T* __restrict__ gamma, const T* __restrict__ beta,
                     int hidden, int64_t vocab, int64_t n_pos, int64_t n_types, float eps, T* __restrict__ out,
-                    int* status) {
+                    T* __restrict__ out_lo, float* __restrict__ out_f32, int* status) {
   const int lane = threadIdx.x & 31;
   const int warps_total = gridDim.x * kRowsPerBlock;
   for (int64_t t = (int64_t)blockIdx.x * kRowsPerBlock + (threadIdx.x >> 5); t < n_tokens; t += warps_total) {
@@ -236,8 +398,12 @@ embedding_ln_kernel(const int64_t* __restrict__ ids, const int64_t* __restrict__
     float sq = 0.f;
     for (int c = lane; c < hidden; c += 32) { float d = val(c) - mean; sq += d * d; }
     const float rstd = rsqrtf(warp_sum(sq) / (float)hidden + eps);
-    for (int c = lane; c < hidden; c += 32)
-      out[t * hidden + c] = from_f<T>(to_f(beta[c]) + to_f(gamma[c]) * rstd * (val(c) - mean));
+    for (int c = lane; c < hidden; c += 32) {
+      const float y = to_f(beta[c]) + to_f(gamma[c]) * rstd * (val(c) - mean);
+      out[t * hidden + c] = from_f<T>(y);
+      if (out_f32) out_f32[t * hidden + c] = y;
+      if (out_lo) out_lo[t * hidden + c] = from_f<T>(y - to_f(from_f<T>(y)));
+    }
   }
 }
 
@@ -497,8 +663,8 @@ extern "C" int ttb_add_bias_layernorm(ttb_ctx* ctx, int dtype, void* out, const 
   TTB_REQUIRE(ctx, M == 0 || (out && input && bias && gamma && beta), "add_bias_layernorm: null pointer");
   DeviceGuard g(ctx->device);
   TTB_DISPATCH_FLOAT(ctx, dtype, T,
-                     return (launch_layernorm<T, true>(ctx, (const T*)out, (const T*)input, (const T*)bias, (const T*)gamma,
-                                                       (const T*)beta, (T*)out, M, N, eps)));
+                     return (launch_layernorm<T, T, true>(ctx, (const T*)out, (const T*)input, (const T*)bias, (const T*)gamma,
+                                                          (const T*)beta, (T*)out, nullptr, nullptr, M, N, eps)));
   return TTB_OK;
 }
 
@@ -509,9 +675,29 @@ extern "C" int ttb_layernorm(ttb_ctx* ctx, int dtype, const void* in, void* out,
   TTB_REQUIRE(ctx, M == 0 || (in && out && gamma && beta), "layernorm: null pointer");
   DeviceGuard g(ctx->device);
   TTB_DISPATCH_FLOAT(ctx, dtype, T,
-                     return (launch_layernorm<T, false>(ctx, (const T*)in, nullptr, nullptr, (const T*)gamma,
-                                                        (const T*)beta, (T*)out, M, N, eps)));
+                     return (launch_layernorm<T, T, false>(ctx, (const T*)in, nullptr, nullptr, (const T*)gamma,
+                                                           (const T*)beta, (T*)out, nullptr, nullptr, M, N, eps)));
   return TTB_OK;
+}
+
+extern "C" int ttb_layernorm_planes(ttb_ctx* ctx, int in_dtype, int out_dtype, const void* in, void* out, void* out_lo, float* out_f32,
+                                    const void* gamma, const void* beta, int64_t M, int64_t N, float eps) {
+  if (!ctx) return TTB_ERR_INVALID;
+  TTB_REQUIRE(ctx, M >= 0 && N > 0, "layernorm_planes: bad shape");
+  TTB_REQUIRE(ctx, M == 0 || (in && out && gamma && beta), "layernorm_planes: null pointer");
+  TTB_REQUIRE(ctx, out_dtype == TTB_F16 || out_dtype == TTB_BF16, "layernorm_planes: the output dtype must be F16 or BF16");
+  TTB_REQUIRE(ctx, in_dtype == out_dtype || in_dtype == TTB_F32, "layernorm_planes: the input is of the output dtype or F32");
+  DeviceGuard g(ctx->device);
+  if (out_dtype == TTB_F16) {
+    using T = __half;
+    if (in_dtype == TTB_F32)
+      return launch_layernorm<float, T, false>(ctx, (const float*)in, nullptr, nullptr, (const T*)gamma, (const T*)beta, (T*)out, (T*)out_lo, out_f32, M, N, eps);
+    return launch_layernorm<T, T, false>(ctx, (const T*)in, nullptr, nullptr, (const T*)gamma, (const T*)beta, (T*)out, (T*)out_lo, out_f32, M, N, eps);
+  }
+  using T = __nv_bfloat16;
+  if (in_dtype == TTB_F32)
+    return launch_layernorm<float, T, false>(ctx, (const float*)in, nullptr, nullptr, (const T*)gamma, (const T*)beta, (T*)out, (T*)out_lo, out_f32, M, N, eps);
+  return launch_layernorm<T, T, false>(ctx, (const T*)in, nullptr, nullptr, (const T*)gamma, (const T*)beta, (T*)out, (T*)out_lo, out_f32, M, N, eps);
 }
 
 extern "C" int ttb_add_bias_act(ttb_ctx* ctx, int dtype, void* out, const void* bias, int64_t M, int64_t N, int act) {
@@ -581,6 +767,15 @@ extern "C" int ttb_embedding_ln(ttb_ctx* ctx, int dtype, const int64_t* ids, con
                                 int64_t n_tokens, const void* word, const void* position, const void* token_type,
                                 const void* gamma, const void* beta, int64_t hidden, int64_t vocab,
                                 int64_t n_positions, int64_t n_types, float eps, void* out) {
+  return ttb_embedding_ln_planes(ctx, dtype, ids, position_ids, token_type_ids, cu_seqlens, B, seq_len, n_tokens, word, position, token_type,
+                                 gamma, beta, hidden, vocab, n_positions, n_types, eps, out, nullptr, nullptr);
+}
+
+extern "C" int ttb_embedding_ln_planes(ttb_ctx* ctx, int dtype, const int64_t* ids, const int64_t* position_ids,
+                                       const int64_t* token_type_ids, const int32_t* cu_seqlens, int64_t B, int64_t seq_len,
+                                       int64_t n_tokens, const void* word, const void* position, const void* token_type,
+                                       const void* gamma, const void* beta, int64_t hidden, int64_t vocab, int64_t n_positions,
+                                       int64_t n_types, float eps, void* out, void* out_lo, float* out_f32) {
   if (!ctx) return TTB_ERR_INVALID;
   TTB_REQUIRE(ctx, n_tokens >= 0 && hidden > 0 && vocab > 0 && n_positions > 0 && n_types > 0, "embedding_ln: bad shape");
   if (n_tokens == 0) return TTB_OK;
@@ -593,7 +788,7 @@ extern "C" int ttb_embedding_ln(ttb_ctx* ctx, int dtype, const int64_t* ids, con
                      (embedding_ln_kernel<T><<<grid, kRowsPerBlock * 32, 0, ctx->stream>>>(
                          ids, position_ids, token_type_ids, cu_seqlens, (int)B, (int)(seq_len > 0 ? seq_len : 1), n_tokens,
                          (const T*)word, (const T*)position, (const T*)token_type, (const T*)gamma, (const T*)beta,
-                         (int)hidden, vocab, n_positions, n_types, eps, (T*)out, ctx->d_status)));
+                         (int)hidden, vocab, n_positions, n_types, eps, (T*)out, (T*)out_lo, out_f32, ctx->d_status)));
   return launched(ctx, "embedding_ln");
 }
 
@@ -746,9 +941,46 @@ extern "C" int ttb_quantize_tensor_affine(ttb_ctx* ctx, int dtype, const void* x
   return launched(ctx, "quantize_tensor_affine");
 }
 
+namespace {
+// Up to this many lengths travel inside the kernel's parameter block: no staging copy and nothing for the host to wait for.
+constexpr int kLensInParams = 960;
+struct LensParam {
+  int32_t v[kLensInParams];
+};
+__global__ void cu_seqlens_from_params_kernel(const LensParam lens, int B, int32_t* __restrict__ cu) {
+  // one warp: an inclusive scan over chunks of 32 lengths, carrying the running total
+  const int lane = threadIdx.x;
+  int carry = 0;
+  if (lane == 0) cu[0] = 0;
+  for (int base = 0; base < B; base += 32) {
+    int v = (base + lane < B) ? lens.v[base + lane] : 0;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, v, o);
+      if (lane >= o) v += n;
+    }
+    if (base + lane < B) cu[base + lane + 1] = carry + v;
+    carry += __shfl_sync(0xffffffffu, v, 31);
+  }
+}
+}  // namespace
+
 extern "C" int ttb_build_cu_seqlens(ttb_ctx* ctx, const int64_t* host_seq_lens, int64_t B, int32_t* cu_dev) {
   if (!ctx) return TTB_ERR_INVALID;
   TTB_REQUIRE(ctx, B >= 0 && (B == 0 || host_seq_lens) && cu_dev, "build_cu_seqlens: bad arguments");
+  if (B <= kLensInParams) {
+    LensParam lp;
+    int64_t total = 0;
+    for (int64_t b = 0; b < B; ++b) {
+      TTB_REQUIRE(ctx, host_seq_lens[b] >= 0, "build_cu_seqlens: negative length at %lld", (long long)b);
+      total += host_seq_lens[b];
+      TTB_REQUIRE(ctx, total <= INT32_MAX, "build_cu_seqlens: more than 2^31 tokens");
+      lp.v[b] = (int32_t)host_seq_lens[b];
+    }
+    DeviceGuard g(ctx->device);
+    cu_seqlens_from_params_kernel<<<1, 32, 0, ctx->stream>>>(lp, (int)B, cu_dev);
+    return launched(ctx, "build_cu_seqlens");
+  }
   std::vector<int32_t> cu((size_t)B + 1, 0);
   for (int64_t b = 0; b < B; ++b) {
     TTB_REQUIRE(ctx, host_seq_lens[b] >= 0, "build_cu_seqlens: negative length at %lld", (long long)b);

@@ -52,7 +52,17 @@ extern "C" int ttb_linear_int8_dynamic_noalloc(ttb_ctx* ctx, int dtype, const vo
               "linear_int8_dynamic_noalloc: M=%lld K=%lld exceeds the built-in scratch (M <= %zu rows and M*K <= %zu); "
               "use ttb_quantize_rows_int8 + ttb_linear_int8 with caller-provided buffers for larger problems",
               (long long)M, (long long)K, kMaxRows, kMaxActivationBytes);
+  // Everything the two kernels below would reject is rejected here, so that a refused call has launched nothing and
+  // has not touched the shared scratch.
+  TTB_REQUIRE(ctx, dtype == TTB_F16 || dtype == TTB_BF16, "linear_int8_dynamic_noalloc: dtype must be F16 or BF16");
+  TTB_REQUIRE(ctx, epilogue >= TTB_EPI_NONE && epilogue <= TTB_EPI_BIAS_TANH, "linear_int8_dynamic_noalloc: unknown epilogue %d", epilogue);
+  TTB_REQUIRE(ctx, K % 16 == 0, "linear_int8_dynamic_noalloc: K=%lld must be a multiple of 16", (long long)K);
+  TTB_REQUIRE(ctx, ldo >= N, "linear_int8_dynamic_noalloc: ldo < N");
   if (M == 0) return TTB_OK;
+  TTB_REQUIRE(ctx, x && Wq && w_scale && out, "linear_int8_dynamic_noalloc: null pointer");
+  TTB_REQUIRE(ctx, epilogue == TTB_EPI_NONE || bias, "linear_int8_dynamic_noalloc: epilogue %d needs a bias", epilogue);
+  TTB_REQUIRE(ctx, epilogue != TTB_EPI_BIAS_RESIDUAL || residual, "linear_int8_dynamic_noalloc: the residual epilogue needs a residual");
+  TTB_REQUIRE(ctx, reinterpret_cast<uintptr_t>(Wq) % 16 == 0, "linear_int8_dynamic_noalloc: the weights must be 16-byte aligned");
   unsigned char* scratch = nullptr;
   int s = scratch_for(ctx, &scratch);
   if (s != TTB_OK) return s;

@@ -4,7 +4,8 @@ A forward pass of this library is some ninety small launches; at batch 1 the hos
 retires them. `CapturedForward` records the launches once into a CUDA graph and replays it: the pass then costs one graph
 launch on the host. During the capture the library's allocator runs in arena mode (`ttb_arena_begin`): every temporary and the
 outputs get fixed addresses inside one reserved buffer, so the graph can be replayed as is. The shapes (and, for variable-length
-batches, the lengths) are frozen into the graph: use one CapturedForward per shape.
+batches, the lengths) are frozen into the graph: use one CapturedForward per shape. Every CapturedForward owns the buffer
+its graph runs over (several may be alive and replayed in any order); `close()` or garbage collection releases it.
 
     fwd = CapturedForward(lambda ids: model(ids), example_ids)      # example_ids: a CUDA tensor, becomes the static input
     seq, pooled = fwd(new_ids)                                      # copies new_ids in, replays, returns the static outputs
@@ -45,11 +46,29 @@ class CapturedForward:
             with torch.cuda.graph(self.graph):
                 self.outputs = fn(*static_inputs)
         finally:
-            self.arena_used = cxx.arena_end(self.device)
+            self.arena_used, self._arena = cxx.arena_end(self.device)
+            # the capture ran on a side stream: point the library back at the caller's stream
+            cxx.set_stream(self.device, torch.cuda.current_stream(self.device).cuda_stream)
+
+    def close(self):
+        """Drops the graph and releases its buffer (the returned output tensors become invalid)."""
+        arena, self._arena = getattr(self, "_arena", 0), 0
+        if arena:
+            self.graph = None
+            self.outputs = None
+            cxx.arena_release(self.device, arena)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
     def __call__(self, *inputs: torch.Tensor):
         for dst, src in zip(self.inputs, inputs):
             if dst.data_ptr() != src.data_ptr():
                 dst.copy_(src, non_blocking=True)
+        if self.graph is None:
+            raise RuntimeError("this CapturedForward has been closed")
         self.graph.replay()
         return self.outputs

@@ -59,8 +59,9 @@ class GPT2Model:
             m = torch.triu(torch.full((L, L), -10000.0, dtype=torch.float32, device="cuda"), 1)
             mask = convert2tt_tensor(m.unsqueeze(0).repeat(B, 1, 1).contiguous())
         for i, (attn, ffn) in enumerate(self.blocks):
-            a, probs, y = _empty(), _empty(), _empty()
-            attn(x, x, x, mask, "self", a, probs, past[i] if past is not None else {}, True, False, True, False)  # pre-LN, + input
+            a, y = _empty(), _empty()
+            # no score tensor is asked for (None): 16-bit models run the fused attention kernel; pre-LN, + input
+            attn(x, x, x, mask, "self", a, None, past[i] if past is not None else {}, True, False, True, False)
             ffn(a, y, False)
             x = y
         h = _empty()

@@ -162,7 +162,10 @@ class BertModelNoPoolerSmartBatch:
         ids = pack_ids(inputs)
         use_current_stream(ids)
         hidden = cxx.Tensor.create_empty()
-        self.embeddings.packed(convert2tt_tensor(ids), lens, hidden)
+        # segment and position ids are packed the same way as the ids (one per token, requests back to back)
+        pos = convert2tt_tensor(pack_ids(position_ids)) if position_ids is not None else cxx.Tensor.create_empty()
+        types = convert2tt_tensor(pack_ids(token_type_ids)) if token_type_ids is not None else cxx.Tensor.create_empty()
+        self.embeddings.packed(convert2tt_tensor(ids), lens, hidden, pos, types)
         return self.encoder(hidden_states=hidden, query_seq_len_list=lens, attention_mask=attention_masks,
                             output_attentions=output_attentions, output_hidden_states=output_hidden_states, return_type=return_type)
 
