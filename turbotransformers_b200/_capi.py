@@ -159,6 +159,10 @@ class Context:
                        epilogue, ptr(out), ptr(out_lo), ldo or N)
         self.check(lib().ttb_linear_ex(self.h, C.byref(a)))
 
+    def set_stream(self, cuda_stream):
+        """Queue what follows on this cudaStream_t (an int; 0 = the legacy default stream)."""
+        self.check(lib().ttb_ctx_set_stream(self.h, p(cuda_stream) if cuda_stream else None))
+
     def device_status(self):
         return lib().ttb_device_status(self.h)
 

@@ -3,15 +3,21 @@
 // Persistent kernel, one CTA per SM, two independent streams per CTA. A work item is one 128-row query tile of one
 // (sequence, head); a stream takes every other item of its CTA and walks the key/value tiles (128 rows) of one item
 // after the other as one flat sequence of tiles g = 0, 1, 2, ...
-//   warps 0, 2  : TMA loaders of stream 0 / 1 - the item's Q tile (double-buffered), then K_g / V_g into a 2-stage ring.
+//   warps 0, 2  : TMA loaders of stream 0 / 1 - the item's Q tile (double-buffered) and K_g / V_g into 2-stage rings, by
+//                 two independent cursors (Q + K tiles, V tiles) that each issue as soon as their slot is free, so the next
+//                 item's Q and first K tile are in flight a whole tile before they are needed.
 //                 Every tile is a [128 rows x 64 columns] 128-byte-swizzled box straight out of the [T, 3H] QKV matrix.
 //   warps 1, 3  : MMA issuers of stream 0 / 1 - S = Q K_g^T (128x128x64, fp32 in TMEM) and O += P V_g (128x64x128) with P
 //                 read from TMEM and V used in place as an MN-major operand. Per stream the order is
 //                 QK(0) | QK(g+1) PV(g) | ..., across item boundaries: QK(g+1) goes out as soon as the softmax warps hold
 //                 the scores of tile g in registers, so the next scores are in TMEM before the current softmax ends. A
 //                 wait in an issuing thread only returns once the MMAs that thread has issued have drained, so each
-//                 stream has its own issuer, and an issuer waits on one barrier per MMA group: the softmax warps vouch
-//                 for the Q/K/V tiles a group reads.
+//                 stream has its own issuer. It waits for the softmax warps' go-ahead first (which lets its earlier MMAs
+//                 drain) and then for the operand tiles of the group (a barrier poll each): the softmax warps never wait
+//                 on a load. Measured with per-phase cycle stamps on 32 x 512: a stream's tile period is the softmax
+//                 warps' serial chain (score load 350-600 cycles, 128 exponentials per thread 2000-2900 while the other
+//                 stream's warp shares the scheduler, P store 150-400, two satisfied barrier waits 200-350 each) plus about
+//                 one tile's worth per item for the row maximum, the output pass and the item bookkeeping.
 //   warps 4..7  : softmax of stream 0, warps 8..11: of stream 1 (registers are moved from the first
 //                 warpgroup to the softmax ones with setmaxnreg) - one query row per thread: scores from TMEM, running
 //                 max / sum in fp32, exp2 with the scale folded in, P written back to TMEM as packed 16-bit pairs.
@@ -214,23 +220,80 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
       // ------------------------------------------------------------------ loader of stream `s`
       const int s = warp >> 1;
       if (lane == 0) {
-        uint32_t g = 0, nq = 0;
-        bool ok = true;
-        for (int i = 2 * (int)blockIdx.x + s; i < n_items && ok; i += stride, ++nq) {
-          const Item it = decode_item(i, p, s_cu, s_prefix, s_order);
-          const int b = nq & 1;
-          if (!mbar_wait(q_empty(s, b), ((nq >> 1) & 1u) ^ 1u, abort_flag)) break;
-          mbar_expect_tx(q_full(s, b), TILE_BYTES);
-          tma_load_2d(smem_q(s, b), &tm, q_full(s, b), it.head * D, it.tok0 + it.q0);
-          for (int j = 0; j < it.n; ++j, ++g) {
-            const int st = g & 1;
-            const uint32_t par = ((g >> 1) & 1u) ^ 1u;
-            if (!mbar_wait(k_empty(s, st), par, abort_flag)) { ok = false; break; }
-            mbar_expect_tx(k_full(s, st), TILE_BYTES);
-            tma_load_2d(smem_k(s, st), &tm, k_full(s, st), H + it.head * D, it.tok0 + j * KT);
-            if (!mbar_wait(v_empty(s, st), par, abort_flag)) { ok = false; break; }
-            mbar_expect_tx(v_full(s, st), TILE_BYTES);
-            tma_load_2d(smem_v(s, st), &tm, v_full(s, st), 2 * H + it.head * D, it.tok0 + j * KT);
+        // Two cursors walk the stream's tile sequence independently: one issues Q and K tiles, the other V tiles, each
+        // as soon as its ring slot is free. (Were they one in-order sequence, the next item's Q and first K tile would
+        // queue behind the current item's last V tile, whose slot frees late, and arrive a tile too late.) Nothing
+        // blocks: slots are polled, and the thread gives up when neither cursor has moved for the wait limit.
+        struct LoadCursor {
+          int i, j, n;
+          uint32_t g, nq;
+          Item it;
+        } kc, vc;
+        kc.i = 2 * (int)blockIdx.x + s;
+        kc.j = 0;
+        kc.g = 0;
+        kc.nq = 0;
+        kc.n = 0;
+        if (kc.i < n_items) {
+          kc.it = decode_item(kc.i, p, s_cu, s_prefix, s_order);
+          kc.n = kc.it.n;
+        }
+        vc = kc;
+        bool q_issued = false;
+        auto advance = [&](LoadCursor& c) {
+          ++c.g;
+          if (++c.j == c.n) {
+            c.j = 0;
+            c.i += stride;
+            ++c.nq;
+            if (c.i < n_items) {
+              c.it = decode_item(c.i, p, s_cu, s_prefix, s_order);
+              c.n = c.it.n;
+            }
+          }
+        };
+        long long t_progress = clock64();
+        while (kc.i < n_items || vc.i < n_items) {
+          bool progressed = false;
+          if (kc.i < n_items) {
+            if (kc.j == 0 && !q_issued) {
+              const int b = kc.nq & 1;
+              if (mbar_test_wait(q_empty(s, b), ((kc.nq >> 1) & 1u) ^ 1u)) {
+                mbar_expect_tx(q_full(s, b), TILE_BYTES);
+                tma_load_2d(smem_q(s, b), &tm, q_full(s, b), kc.it.head * D, kc.it.tok0 + kc.it.q0);
+                q_issued = true;
+                progressed = true;
+              }
+            }
+            if (kc.j > 0 || q_issued) {
+              const int st = kc.g & 1;
+              if (mbar_test_wait(k_empty(s, st), ((kc.g >> 1) & 1u) ^ 1u)) {
+                mbar_expect_tx(k_full(s, st), TILE_BYTES);
+                tma_load_2d(smem_k(s, st), &tm, k_full(s, st), H + kc.it.head * D, kc.it.tok0 + kc.j * KT);
+                advance(kc);
+                if (kc.j == 0) q_issued = false;
+                progressed = true;
+              }
+            }
+          }
+          if (vc.i < n_items) {
+            const int st = vc.g & 1;
+            if (mbar_test_wait(v_empty(s, st), ((vc.g >> 1) & 1u) ^ 1u)) {
+              mbar_expect_tx(v_full(s, st), TILE_BYTES);
+              tma_load_2d(smem_v(s, st), &tm, v_full(s, st), 2 * H + vc.it.head * D, vc.it.tok0 + vc.j * KT);
+              advance(vc);
+              progressed = true;
+            }
+          }
+          if (progressed) {
+            t_progress = clock64();
+          } else {
+            if (*abort_flag) break;
+            if (clock64() - t_progress > kWaitCycles) {
+              *abort_flag = 1;
+              break;
+            }
+            __nanosleep(64);
           }
         }
         if (*abort_flag) {  // let copies in flight land before shared memory is released
@@ -272,9 +335,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
           if (qc.j == qc.n - 1) tc_commit(q_empty(s, qb));  // last reader of this item's Q
           advance(qc);
         };
-        // first tile: nothing is in flight yet, so waiting here costs nothing
+        // The operand tiles of a group are waited for here, right before the group is issued and after the wait on
+        // the softmax warps (which has already let the MMAs issued before it drain, so these cost a barrier poll each).
+        auto operands_of_qk = [&]() {
+          bool landed = mbar_wait(k_full(s, qc.g & 1), (qc.g >> 1) & 1u, abort_flag);
+          if (landed && qc.j == 0) landed = mbar_wait(q_full(s, qc.nq & 1), (qc.nq >> 1) & 1u, abort_flag);
+          return landed;
+        };
         if (qc.i < n_items) {
-          ok = mbar_wait(q_full(s, 0), 0, abort_flag) && mbar_wait(k_full(s, 0), 0, abort_flag);
+          ok = operands_of_qk();
           if (ok) qk();
         }
         while (ok && pc.i < n_items) {
@@ -282,11 +351,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
           // for the Q and K tiles the MMA reads)
           if (qc.i < n_items) {
             if (!mbar_wait(s_free(s), (qc.g - 1) & 1u, abort_flag)) break;
+            if (!operands_of_qk()) break;
             tc_fence_after();
             qk();
           }
           // O (+)= P V_g once the softmax warps have released P (and vouched for V_g)
           if (!mbar_wait(p_ready(s), pc.g & 1u, abort_flag)) break;
+          if (!mbar_wait(v_full(s, pc.g & 1), (pc.g >> 1) & 1u, abort_flag)) break;
           tc_fence_after();
           const int st = pc.g & 1;
           const uint32_t v_lo = desc_lo(smem_v(s, st));
@@ -342,7 +413,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
 
     for (int i = 2 * (int)blockIdx.x + s; i < n_items && ok; i += stride, ++nq) {
       const Item it = decode_item(i, p, s_cu, s_prefix, s_order);
-      const bool has_next = i + stride < n_items;
       const int qrow = it.q0 + row;  // row within the sequence
       float m_used = -INFINITY, l_run = 0.f;
 
@@ -353,12 +423,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
         uint32_t sr[4][32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32_issue(ts + (uint32_t)(c * 32), sr[c]);
-        // the stream's next score MMA reads K_{g+1}, and the next item's Q when this is the item's last tile
-        if (j + 1 < it.n || has_next) {
-          bool landed = mbar_wait(k_full(s, (g + 1) & 1), ((g + 1) >> 1) & 1u, abort_flag);
-          if (j + 1 == it.n) landed = mbar_wait(q_full(s, (nq + 1) & 1), ((nq + 1) >> 1) & 1u, abort_flag) && landed;
-          if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }
-        }
         tmem_ld_wait();
         tc_fence_before();  // S_g is in registers: the next scores may overwrite it (one phase per tile)
         __syncwarp();
@@ -366,8 +430,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
         // The previous item's output pass. It reads O before this warp's next p_ready arrival, which is what the next
         // output MMA (the one that overwrites O) waits for; it also proves PV(g-1) complete, so P may be rewritten.
         if (pend && !flush_output()) { ok = false; break; }
-        // the output MMA released by this tile's P reads V_g
-        if (!__all_sync(0xffffffffu, mbar_wait(v_full(s, g & 1), (g >> 1) & 1u, abort_flag))) { ok = false; break; }
         // keys of this tile that at least one row of this warp can see, in 32-key chunks: the others cost no exponentials
         int lim = it.len - k0;
         if (p.causal) lim = min(lim, it.q0 + quad * 32 + 32 - k0);

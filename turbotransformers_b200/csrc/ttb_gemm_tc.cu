@@ -39,7 +39,8 @@ constexpr int BM = 128;          // rows of A per tile == TMEM lanes
 constexpr int BK_BYTES = 128;    // bytes of K per ring slot row: one 128-byte swizzle span
 constexpr int UMMA_K_BYTES = 32; // K bytes consumed by one tcgen05.mma (16 x 16-bit, 32 x 8-bit, 8 x tf32)
 constexpr int kThreads = 320;    // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue (two per TMEM lane quarter)
-constexpr int kMaxSplit = 6;     // CTAs of a cluster that may share one tile's K range
+constexpr int kMaxSplit = 4;     // CTAs of a cluster that may share one tile's K range (clusters of 6 pack badly into the GPCs:
+                                 // 24 of them did not fit the chip at once and the launch took two waves)
 
 // TWO = a pair of CTAs (one cluster of two SMs) computes a 256 x BN tile with cta_group::2 MMAs: each CTA stages its
 // own 128 rows of A and its own half (BN/2 rows) of W, so a k-block costs 32 KB of L2->SM traffic per CTA instead of 48.
@@ -191,6 +192,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+  if (threadIdx.x == 32) {  // the descriptors are kernel parameters: fetching them does not depend on the previous kernel
+    prefetch_tensormap(&tmA0);
+    prefetch_tensormap(&tmB0);
+    if (p.npass > 1) {
+      prefetch_tensormap(&tmA1);
+      prefetch_tensormap(&tmB1);
+    }
+    if (p.tma_store) prefetch_tensormap(&tmO);
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(full_bar(s), 1);
@@ -755,12 +765,47 @@ int pair_mode() {
   }();
   return mode;
 }
-bool splitk_enabled() {
-  static const bool on = [] {
+// TTB_GEMM_SPLITK: 0 disables split-K, 2..6 caps the number of CTAs that share a tile (measurement switch).
+int splitk_cap() {
+  static const int cap = [] {
     const char* e = getenv("TTB_GEMM_SPLITK");
-    return !(e && e[0] == '0');
+    if (!e || !e[0]) return kMaxSplit;
+    const int v = atoi(e);
+    return v <= 1 ? 1 : (v > kMaxSplit ? kMaxSplit : v);
   }();
-  return on;
+  return cap;
+}
+
+// Clusters of `split` CTAs of the split-K kernel that can be resident on the device at once (cached per device and size).
+template <int KIND, typename OutT, int VAR>
+int max_resident_clusters(ttb_ctx* ctx, int split) {
+  using C = Cfg<32, false, true>;
+  static int cached[64][kMaxSplit + 1] = {};
+  const int dev = ctx->device < 64 ? ctx->device : 63;
+  if (ctx->device < 64 && cached[dev][split] != 0) return cached[dev][split] > 0 ? cached[dev][split] : 0;
+  auto kern = gemm_tc_kernel<32, KIND, OutT, false, true, VAR>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  cudaLaunchConfig_t probe = {};
+  probe.gridDim = dim3((unsigned)(split * ctx->sm_count));
+  probe.blockDim = dim3(kThreads);
+  probe.dynamicSmemBytes = C::SMEM_BYTES;
+  cudaLaunchAttribute pa[1];
+  pa[0].id = cudaLaunchAttributeClusterDimension;
+  pa[0].val.clusterDim.x = (unsigned)split;
+  pa[0].val.clusterDim.y = 1;
+  pa[0].val.clusterDim.z = 1;
+  probe.attrs = pa;
+  probe.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &probe) != cudaSuccess) {
+    cudaGetLastError();
+    n = 0;
+  }
+  if (ctx->device < 64) cached[dev][split] = n > 0 ? n : -1;
+  return n;
 }
 
 template <int KIND, typename OutT, int VAR = VAR_PLAIN>
@@ -785,10 +830,15 @@ int pick_tile(ttb_ctx* ctx, const Operands& op, GemmParams& p) {
   // of a cluster so that the weights stream through (nearly) all SMs instead of a few.
   const int64_t t32 = tiles(32);
   const int64_t total_kb = (((int64_t)p.K * IN_BYTES + BK_BYTES - 1) / BK_BYTES) * p.npass;
-  if (splitk_enabled() && t32 * 2 <= ctx->sm_count && total_kb >= 4) {
+  // Measured at M = 128 in a replayed graph: K = 3072 (48 k-blocks) 15.6 us in one CTA per tile, 9.0 us split four ways;
+  // K = 768 (12 k-blocks) 6.1 us unsplit and no faster split (the launch, the pipeline fill and the epilogue are what is left).
+  if (splitk_cap() > 1 && t32 * 2 <= ctx->sm_count && total_kb >= 24) {
     int64_t s = ctx->sm_count / t32;
-    if (s > kMaxSplit) s = kMaxSplit;
+    if (s > splitk_cap()) s = splitk_cap();
     if (s > total_kb / 2) s = total_kb / 2;  // at least two k-blocks per CTA
+    // all clusters must be resident at once (one wave): how many clusters of s CTAs the device holds depends on how
+    // they pack into its GPCs
+    while (s >= 2 && t32 > max_resident_clusters<KIND, OutT, VAR>(ctx, (int)s)) --s;
     if (s >= 2) {
       p.split_k = (int)s;
       return launch_tc<32, KIND, OutT, false, true, VAR>(ctx, op, p);

@@ -42,6 +42,39 @@ def timed_burst(fns, warmup, iters):
     return sum(ts) / len(ts), ts[len(ts) // 2], ts[0]
 
 
+def timed_graph(ctx, fns, warmup, iters):
+    """Mean device time of one launch with the host out of the picture: the launches of `fns` (different buffer sets) are
+    recorded once into a CUDA graph and the graph is replayed. What is left is the kernel and the gap to its neighbour,
+    as inside a replayed forward pass."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        ctx.set_stream(side.cuda_stream)
+        for _ in range(max(1, warmup)):
+            for f in fns:
+                f()
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for f in fns:
+                f()
+    torch.cuda.current_stream().wait_stream(side)
+    ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        graph.replay()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e) / len(fns))
+    ts.sort()
+    return sum(ts) / len(ts), ts[len(ts) // 2], ts[0]
+
+
 def timed(fn, warmup, iters, flush=True):
     buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
     for _ in range(warmup):
@@ -75,6 +108,7 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--burst", type=int, default=0, help="linear/attention: time this many back-to-back launches on rotating buffer sets")
+    ap.add_argument("--graph", action="store_true", help="with --burst: replay the launches from a CUDA graph (no host time in the number)")
     ap.add_argument("--b-trans", action="store_true", help="matmul: B is stored [N, K]")
     ap.add_argument("--yardstick", action="store_true", help="matmul: also time torch.matmul (cuBLAS SGEMM, TF32 off) on the same operands")
     ap.add_argument("--pad-rows", action="store_true", help="linear: output rows padded to a multiple of 8 elements, padding declared scratch")
@@ -108,7 +142,8 @@ def main():
                 if a.dtype == "i8":
                     return lambda: ctx.call("linear_int8", ocode, xx, xs, w, ws, b, r, N, M, N, K, EPI[a.epilogue], oo, N)
                 return lambda: ctx.call("linear", ocode, xx, K, w, b, r, N if r is not None else 0, M, N, K, EPI[a.epilogue] | flag, oo, ldo)
-            mean, med, best = timed_burst([make() for _ in range(a.burst)], a.warmup, a.iters)
+            fns = [make() for _ in range(a.burst)]
+            mean, med, best = timed_graph(ctx, fns, a.warmup, a.iters) if a.graph else timed_burst(fns, a.warmup, a.iters)
         else:
             mean, med, best = timed(fn, a.warmup, a.iters, not a.no_flush)
         out.update(shape=[M, N, K], dtype=a.dtype, epilogue=a.epilogue, us=round(mean * 1e3, 2), us_median=round(med * 1e3, 2),
@@ -141,7 +176,8 @@ def main():
             def make():
                 qq, oo = torch.randn_like(qkv), torch.empty_like(o)
                 return lambda: ctx.call("attention_fwd", code, qq, T, cu, len(lens), max(lens), a.heads, 64, None, 0, 0, int(a.causal), 0.125, oo)
-            mean, med, best = timed_burst([make() for _ in range(a.burst)], a.warmup, a.iters)
+            fns = [make() for _ in range(a.burst)]
+            mean, med, best = timed_graph(ctx, fns, a.warmup, a.iters) if a.graph else timed_burst(fns, a.warmup, a.iters)
         else:
             mean, med, best = timed(fn, a.warmup, a.iters, not a.no_flush)
         fl = sum((2.0 * H * L * (L + 1)) if a.causal else (4.0 * H * L * L) for L in lens)
