@@ -270,9 +270,16 @@ int ttb_linear_int8_dynamic_noalloc(ttb_ctx* ctx, int dtype, const void* x, cons
                                     const void* bias, const void* residual, int64_t ldr, int64_t M, int64_t N,
                                     int64_t K, int epilogue, void* out, int64_t ldo);
 
-/* Per-row dynamic symmetric int8 quantisation: scale[m] = max|x[m,:]|/127, xq = rint(x/scale). */
+/* Per-row dynamic symmetric int8 quantisation: scale[m] = max|x[m,:]|/127, xq = clamp(rint(x * (1/scale)), -127, 127)
+ * with the reciprocal rounded to fp32. */
 int ttb_quantize_rows_int8(ttb_ctx* ctx, int dtype, const void* x, int64_t M, int64_t K, int8_t* xq,
                            float* row_scale);
+
+/* ttb_layernorm followed by ttb_quantize_rows_int8 of its output, in one pass: out (16-bit, may be `in`) is the layer
+ * norm, xq / row_scale its per-row int8 form. For int8 models, whose Linears take the normalised activations as int8 and
+ * whose residual path takes them in 16 bits (no reference counterpart: the reference quantises inside torch). */
+int ttb_layernorm_quant_int8(ttb_ctx* ctx, int dtype, const void* in, void* out, int8_t* xq, float* row_scale, const void* gamma,
+                             const void* beta, int64_t M, int64_t N, float eps);
 
 /* Self-attention over packed tokens, replacing BatchMatMul + ApplyMaskAndSoftmax + BatchMatMul +
  * TransposeForScore and all *Pad kernels (multi_headed_attention.cpp:320-354,

@@ -386,11 +386,14 @@ def q_quantize_weight(w):
 
 
 def q_quantize_rows(x):
-    """Per-row dynamic symmetric int8 for activations: scale_r = max|x_r|/127 (1.0 for an all-zero row)."""
+    """Per-row dynamic symmetric int8 for activations: scale_r = max|x_r|/127 (1.0 for an all-zero row),
+    q = clip(rint(x * (1 / scale_r))) with the reciprocal rounded to fp32 first (multiplying by the inverse scale is how
+    quantisers are usually written, torch's among them)."""
     x = x.astype(F32)
     amax = np.abs(x).max(-1, keepdims=True)
     scale = np.where(amax > 0, amax / F32(127.0), F32(1.0)).astype(F32)
-    q = np.clip(np.rint(x / scale), -127, 127).astype(np.int8)
+    inv = (F32(1.0) / scale).astype(F32)
+    q = np.clip(np.rint((x * inv).astype(F32)), -127, 127).astype(np.int8)
     return q, scale
 
 

@@ -107,3 +107,44 @@ def test_context_attention_per_query_mask_and_error_cases():
     x = torch.randn(2, 4, 128, device=DEV)
     with pytest.raises(Exception, match="separate q, k, v"):
         bert_att(x, x, x, attn_type="context")
+
+
+@pytest.mark.parametrize("dt", ["f32", "f16"])
+@pytest.mark.parametrize("flags", [(False, False, False), (True, False, True), (False, True, False)])
+def test_smart_batch_context_attention_with_query_and_key_length_lists(dt, flags):
+    """MultiHeadedAttentionSmartBatch with attn_type="context" (multi_headed_attention_smart_batch.cpp:34-170): packed queries
+    of lengths [9, 7, 13] against packed keys / values of lengths [10, 19, 20], the lists of the reference's own test
+    (python/tests/multi_head_attn_smart_batch_test.py:155-165). As there, the expected result is every sequence run alone
+    through the fixed-length attention (here its restatement, pinned to the compiled reference), concatenated."""
+    pre, post, add = flags
+    H, heads = 768, 12
+    q_lens, k_lens = [9, 7, 13], [10, 19, 20]
+    w = {k: rounded(v, dt) for k, v in ref_driver.context_attention_weights(H, 21).items()}
+    r = np.random.default_rng(22)
+    qs = [rounded(r.random((1, n, H)).astype(np.float32), dt) for n in q_lens]
+    ks = [rounded(r.random((1, n, H)).astype(np.float32), dt) for n in k_lens]
+    vs = [rounded(r.random((1, n, H)).astype(np.float32), dt) for n in k_lens]
+    want = np.concatenate([restate.context_attention(q, k, v, None, w, heads, None, pre, post, add)[0] for q, k, v in zip(qs, ks, vs)], 1)
+    mod = OnmtStyleAttention(w, heads).to(DEV).to(TORCH_DT[dt])
+    ln = torch.nn.LayerNorm(H)
+    ln.weight.copy_(torch.from_numpy(w["ln_gamma"]))
+    ln.bias.copy_(torch.from_numpy(w["ln_beta"]))
+    att = tt.MultiHeadedAttentionSmartBatch.from_onmt(mod, ln.to(DEV).to(TORCH_DT[dt]))
+    Q, K, V = (on_dev(np.concatenate(x, 1), dt) for x in (qs, ks, vs))
+    kw = dict(attn_type="context", pre_layernorm=pre, post_layernorm=post, post_add_input=add)
+    out, prob = att(K, V, Q, q_lens, k_lens, mask=None, **kw)
+    assert tuple(out.shape) == (1, sum(q_lens), H)
+    assert diff(out, want) < TOL[dt]
+    prob = torch.utils.dlpack.from_dlpack(prob.to_dlpack())
+    assert tuple(prob.shape) == (3, heads, max(q_lens), max(k_lens))
+    assert float(prob[0, :, :9, 10:].float().abs().max()) == 0.0   # keys beyond a sequence's own length get no weight
+    # the projected memory can be kept and used again, as in the fixed-length class
+    cache = {"memory_keys": None, "memory_values": None}
+    out1, _ = att(K, V, Q, q_lens, k_lens, layer_cache=cache, **kw)
+    assert diff(out1, want) < TOL[dt] and tuple(cache["memory_keys"].shape) == (3, heads, max(k_lens), H // heads)
+    junk = torch.zeros_like(K)
+    out2, _ = att(junk, junk, Q, q_lens, k_lens, layer_cache=cache, **kw)
+    assert diff(out2, want) < TOL[dt]
+    with pytest.raises(Exception, match="batch size"):
+        att(K, V, Q, q_lens, k_lens[:2], **kw)
+    assert tt._cxx_module.device_status(0) == 0

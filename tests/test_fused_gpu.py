@@ -343,3 +343,26 @@ def test_attention_edge_batches(ctx, kernel, case, monkeypatch):
     got = host(out)
     assert np.isfinite(got).all()
     assert maxdiff(got, want) < 4e-3
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("M,N", [(300, 768), (1, 768), (4097, 1024), (50, 256), (33, 3072), (7, 100)])
+def test_layernorm_with_int8_output_equals_the_two_kernels_in_sequence(ctx, dt, M, N):
+    r = rng(M + N)
+    x = dev(r.standard_normal((M, N)).astype(np.float32) * 2.0 + 0.5, dt)
+    g = dev(1.0 + 0.1 * r.standard_normal(N).astype(np.float32), dt)
+    b = dev(0.1 * r.standard_normal(N).astype(np.float32), dt)
+    want = torch.empty_like(x)
+    ctx.call("layernorm", code(dt), x, want, g, b, M, N, 1e-12)
+    want_q = torch.empty((M, N), dtype=torch.int8, device="cuda")
+    want_s = torch.empty(M, dtype=torch.float32, device="cuda")
+    ctx.call("quantize_rows_int8", code(dt), want, M, N, want_q, want_s)
+    out = x.clone()
+    q = torch.full((M, N), 99, dtype=torch.int8, device="cuda")
+    s = torch.full((M,), -1.0, dtype=torch.float32, device="cuda")
+    ctx.call("layernorm_quant_int8", code(dt), out, out, q, s, g, b, M, N, 1e-12)   # in place
+    assert ctx.device_status() == _capi.OK
+    assert torch.equal(out, want) and torch.equal(q, want_q) and torch.equal(s, want_s)
+    # and the quantiser against the numpy statement of the scheme
+    xq, xs = restate.q_quantize_rows(host(want))
+    assert (want_q.cpu().numpy() == xq).all() and maxdiff(host(want_s), xs.reshape(-1)) == 0.0

@@ -156,6 +156,8 @@ class Tensor {
   //   f32 : same shape in fp32, the unrounded value (the residual stream of a bf16 model)
   const Tensor* lo() const;
   const Tensor* f32() const;
+  const Tensor* q8() const;
+  const Tensor* q8_scale() const;
   TensorExtras& NewExtras();
   void DropExtras() { extras_.reset(); }
 
@@ -172,9 +174,15 @@ class Tensor {
 struct TensorExtras {
   Tensor lo{nullptr};
   Tensor f32{nullptr};
+  // int8 models: the per-row symmetric int8 form of this activation and its row scales, written by the layer norm that
+  // produced it so that the next int8 Linear does not quantise it again
+  Tensor q8{nullptr};
+  Tensor q8_scale{nullptr};
 };
 inline const Tensor* Tensor::lo() const { return extras_ && !extras_->lo.is_null() ? &extras_->lo : nullptr; }
 inline const Tensor* Tensor::f32() const { return extras_ && !extras_->f32.is_null() ? &extras_->f32 : nullptr; }
+inline const Tensor* Tensor::q8() const { return extras_ && !extras_->q8.is_null() ? &extras_->q8 : nullptr; }
+inline const Tensor* Tensor::q8_scale() const { return extras_ && !extras_->q8_scale.is_null() ? &extras_->q8_scale : nullptr; }
 inline TensorExtras& Tensor::NewExtras() {
   extras_ = std::make_shared<TensorExtras>();
   return *extras_;

@@ -55,6 +55,17 @@ void LayerNormPlanes(ttb_ctx* c, bool in_f32, const void* in, Tensor* out, const
   Check(ttb_layernorm_planes(c, in_f32 ? TTB_F32 : dt, dt, in, out_ptr, lo, f32, gamma.raw(), beta.raw(), M, N, eps), c, name);
 }
 
+// In-place layer norm of a 16-bit tensor that an int8 (per-row scheme) Linear produced: the int8 form of the result is
+// written along and attached, because the next Linear of an int8 model will want it.
+void LayerNormWithInt8(ttb_ctx* c, Tensor* t, const Tensor& gamma, const Tensor& beta, int64_t M, int64_t N, float eps, const char* name) {
+  const int dt = core::ToTTBDtype(t->dtype());
+  void* ptr = t->raw_mut();
+  core::TensorExtras& ex = t->NewExtras();
+  int8_t* q = static_cast<int8_t*>(ex.q8.Reshape(core::kInt8, {M, N}, kDLCUDA, t->device_id(), "linear/int8_activations"));
+  float* s = ex.q8_scale.Reshape<float>({M}, kDLCUDA, t->device_id(), "linear/int8_row_scales");
+  Check(ttb_layernorm_quant_int8(c, dt, ptr, ptr, q, s, gamma.raw(), beta.raw(), M, N, eps), c, name);
+}
+
 // dst (16-bit, [M, N]) = src (fp32): the re-layout kernel with an already K-major source is a plain conversion.
 void CastFromF32(ttb_ctx* c, const float* src, int dst_dt, void* dst, int64_t M, int64_t N, const char* name) {
   Check(ttb_prepack_weight(c, TTB_F32, src, 1, N, M, dst_dt, dst), c, name);
@@ -203,6 +214,11 @@ void PackedLinear::Forward(const Tensor& x, int64_t M, int epilogue, const void*
     const int8_t* wq;
     const float* ws;
     Int8(is_trans, &wq, &ws);
+    if (x.q8() && x.q8_scale() && x.q8()->numel() == M * K) {  // the producer already quantised this activation
+      Check(ttb_linear_int8(c, dt, x.q8()->data<int8_t>(), x.q8_scale()->data<float>(), wq, ws, bias, residual, N, M, N, K, epilogue, out, N), c,
+            name);
+      return;
+    }
     Tensor xq(nullptr), xs(nullptr);
     xq.Reshape(core::kInt8, {M, K}, kDLCUDA, x.device_id(), "linear/int8_activations");
     xs.Reshape(core::kFloat32, {M}, kDLCUDA, x.device_id(), "linear/int8_row_scales");
@@ -388,15 +404,26 @@ void MultiHeadedAttentionSmartBatch::operator()(const Tensor& key_tensor, const 
                                                 bool post_layernorm, bool post_add_input, bool is_trans_weight) const {
   TT_ENFORCE_EQ(query_tensor.n_dim(), 3, "The query_tensors should be a matrix with shape [1, sum_query_seq_len, hidden_size].");
   TT_ENFORCE_EQ(query_tensor.shape(0), 1, "The packed query tensor's first dimension must be 1.");
-  if (attn_type != "self") {
-    if (attn_type == "context") TT_THROW("context (encoder-decoder) attention is outside the scope of this runtime");
-    TT_THROW("attn_type should be context or self.");
-  }
-  for (auto& kv : layer_cache)
-    if (kv.second && !kv.second->is_null()) TT_THROW("incremental decoding caches (layer_cache) are outside the scope of this runtime");
   TT_ENFORCE(!query_seq_len_list.empty(), "query_seq_len_list is empty");
   const int64_t total = std::accumulate(query_seq_len_list.begin(), query_seq_len_list.end(), (int64_t)0);
   TT_ENFORCE_EQ(query_tensor.shape(1), total, "The query_tensor shape 1 should be the sum of seq_len_list.");
+  if (attn_type == "context") {
+    // multi_headed_attention_smart_batch.cpp:34-170: queries of one set of lengths against keys / values of another
+    TT_ENFORCE_EQ(key_seq_len_list.size(), query_seq_len_list.size(), "query_seq_len_list and key_seq_len_list differ in batch size");
+    Tensor *mem_k = nullptr, *mem_v = nullptr;
+    for (auto& kv : layer_cache) {
+      if (kv.first == "memory_keys") mem_k = kv.second;
+      else if (kv.first == "memory_values") mem_v = kv.second;
+    }
+    TT_ENFORCE((mem_k == nullptr) == (mem_v == nullptr), "layer_cache needs both memory_keys and memory_values");
+    RunContext(key_tensor, value_tensor, query_tensor, attention_mask, output, att_score, mem_k, mem_v, pre_layernorm, post_layernorm,
+               post_add_input, is_trans_weight, &query_seq_len_list, &key_seq_len_list);
+    return;
+  }
+  if (attn_type != "self") TT_THROW("attn_type should be context or self.");
+  for (auto& kv : layer_cache)
+    if (kv.second && !kv.second->is_null())
+      TT_THROW("the packed self-attention takes no key/value cache (decode with the fixed-length MultiHeadedAttention)");
   Run(query_tensor, attention_mask, &query_seq_len_list, output, att_score, pre_layernorm, post_layernorm, post_add_input,
       is_trans_weight);
 }
@@ -575,15 +602,20 @@ void MultiHeadedAttention::Finish(const Tensor& context, const Tensor& x, int64_
           c, "AddBiasLayerNorm");
   } else {
     dense_.Forward(context, T, TTB_EPI_BIAS_RESIDUAL, x.raw(), output->raw_mut(), is_trans_weight, "gemm5");
-    Check(ttb_layernorm(c, dt, output->raw(), output->raw_mut(), layernorm_gamma_.raw(), layernorm_beta_.raw(), T, H, 1e-12f), c,
-          "AddBiasLayerNorm");
+    if (dense_.int8_mode() == PackedLinear::kInt8PerRow) {
+      LayerNormWithInt8(c, output, layernorm_gamma_, layernorm_beta_, T, H, 1e-12f, "AddBiasLayerNorm");
+    } else {
+      Check(ttb_layernorm(c, dt, output->raw(), output->raw_mut(), layernorm_gamma_.raw(), layernorm_beta_.raw(), T, H, 1e-12f), c,
+            "AddBiasLayerNorm");
+    }
   }
 }
 
 void MultiHeadedAttention::RunContext(const Tensor& key_tensor, const Tensor& value_tensor, const Tensor& query_tensor,
                                       const Tensor& attention_mask, Tensor* output, Tensor* att_score, Tensor* memory_keys,
                                       Tensor* memory_values, bool pre_layernorm, bool post_layernorm, bool post_add_input,
-                                      bool is_trans_weight) const {
+                                      bool is_trans_weight, const std::vector<int64_t>* q_lens,
+                                      const std::vector<int64_t>* k_lens) const {
   // The reference's sequence (multi_headed_attention.cpp:45-167, 308-354) on this library's kernels: three separate
   // projections, AddBiasTransposeForScore into [B, heads, L, d], scores materialised, mask + softmax, weighted values,
   // transpose back, output projection. The encoder memory's keys / values are projected once per sequence when the caller
@@ -596,7 +628,15 @@ void MultiHeadedAttention::RunContext(const Tensor& key_tensor, const Tensor& va
   SameTypeDevice(x, q_.weight(), "attention");
   const int dev = x.device_id();
   ttb_ctx* c = DeviceContext(dev);
-  const int64_t B = x.shape(0), Lq = x.shape(1), H = x.shape(2), heads = num_attention_heads_, d = H / heads, T = B * Lq;
+  const bool packed = q_lens != nullptr;
+  TT_ENFORCE(packed == (k_lens != nullptr), "packed context attention needs both length lists");
+  const int64_t H = x.shape(2), heads = num_attention_heads_, d = H / heads;
+  const int64_t B = packed ? (int64_t)q_lens->size() : x.shape(0);
+  const int64_t Lq = packed ? *std::max_element(q_lens->begin(), q_lens->end()) : x.shape(1);  // padded query length
+  const int64_t T = x.rows();
+  // prefix sums of the packed rows (null handles = equal lengths, rows b * L + l)
+  const core::CuSeqlensHandle cu_q = packed ? core::CuSeqlens(dev, *q_lens) : core::CuSeqlensHandle();
+  const core::CuSeqlensHandle cu_k = packed ? core::CuSeqlens(dev, *k_lens) : core::CuSeqlensHandle();
   TT_ENFORCE_EQ(d * heads, H, "hidden size %lld is not divisible by %lld heads", (long long)H, (long long)heads);
   TT_ENFORCE_EQ(q_.out_dim(is_trans_weight), H, "q weight does not map hidden -> hidden");
   if (pre_layernorm || post_layernorm) TT_ENFORCE(!layernorm_gamma_.is_null(), "this attention layer was built without layer norm weights");
@@ -614,7 +654,7 @@ void MultiHeadedAttention::RunContext(const Tensor& key_tensor, const Tensor& va
   lin.Reshape(x.dtype(), {T, H}, kDLCUDA, dev, "context/gemm0/q_out1/Reshape");
   q_.Forward(*q_in, T, TTB_EPI_NONE, nullptr, lin.raw_mut(), is_trans_weight, "context/gemm0");
   q.Reshape(x.dtype(), {B, heads, Lq, d}, kDLCUDA, dev, "context/AddBiasTransposeForScore/q_out2/Reshape");
-  Check(ttb_add_bias_transpose_for_score(c, dt, lin.raw(), q_.bias().raw(), B, Lq, heads, d, q.raw_mut()), c,
+  Check(ttb_add_bias_transpose_for_score_pad(c, dt, lin.raw(), q_.bias().raw(), cu_q.get(), B, Lq, heads, d, q.raw_mut()), c,
         "context/AddBiasTransposeForScore");
 
   // 2) keys / values: from the cache when it is filled, otherwise projected (and filed when a cache entry was passed)
@@ -630,24 +670,32 @@ void MultiHeadedAttention::RunContext(const Tensor& key_tensor, const Tensor& va
                    core::SameType(v->dtype(), x.dtype()),
                "layer_cache memory_values does not match memory_keys");
   } else {
-    TT_ENFORCE_EQ(key_tensor.shape(0), B, "key_tensor and query_tensor disagree on the batch size");
-    TT_ENFORCE(key_tensor.shape(1) == value_tensor.shape(1) && key_tensor.shape(2) == H && value_tensor.shape(2) == H &&
-                   value_tensor.shape(0) == B,
-               "key_tensor and value_tensor must both be [batch, key_len, hidden]");
+    if (packed) {
+      const int64_t sum_k = std::accumulate(k_lens->begin(), k_lens->end(), (int64_t)0);
+      TT_ENFORCE(key_tensor.shape(0) == 1 && key_tensor.shape(1) == sum_k, "The key_tensor shape 1 should be the sum of seq_len_list.");
+      TT_ENFORCE(value_tensor.shape(0) == 1 && value_tensor.shape(1) == sum_k, "The value_tensor shape 1 should be the sum of seq_len_list.");
+      TT_ENFORCE(key_tensor.shape(2) == H && value_tensor.shape(2) == H, "key_tensor and value_tensor must be [1, sum_key_len, hidden]");
+    } else {
+      TT_ENFORCE_EQ(key_tensor.shape(0), B, "key_tensor and query_tensor disagree on the batch size");
+      TT_ENFORCE(key_tensor.shape(1) == value_tensor.shape(1) && key_tensor.shape(2) == H && value_tensor.shape(2) == H &&
+                     value_tensor.shape(0) == B,
+                 "key_tensor and value_tensor must both be [batch, key_len, hidden]");
+    }
     SameTypeDevice(key_tensor, k_.weight(), "attention");
     SameTypeDevice(value_tensor, v_.weight(), "attention");
-    const int64_t Lk = key_tensor.shape(1);
+    const int64_t Lk = packed ? *std::max_element(k_lens->begin(), k_lens->end()) : key_tensor.shape(1);  // padded key length
+    const int64_t Tk = key_tensor.rows();
     if (memory_keys) { k = memory_keys; v = memory_values; }
     Tensor k_lin(nullptr), v_lin(nullptr);
-    k_lin.Reshape(x.dtype(), {B * Lk, H}, kDLCUDA, dev, "context/gemm2/k_out1/Reshape");
-    v_lin.Reshape(x.dtype(), {B * Lk, H}, kDLCUDA, dev, "context/gemm1/v_out1/Reshape");
-    k_.Forward(key_tensor, B * Lk, TTB_EPI_NONE, nullptr, k_lin.raw_mut(), is_trans_weight, "context/gemm1");
-    v_.Forward(value_tensor, B * Lk, TTB_EPI_NONE, nullptr, v_lin.raw_mut(), is_trans_weight, "context/gemm2");
+    k_lin.Reshape(x.dtype(), {Tk, H}, kDLCUDA, dev, "context/gemm2/k_out1/Reshape");
+    v_lin.Reshape(x.dtype(), {Tk, H}, kDLCUDA, dev, "context/gemm1/v_out1/Reshape");
+    k_.Forward(key_tensor, Tk, TTB_EPI_NONE, nullptr, k_lin.raw_mut(), is_trans_weight, "context/gemm1");
+    v_.Forward(value_tensor, Tk, TTB_EPI_NONE, nullptr, v_lin.raw_mut(), is_trans_weight, "context/gemm2");
     k->Reshape(x.dtype(), {B, heads, Lk, d}, kDLCUDA, dev, "context/keys/AddBiasTransposeForScore/Reshape");
     v->Reshape(x.dtype(), {B, heads, Lk, d}, kDLCUDA, dev, "context/values/AddBiasTransposeForScore/Reshape");
-    Check(ttb_add_bias_transpose_for_score(c, dt, k_lin.raw(), k_.bias().raw(), B, Lk, heads, d, k->raw_mut()), c,
+    Check(ttb_add_bias_transpose_for_score_pad(c, dt, k_lin.raw(), k_.bias().raw(), cu_k.get(), B, Lk, heads, d, k->raw_mut()), c,
           "context/keys/AddBiasTransposeForScore");
-    Check(ttb_add_bias_transpose_for_score(c, dt, v_lin.raw(), v_.bias().raw(), B, Lk, heads, d, v->raw_mut()), c,
+    Check(ttb_add_bias_transpose_for_score_pad(c, dt, v_lin.raw(), v_.bias().raw(), cu_k.get(), B, Lk, heads, d, v->raw_mut()), c,
           "context/values/AddBiasTransposeForScore");
   }
   const int64_t Lk = k->shape(2);
@@ -659,6 +707,17 @@ void MultiHeadedAttention::RunContext(const Tensor& key_tensor, const Tensor& va
   Check(ttb_batch_matmul(c, dt, q.raw(), 0, k->raw(), 1, B * heads, Lq, Lk, d, scale, 0.0f, scores->raw_mut()), c, "batch_gemm3");
   const float* mask = nullptr;
   int is2d = 1;
+  Tensor pad_mask(nullptr);
+  if (attention_mask.is_null() && packed) {
+    // no mask tensor: keys beyond each sequence's own length are padding; the [B, 1, maxLk] additive mask the reference's
+    // Python layer builds for this case (modeling_smart_pad.py:95-110)
+    std::vector<float> host_mask((size_t)(B * Lk), 0.f);
+    for (int64_t b = 0; b < B; ++b)
+      for (int64_t l = (*k_lens)[b]; l < Lk; ++l) host_mask[b * Lk + l] = -1e9f;
+    float* dm = pad_mask.Reshape<float>({B, 1, Lk}, kDLCUDA, dev, "context/pad_mask");
+    Check(ttb_memcpy_h2d(c, dm, host_mask.data(), host_mask.size() * sizeof(float)), c, "context/pad_mask");
+    mask = dm;
+  }
   if (!attention_mask.is_null()) {
     TT_ENFORCE(attention_mask.on_gpu() && core::SameType(attention_mask.dtype(), core::kFloat32),
                "the attention mask must be an fp32 tensor on the GPU");
@@ -671,7 +730,7 @@ void MultiHeadedAttention::RunContext(const Tensor& key_tensor, const Tensor& va
   ctx_heads.Reshape(x.dtype(), {B, heads, Lq, d}, kDLCUDA, dev, "ApplyMaskAndSoftmax/Reshape");
   Check(ttb_batch_matmul(c, dt, scores->raw(), 0, v->raw(), 0, B * heads, Lq, d, Lk, 1.0f, 0.0f, ctx_heads.raw_mut()), c, "batch_gemm4");
   context.Reshape(x.dtype(), {T, H}, kDLCUDA, dev, "batch_gemm4/Reshape");
-  Check(ttb_transpose_for_score(c, dt, ctx_heads.raw(), B, heads, Lq, d, context.raw_mut()), c, "TransposeForScore");
+  Check(ttb_transpose_for_score_pad(c, dt, ctx_heads.raw(), cu_q.get(), B, Lq, heads, d, context.raw_mut()), c, "TransposeForScore");
 
   Finish(context, x, T, output, post_layernorm, post_add_input, is_trans_weight);
 }
@@ -725,9 +784,13 @@ void BertOutput::operator()(const Tensor& hidden_states, const Tensor& input_ten
     LayerNormPlanes(c, true, s, output_tensor, layer_norm_weight_, layer_norm_bias_, M, N, 1e-12f, true, "BertOutput/AddBiasLayerNorm");
   } else {
     dense_.Forward(hidden_states, M, TTB_EPI_BIAS_RESIDUAL, input_tensor.raw(), output_tensor->raw_mut(), false, "BertOutput/MatMul");
-    Check(ttb_layernorm(c, dt, output_tensor->raw(), output_tensor->raw_mut(), layer_norm_weight_.raw(), layer_norm_bias_.raw(), M, N,
-                        1e-12f),
-          c, "BertOutput/AddBiasLayerNorm");
+    if (dense_.int8_mode() == PackedLinear::kInt8PerRow) {
+      LayerNormWithInt8(c, output_tensor, layer_norm_weight_, layer_norm_bias_, M, N, 1e-12f, "BertOutput/AddBiasLayerNorm");
+    } else {
+      Check(ttb_layernorm(c, dt, output_tensor->raw(), output_tensor->raw_mut(), layer_norm_weight_.raw(), layer_norm_bias_.raw(), M, N,
+                          1e-12f),
+            c, "BertOutput/AddBiasLayerNorm");
+    }
   }
 }
 

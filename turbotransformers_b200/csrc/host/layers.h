@@ -45,6 +45,7 @@ class PackedLinear {
   void set_int8(bool on) { int8_mode_ = on ? kInt8PerRow : kInt8Off; }
   void set_int8_mode(int mode) { int8_mode_ = mode; }
   bool use_int8() const { return int8_mode_ != kInt8Off; }
+  int int8_mode() const { return int8_mode_; }
 
   // out[M,N] = epilogue(x[M,K] . W + bias); picks the kernel by dtype / int8 mode.
   // `ldo` (elements between output rows) defaults to N. A bf16 x that carries a lo plane is used at full precision
@@ -125,14 +126,17 @@ class MultiHeadedAttention {
   void QuantizeInt8() { qkv_.set_int8(true); dense_.set_int8(true); }
   int64_t num_attention_heads() const { return num_attention_heads_; }
 
- private:
+ protected:
   // attn_type == "context" (encoder-decoder attention, multi_headed_attention.cpp:45-167 of the reference): queries from
   // query_tensor [B, Lq, H], keys / values from key_tensor / value_tensor [B, Lk, H] or, once computed, from
   // layer_cache["memory_keys" / "memory_values"] ([B, heads, Lk, d], the reference's layout).
+  // q_lens / k_lens (both or neither): the packed form of MultiHeadedAttentionSmartBatch, query_tensor [1, sum(q_lens), H]
+  // and key_tensor / value_tensor [1, sum(k_lens), H] (multi_headed_attention_smart_batch.cpp:34-170).
   void RunContext(const core::Tensor& key_tensor, const core::Tensor& value_tensor, const core::Tensor& query_tensor,
                   const core::Tensor& attention_mask, core::Tensor* output, core::Tensor* att_score, core::Tensor* memory_keys,
                   core::Tensor* memory_values, bool pre_layernorm, bool post_layernorm, bool post_add_input,
-                  bool is_trans_weight) const;
+                  bool is_trans_weight, const std::vector<int64_t>* q_lens = nullptr,
+                  const std::vector<int64_t>* k_lens = nullptr) const;
   // Output projection of the token-major attention result [T, H] and what follows it (residual, layer norm).
   void Finish(const core::Tensor& context, const core::Tensor& x, int64_t T, core::Tensor* output, bool post_layernorm,
               bool post_add_input, bool is_trans_weight) const;

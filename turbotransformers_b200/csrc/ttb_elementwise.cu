@@ -587,11 +587,181 @@ quantize_rows_kernel(const T* __restrict__ x, int64_t M, int K, int8_t* __restri
     for (int c = lane; c < K; c += 32) amax = fmaxf(amax, fabsf(to_f(xr[c])));
     amax = warp_max(amax);
     const float sc = amax > 0.f ? amax / 127.0f : 1.0f;
+    const float inv = __frcp_rn(sc);
     if (lane == 0) scale[row] = sc;
     for (int c = lane; c < K; c += 32) {
-      float q = rintf(to_f(xr[c]) / sc);
+      float q = rintf(__fmul_rn(to_f(xr[c]), inv));
       q = fminf(fmaxf(q, -127.f), 127.f);
       xq[row * K + c] = (int8_t)q;
+    }
+  }
+}
+
+// The same for 16-bit rows of up to 3072 elements (K % 8 == 0): the row is loaded once with 16-byte accesses and kept
+// packed in registers, two rows per warp in flight, and the int8 row leaves as 8-byte stores.
+template <typename T, int ITERS>
+__global__ void __launch_bounds__(kLnWarps * 32)
+quantize_rows16_kernel(const T* __restrict__ x, int64_t M, int K, int8_t* __restrict__ xq, float* __restrict__ scale) {
+  pdl_trigger();
+  pdl_wait();
+  constexpr int ROWS = 2;
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_total = (int64_t)gridDim.x * kLnWarps;
+  for (int64_t row0 = ((int64_t)blockIdx.x * kLnWarps + (threadIdx.x >> 5)) * ROWS; row0 < M; row0 += warps_total * ROWS) {
+    uint4 raw[ROWS][ITERS];
+    float amax[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      amax[r] = 0.f;
+#pragma unroll
+      for (int it = 0; it < ITERS; ++it) {
+        const int col = (it * 32 + lane) * 8;
+        raw[r][it] = (row0 + r < M && col < K) ? *reinterpret_cast<const uint4*>(x + (row0 + r) * K + col) : make_uint4(0, 0, 0, 0);
+        const T* h = reinterpret_cast<const T*>(&raw[r][it]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax[r] = fmaxf(amax[r], fabsf(to_f(h[j])));
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) amax[r] = warp_max(amax[r]);
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const int64_t row = row0 + r;
+      if (row >= M) continue;
+      const float sc = amax[r] > 0.f ? amax[r] / 127.0f : 1.0f;
+      const float inv = __frcp_rn(sc);
+      if (lane == 0) scale[row] = sc;
+#pragma unroll
+      for (int it = 0; it < ITERS; ++it) {
+        const int col = (it * 32 + lane) * 8;
+        if (col < K) {
+          const T* h = reinterpret_cast<const T*>(&raw[r][it]);
+          uint32_t w[2] = {0u, 0u};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float q = fminf(fmaxf(rintf(__fmul_rn(to_f(h[j]), inv)), -127.f), 127.f);
+            w[j >> 2] |= ((uint32_t)(int)q & 0xffu) << ((j & 3) * 8);
+          }
+          *reinterpret_cast<uint2*>(xq + row * K + col) = make_uint2(w[0], w[1]);
+        }
+      }
+    }
+  }
+}
+
+// Wide 16-bit rows (K % 8 == 0): two passes over the row with 16-byte accesses (the second one hits L1 / L2), so that
+// nothing but the running maximum lives in registers and many warps fit an SM.
+template <typename T>
+__global__ void __launch_bounds__(kLnWarps * 32)
+quantize_rows16_wide_kernel(const T* __restrict__ x, int64_t M, int K, int8_t* __restrict__ xq, float* __restrict__ scale) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_total = (int64_t)gridDim.x * kLnWarps;
+  for (int64_t row = (int64_t)blockIdx.x * kLnWarps + (threadIdx.x >> 5); row < M; row += warps_total) {
+    const T* xr = x + row * K;
+    float amax = 0.f;
+    for (int col = lane * 8; col < K; col += 256) {
+      const uint4 q = *reinterpret_cast<const uint4*>(xr + col);
+      const T* h = reinterpret_cast<const T*>(&q);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(to_f(h[j])));
+    }
+    amax = warp_max(amax);
+    const float sc = amax > 0.f ? amax / 127.0f : 1.0f;
+    const float inv = __frcp_rn(sc);
+    if (lane == 0) scale[row] = sc;
+    for (int col = lane * 8; col < K; col += 256) {
+      const uint4 q = *reinterpret_cast<const uint4*>(xr + col);
+      const T* h = reinterpret_cast<const T*>(&q);
+      uint32_t w[2] = {0u, 0u};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float v = fminf(fmaxf(rintf(__fmul_rn(to_f(h[j]), inv)), -127.f), 127.f);
+        w[j >> 2] |= ((uint32_t)(int)v & 0xffu) << ((j & 3) * 8);
+      }
+      *reinterpret_cast<uint2*>(xq + row * K + col) = make_uint2(w[0], w[1]);
+    }
+  }
+}
+
+// LayerNorm of 16-bit rows that also leaves the int8 form of its output (per-row symmetric, the quantiser above applied
+// to the rounded 16-bit values, so the result is the same as running the two kernels one after the other): the input of
+// an int8 Linear is produced where it is computed instead of by another pass over the activations.
+template <typename T, int ITERS>
+__global__ void __launch_bounds__(kLnWarps * 32)
+layernorm16_quant_kernel(const T* x, const T* __restrict__ gamma, const T* __restrict__ beta, T* out, int8_t* __restrict__ xq,
+                         float* __restrict__ scale, int64_t M, int N, float eps) {
+  pdl_trigger();
+  pdl_wait();
+  constexpr int ROWS = 2;
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_total = (int64_t)gridDim.x * kLnWarps;
+  for (int64_t row0 = ((int64_t)blockIdx.x * kLnWarps + (threadIdx.x >> 5)) * ROWS; row0 < M; row0 += warps_total * ROWS) {
+    uint4 raw[ROWS][ITERS];
+    float mean[ROWS], rstd[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      float sum = 0.f, sq = 0.f;
+#pragma unroll
+      for (int it = 0; it < ITERS; ++it) {
+        const int col = (it * 32 + lane) * 8;
+        raw[r][it] = (row0 + r < M && col < N) ? *reinterpret_cast<const uint4*>(x + (row0 + r) * N + col) : make_uint4(0, 0, 0, 0);
+        const T* h = reinterpret_cast<const T*>(&raw[r][it]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { const float f = to_f(h[j]); sum += f; sq = fmaf(f, f, sq); }
+      }
+      mean[r] = sum;
+      rstd[r] = sq;
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      mean[r] = warp_sum(mean[r]) / (float)N;
+      rstd[r] = rsqrtf(fmaxf(warp_sum(rstd[r]) / (float)N - mean[r] * mean[r], 0.f) + eps);
+    }
+    // normalise in place: the packed registers now hold the rounded 16-bit output, which is also what gets quantised
+    float amax[ROWS] = {0.f, 0.f};
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int col = (it * 32 + lane) * 8;
+      if (col < N) {
+        const uint4 gq = *reinterpret_cast<const uint4*>(gamma + col), bq = *reinterpret_cast<const uint4*>(beta + col);
+        const T* g = reinterpret_cast<const T*>(&gq);
+        const T* b = reinterpret_cast<const T*>(&bq);
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+          T* h = reinterpret_cast<T*>(&raw[r][it]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            h[j] = from_f<T>(to_f(b[j]) + to_f(g[j]) * rstd[r] * (to_f(h[j]) - mean[r]));
+            amax[r] = fmaxf(amax[r], fabsf(to_f(h[j])));
+          }
+          if (row0 + r < M) *reinterpret_cast<uint4*>(out + (row0 + r) * N + col) = raw[r][it];
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const int64_t row = row0 + r;
+      const float am = warp_max(amax[r]);
+      if (row >= M) continue;
+      const float sc = am > 0.f ? am / 127.0f : 1.0f;
+      const float inv = __frcp_rn(sc);
+      if (lane == 0) scale[row] = sc;
+#pragma unroll
+      for (int it = 0; it < ITERS; ++it) {
+        const int col = (it * 32 + lane) * 8;
+        if (col < N) {
+          const T* h = reinterpret_cast<const T*>(&raw[r][it]);
+          uint32_t w[2] = {0u, 0u};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float v = fminf(fmaxf(rintf(__fmul_rn(to_f(h[j]), inv)), -127.f), 127.f);
+            w[j >> 2] |= ((uint32_t)(int)v & 0xffu) << ((j & 3) * 8);
+          }
+          *reinterpret_cast<uint2*>(xq + row * N + col) = make_uint2(w[0], w[1]);
+        }
+      }
     }
   }
 }
@@ -917,6 +1087,31 @@ extern "C" int ttb_quantize_rows_int8(ttb_ctx* ctx, int dtype, const void* x, in
   if (M == 0) return TTB_OK;
   TTB_REQUIRE(ctx, x && xq && row_scale, "quantize_rows_int8: null pointer");
   DeviceGuard g(ctx->device);
+  const bool aligned = K % 8 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(xq)) & 15) == 0;
+  if ((dtype == TTB_F16 || dtype == TTB_BF16) && aligned && K > 1024) {
+    const int gridw = grid_for(M, kLnWarps, ctx->sm_count);
+    if (dtype == TTB_F16)
+      launch_pdl(quantize_rows16_wide_kernel<__half>, dim3(gridw), dim3(kLnWarps * 32), 0, ctx->stream, (const __half*)x, M, (int)K, xq, row_scale);
+    else
+      launch_pdl(quantize_rows16_wide_kernel<__nv_bfloat16>, dim3(gridw), dim3(kLnWarps * 32), 0, ctx->stream, (const __nv_bfloat16*)x, M, (int)K, xq,
+                 row_scale);
+    return launched(ctx, "quantize_rows_int8");
+  }
+  if ((dtype == TTB_F16 || dtype == TTB_BF16) && aligned) {
+    const int grid16 = grid_for((M + 1) / 2, kLnWarps, ctx->sm_count);
+#define Q16_CASE(T, IT) launch_pdl(quantize_rows16_kernel<T, IT>, dim3(grid16), dim3(kLnWarps * 32), 0, ctx->stream, (const T*)x, M, (int)K, xq, row_scale)
+#define Q16_PICK(T)                      \
+  do {                                   \
+    if (K <= 256) Q16_CASE(T, 1);        \
+    else if (K <= 768) Q16_CASE(T, 3);   \
+    else Q16_CASE(T, 4);                 \
+  } while (0)
+    if (dtype == TTB_F16) Q16_PICK(__half);
+    else Q16_PICK(__nv_bfloat16);
+#undef Q16_PICK
+#undef Q16_CASE
+    return launched(ctx, "quantize_rows_int8");
+  }
   const int grid = grid_for(M, kRowsPerBlock, ctx->sm_count);
   TTB_DISPATCH_FLOAT(ctx, dtype, T,
                      (quantize_rows_kernel<T><<<grid, kRowsPerBlock * 32, 0, ctx->stream>>>((const T*)x, M, (int)K, xq, row_scale)));
@@ -964,6 +1159,39 @@ __global__ void cu_seqlens_from_params_kernel(const LensParam lens, int B, int32
   }
 }
 }  // namespace
+
+extern "C" int ttb_layernorm_quant_int8(ttb_ctx* ctx, int dtype, const void* in, void* out, int8_t* xq, float* row_scale, const void* gamma,
+                                        const void* beta, int64_t M, int64_t N, float eps) {
+  if (!ctx) return TTB_ERR_INVALID;
+  TTB_REQUIRE(ctx, M >= 0 && N > 0, "layernorm_quant_int8: bad shape");
+  if (M == 0) return TTB_OK;
+  TTB_REQUIRE(ctx, in && out && xq && row_scale && gamma && beta, "layernorm_quant_int8: null pointer");
+  TTB_REQUIRE(ctx, dtype == TTB_F16 || dtype == TTB_BF16, "layernorm_quant_int8: dtype must be F16 or BF16");
+  const bool aligned = N % 8 == 0 && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(xq) |
+                                       reinterpret_cast<uintptr_t>(gamma) | reinterpret_cast<uintptr_t>(beta)) & 15) == 0;
+  if (!aligned || N > 1024) {  // shapes without a fused kernel: the two kernels one after the other give the same result
+    int s = ttb_layernorm(ctx, dtype, in, out, gamma, beta, M, N, eps);
+    if (s != TTB_OK) return s;
+    return ttb_quantize_rows_int8(ctx, dtype, out, M, N, xq, row_scale);
+  }
+  DeviceGuard g(ctx->device);
+  const int grid = grid_for((M + 1) / 2, kLnWarps, ctx->sm_count);
+#define LNQ_CASE(T, IT)                                                                                                                 \
+  launch_pdl(layernorm16_quant_kernel<T, IT>, dim3(grid), dim3(kLnWarps * 32), 0, ctx->stream, (const T*)in, (const T*)gamma, (const T*)beta, \
+             (T*)out, xq, row_scale, M, (int)N, eps)
+#define LNQ_PICK(T)                     \
+  do {                                  \
+    if (N <= 256) LNQ_CASE(T, 1);       \
+    else if (N <= 512) LNQ_CASE(T, 2);  \
+    else if (N <= 768) LNQ_CASE(T, 3);  \
+    else LNQ_CASE(T, 4);                \
+  } while (0)
+  if (dtype == TTB_F16) LNQ_PICK(__half);
+  else LNQ_PICK(__nv_bfloat16);
+#undef LNQ_PICK
+#undef LNQ_CASE
+  return launched(ctx, "layernorm_quant_int8");
+}
 
 extern "C" int ttb_build_cu_seqlens(ttb_ctx* ctx, const int64_t* host_seq_lens, int64_t B, int32_t* cu_dev) {
   if (!ctx) return TTB_ERR_INVALID;

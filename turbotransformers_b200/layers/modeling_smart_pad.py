@@ -32,7 +32,7 @@ class MultiHeadedAttentionSmartBatch(cxx.MultiHeadedAttentionSmartBatch):
         if isinstance(query_tensor, torch.Tensor):
             use_current_stream(query_tensor)
         key_tensor, value_tensor, query_tensor = try_convert(key_tensor), try_convert(value_tensor), try_convert(query_tensor)
-        if mask is None and output_attentions:
+        if mask is None and output_attentions and (attn_type or "self") == "self":
             lens = list(query_seq_len_list)
             m = torch.zeros(len(lens), 1, max(lens), dtype=torch.float32)
             for b, n in enumerate(lens):
@@ -41,10 +41,29 @@ class MultiHeadedAttentionSmartBatch(cxx.MultiHeadedAttentionSmartBatch):
         mask = try_convert(create_empty_if_none(mask))
         output, attn = create_empty_if_none(output), create_empty_if_none(attn)
         cache = {k: (try_convert(v) if v is not None else _empty()) for k, v in (layer_cache or {}).items()}
-        super().__call__(key_tensor, value_tensor, query_tensor, mask, attn_type or "self", output, attn if output_attentions else None, cache,
+        attn_type = attn_type or "self"
+        super().__call__(key_tensor, value_tensor, query_tensor, mask, attn_type, output,
+                         attn if (output_attentions or attn_type == "context") else None, cache,
                          [int(n) for n in query_seq_len_list], [int(n) for n in key_seq_len_list], pre_layernorm, post_layernorm,
                          post_add_input, is_trans_weight)
+        if layer_cache is not None and attn_type == "context":  # the projected encoder memory goes back to the caller's dict
+            for k, v in cache.items():
+                if "memory" in k and not v.is_null():
+                    layer_cache[k] = convert_returns_as_type(v, ReturnType.TORCH)
         return convert_returns_as_type(output, return_type), attn
+
+    @staticmethod
+    def from_onmt(multi_headed_attn, layer_norm=None, is_trans_weight: bool = False):
+        """From an OpenNMT-py style MultiHeadedAttention (linear_keys, linear_values, linear_query, final_linear, head_count),
+        optionally with the block's LayerNorm (modeling_smart_pad.py:113-137 of the reference)."""
+        from .modules import MultiHeadedAttention
+        with torch.no_grad():
+            packed = MultiHeadedAttention.pack_parameter(multi_headed_attn, is_trans_weight)
+            if layer_norm is None:
+                return MultiHeadedAttentionSmartBatch(*packed, multi_headed_attn.head_count)
+            ln = {k: v.detach() for k, v in layer_norm.named_parameters()}
+            return MultiHeadedAttentionSmartBatch(*packed, convert2tt_tensor(ln['weight']), convert2tt_tensor(ln['bias']),
+                                                  multi_headed_attn.head_count)
 
     @staticmethod
     def from_torch(attention, layer_norm=None, is_trans_weight: bool = False):
