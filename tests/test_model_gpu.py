@@ -210,8 +210,9 @@ def test_benchmark_varlen_batch_against_reference_subbatch_and_permutation(dt):
 
 
 def test_bert_large_subbatch_against_oracle():
-    """Benchmark config 4 (BERT-large fp16, seq 512): two sequences against the CPU oracle, 4 layers deep and full depth
-    is covered by the bench's own self-check; batch elements are independent so a sub-batch is representative."""
+    """Benchmark config 4 (BERT-large fp16, seq 512): two sequences against the CPU oracle, 4 layers deep (the quick
+    form; all 24 layers are compared in test_config_size_gpu.py). Batch elements are independent, so a sub-batch is
+    representative."""
     hf32 = synthetic.make_hf_bert("bert-large", 0, num_layers=4)
     ids = synthetic.random_ids(2, 512, hf32.config.vocab_size, 0)
     W = ref_driver.pack_bert_weights(hf32)

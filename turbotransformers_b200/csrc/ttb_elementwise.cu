@@ -4,6 +4,7 @@
 #include <vector>
 
 #include "ttb_common.cuh"
+#include "ttb_sm100.cuh"
 
 using namespace ttb;
 
@@ -119,73 +120,92 @@ layernorm_rows_kernel(const TIn* x, const TIn* __restrict__ residual, const TOut
   }
 }
 
-// The same for 16-bit rows without the residual form (the 16-bit models' hot case): the rows stay in registers as they
-// were loaded (packed 16-bit, half the registers of the fp32 form), so a warp holds four rows and two or three CTAs fit
-// an SM: 8 warps x 2..3 x 4 rows x N x 2 bytes in flight per SM.
-constexpr int kLn16Rows = 4;
+// The same for 16-bit rows without the residual form (the 16-bit models' hot case), as a streaming kernel: a grid that
+// just fills the machine, every warp walking batches of two rows and issuing the loads of its next batch before it
+// works on the current one, so that loads, arithmetic and stores of different batches overlap inside every warp. The
+// rows stay in registers as they were loaded (packed 16-bit); gamma and beta sit in shared memory as fp32, converted
+// once per CTA. About 190 instructions per row at N = 768 (the one-batch-per-warp form it replaces: 340, with all the
+// warps of a wave loading at the same time and then computing at the same time).
+constexpr int kLn16Rows = 2;
+constexpr int kLn16MaxN = 1024;
+
+// The row arithmetic the 16-bit LayerNorm kernels share (so that they agree bit for bit): both moments in one pass,
+// var = E[x^2] - mean^2 as the reference's CPU kernel computes it (layer_norm.cpp:58-66), and the value as two fused
+// multiply-adds, ((x * rstd) - mean * rstd) * gamma + beta.
+__device__ __forceinline__ void ln_row_params(float sum, float sq, float inv_n, float eps, float& rstd, float& shift) {
+  const float mean = sum * inv_n;
+  const float var = fmaxf(sq * inv_n - mean * mean, 0.f);
+  rstd = rsqrtf(var + eps);
+  shift = -mean * rstd;
+}
+__device__ __forceinline__ float ln_value(float x, float rstd, float shift, float g, float b) { return fmaf(fmaf(x, rstd, shift), g, b); }
 
 template <typename T, int ITERS, bool EXTRA>
-__global__ void __launch_bounds__(kLnWarps * 32, ITERS <= 2 ? 3 : 2)
-layernorm16_rows_kernel(const T* x, const T* __restrict__ gamma, const T* __restrict__ beta, T* out, T* __restrict__ out_lo,
-                        float* __restrict__ out_f32, int64_t M, int N, float eps) {
+__global__ void __launch_bounds__(kLnWarps * 32, 2)
+layernorm16_stream_kernel(const T* x, const T* __restrict__ gamma, const T* __restrict__ beta, T* out, T* __restrict__ out_lo,
+                          float* __restrict__ out_f32, int64_t M, int N, float eps) {
+  __shared__ __align__(16) float s_gamma[ITERS * 256], s_beta[ITERS * 256];
   pdl_trigger();
   pdl_wait();
   const int lane = threadIdx.x & 31;
-  const int64_t warps_total = (int64_t)gridDim.x * kLnWarps;
-  for (int64_t row0 = ((int64_t)blockIdx.x * kLnWarps + (threadIdx.x >> 5)) * kLn16Rows; row0 < M; row0 += warps_total * kLn16Rows) {
-    uint4 raw[kLn16Rows][ITERS];
+  const int64_t stride = (int64_t)gridDim.x * kLnWarps;
+  const int64_t batches = (M + kLn16Rows - 1) / kLn16Rows;
+  const float inv_n = 1.0f / (float)N;
+
+  auto load = [&](uint4 (&raw)[kLn16Rows][ITERS], int64_t batch) {
 #pragma unroll
     for (int r = 0; r < kLn16Rows; ++r) {
+      const int64_t row = batch * kLn16Rows + r;
 #pragma unroll
       for (int it = 0; it < ITERS; ++it) {
         const int col = (it * 32 + lane) * 8;
-        raw[r][it] = (row0 + r < M && col < N) ? *reinterpret_cast<const uint4*>(x + (row0 + r) * N + col) : make_uint4(0, 0, 0, 0);
+        raw[r][it] = (row < M && col < N) ? *reinterpret_cast<const uint4*>(x + row * N + col) : make_uint4(0, 0, 0, 0);
       }
     }
-    auto unpack = [](const uint4& q, float (&f)[8]) {
-      const T* h = reinterpret_cast<const T*>(&q);
+  };
+  auto unpack = [](const uint4& q, float (&f)[8]) {
+    const T* h = reinterpret_cast<const T*>(&q);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) f[j] = to_f(h[j]);
-    };
+    for (int j = 0; j < 8; ++j) f[j] = to_f(h[j]);
+  };
+  auto work = [&](uint4 (&raw)[kLn16Rows][ITERS], int64_t batch) {
     // one pass for both moments, var = E[x^2] - mean^2 as the reference's CPU kernel computes it (layer_norm.cpp:58-66)
-    float mean[kLn16Rows], rstd[kLn16Rows];
+    float sum[kLn16Rows], sq[kLn16Rows];
 #pragma unroll
     for (int r = 0; r < kLn16Rows; ++r) {
-      float sum = 0.f, sq = 0.f;
+      sum[r] = 0.f;
+      sq[r] = 0.f;
 #pragma unroll
       for (int it = 0; it < ITERS; ++it) {
         float f[8];
-        unpack(raw[r][it], f);   // lanes beyond N hold zeros
+        unpack(raw[r][it], f);  // lanes beyond N hold zeros
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { sum += f[j]; sq = fmaf(f[j], f[j], sq); }
+        for (int j = 0; j < 8; ++j) { sum[r] += f[j]; sq[r] = fmaf(f[j], f[j], sq[r]); }
         // the packed words stay the only live copy of the row: the second pass converts them again
         asm volatile("" : "+r"(raw[r][it].x), "+r"(raw[r][it].y), "+r"(raw[r][it].z), "+r"(raw[r][it].w));
       }
-      mean[r] = sum;
-      rstd[r] = sq;
     }
+    float rstd[kLn16Rows], shift[kLn16Rows];  // (x - mean) * rstd = x * rstd + shift
 #pragma unroll
-    for (int r = 0; r < kLn16Rows; ++r) {
-      mean[r] = warp_sum(mean[r]) / (float)N;
-      const float var = fmaxf(warp_sum(rstd[r]) / (float)N - mean[r] * mean[r], 0.f);
-      rstd[r] = rsqrtf(var + eps);
-    }
+    for (int r = 0; r < kLn16Rows; ++r) ln_row_params(warp_sum(sum[r]), warp_sum(sq[r]), inv_n, eps, rstd[r], shift[r]);
 #pragma unroll
     for (int it = 0; it < ITERS; ++it) {
       const int col = (it * 32 + lane) * 8;
       if (col < N) {
-        const uint4 gq = *reinterpret_cast<const uint4*>(gamma + col), bq = *reinterpret_cast<const uint4*>(beta + col);
+        float g[8], b[8];
+        *reinterpret_cast<float4*>(&g[0]) = *reinterpret_cast<const float4*>(&s_gamma[col]);
+        *reinterpret_cast<float4*>(&g[4]) = *reinterpret_cast<const float4*>(&s_gamma[col + 4]);
+        *reinterpret_cast<float4*>(&b[0]) = *reinterpret_cast<const float4*>(&s_beta[col]);
+        *reinterpret_cast<float4*>(&b[4]) = *reinterpret_cast<const float4*>(&s_beta[col + 4]);
 #pragma unroll
         for (int r = 0; r < kLn16Rows; ++r) {
-          const int64_t row = row0 + r;
+          const int64_t row = batch * kLn16Rows + r;
           if (row < M) {
-            float f[8], g[8], b[8];
+            float f[8];
             unpack(raw[r][it], f);
-            unpack(gq, g);
-            unpack(bq, b);
             Vec8<T> o;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) o.v[j] = b[j] + g[j] * rstd[r] * (f[j] - mean[r]);
+            for (int j = 0; j < 8; ++j) o.v[j] = ln_value(f[j], rstd[r], shift[r], g[j], b[j]);
             o.store(out + row * N + col);
             if (EXTRA) {
               if (out_f32) {
@@ -205,7 +225,165 @@ layernorm16_rows_kernel(const T* x, const T* __restrict__ gamma, const T* __rest
         }
       }
     }
+  };
+
+  uint4 a[kLn16Rows][ITERS], b[kLn16Rows][ITERS];
+  int64_t batch = (int64_t)blockIdx.x * kLnWarps + (threadIdx.x >> 5);
+  if (batch < batches) load(a, batch);
+  for (int c = threadIdx.x; c < ITERS * 256; c += kLnWarps * 32) {  // in the shadow of the first rows' loads
+    s_gamma[c] = c < N ? to_f(gamma[c]) : 0.f;
+    s_beta[c] = c < N ? to_f(beta[c]) : 0.f;
   }
+  __syncthreads();
+  while (batch < batches) {
+    if (batch + stride < batches) load(b, batch + stride);
+    work(a, batch);
+    batch += stride;
+    if (batch >= batches) break;
+    if (batch + stride < batches) load(a, batch + stride);
+    work(b, batch);
+    batch += stride;
+  }
+}
+
+// Large row counts: the same arithmetic fed by bulk copies. One CTA per SM; a producer thread streams chunks of 32 rows
+// (contiguous in memory) into a ring of shared-memory stages with cp.async.bulk, 16 consumer warps take two rows of a
+// chunk each into registers, release the stage and normalise. The depth of the prefetch is the ring (up to 192 KB per SM
+// in flight), not the register file, and every wait is bounded.
+constexpr int kLnTmaConsumers = 8;
+constexpr int kLnTmaRows = 16;
+constexpr int kLnTmaMaxStages = 6;
+constexpr int kLnTmaCtasPerSm = 2;
+constexpr size_t kLnTmaSmem = 100 * 1024;
+
+template <typename T, int ITERS, bool EXTRA>
+__global__ void __launch_bounds__((kLnTmaConsumers + 1) * 32, kLnTmaCtasPerSm)
+layernorm16_tma_kernel(const T* x, const T* __restrict__ gamma, const T* __restrict__ beta, T* out, T* __restrict__ out_lo,
+                       float* __restrict__ out_f32, int64_t M, int N, float eps, int stages, int* status) {
+  using namespace ttb::sm100;
+  extern __shared__ __align__(128) uint8_t ln_smem[];
+  const uint32_t stage_bytes = (uint32_t)(kLnTmaRows * N * (int)sizeof(T));
+  float* s_gamma = reinterpret_cast<float*>(ln_smem + (size_t)stages * stage_bytes);
+  float* s_beta = s_gamma + N;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_beta + N);  // full[stages], empty[stages]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kLnTmaMaxStages);
+  const uint32_t bar0 = smem_u32(bars);
+  auto full = [&](int st) { return bar0 + 8u * (uint32_t)st; };
+  auto empty = [&](int st) { return bar0 + 8u * (uint32_t)(kLnTmaMaxStages + st); };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int st = 0; st < stages; ++st) {
+      mbar_init(full(st), 1);
+      mbar_init(empty(st), kLnTmaConsumers);
+    }
+    *abort_flag = 0;
+    mbar_init_fence();
+  }
+  pdl_trigger();
+  __syncthreads();  // barriers initialised
+  pdl_wait();
+  const int64_t chunks = (M + kLnTmaRows - 1) / kLnTmaRows;
+  if (warp != kLnTmaConsumers) {  // gamma / beta, in the shadow of the first chunks' copies (the producer does not wait for them)
+    for (int c = threadIdx.x; c < N; c += kLnTmaConsumers * 32) {
+      s_gamma[c] = to_f(gamma[c]);
+      s_beta[c] = to_f(beta[c]);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kLnTmaConsumers * 32) : "memory");
+  }
+  if (warp == kLnTmaConsumers) {
+    if (lane == 0) {
+      uint32_t n = 0;
+      for (int64_t chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x, ++n) {
+        const int st = (int)(n % (uint32_t)stages);
+        const uint32_t round = n / (uint32_t)stages;
+        if (!mbar_wait(empty(st), (round & 1u) ^ 1u, abort_flag)) break;
+        const int64_t rows = min((int64_t)kLnTmaRows, M - chunk * kLnTmaRows);
+        const uint32_t bytes = (uint32_t)(rows * N * (int64_t)sizeof(T));  // a multiple of 16: N is a multiple of 8
+        mbar_expect_tx(full(st), bytes);
+        bulk_load_1d(smem_u32(ln_smem) + (uint32_t)st * stage_bytes, x + chunk * kLnTmaRows * N, bytes, full(st));
+      }
+      if (*abort_flag) {  // let copies in flight land before shared memory is released
+        const long long t0 = clock64();
+        while (clock64() - t0 < 4000000LL) {
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    const float inv_n = 1.0f / (float)N;
+    uint32_t n = 0;
+    for (int64_t chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x, ++n) {
+      const int st = (int)(n % (uint32_t)stages);
+      const uint32_t round = n / (uint32_t)stages;
+      if (!__all_sync(0xffffffffu, mbar_wait(full(st), round & 1u, abort_flag))) break;
+      const T* src = reinterpret_cast<const T*>(ln_smem + (size_t)st * stage_bytes);
+      const int64_t row_base = chunk * kLnTmaRows;
+      uint4 raw[2][ITERS];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int lr = warp + r * kLnTmaConsumers;  // row within the chunk
+#pragma unroll
+        for (int it = 0; it < ITERS; ++it) {
+          const int col = (it * 32 + lane) * 8;
+          raw[r][it] = (row_base + lr < M && col < N) ? *reinterpret_cast<const uint4*>(src + lr * N + col) : make_uint4(0, 0, 0, 0);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty(st));  // the rows are in registers: the stage may be refilled
+      float sum[2] = {0.f, 0.f}, sq[2] = {0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+#pragma unroll
+        for (int it = 0; it < ITERS; ++it) {
+          const T* h = reinterpret_cast<const T*>(&raw[r][it]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { const float f = to_f(h[j]); sum[r] += f; sq[r] = fmaf(f, f, sq[r]); }
+          asm volatile("" : "+r"(raw[r][it].x), "+r"(raw[r][it].y), "+r"(raw[r][it].z), "+r"(raw[r][it].w));
+        }
+      }
+      float rstd[2], shift[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) ln_row_params(warp_sum(sum[r]), warp_sum(sq[r]), inv_n, eps, rstd[r], shift[r]);
+#pragma unroll
+      for (int it = 0; it < ITERS; ++it) {
+        const int col = (it * 32 + lane) * 8;
+        if (col < N) {
+          float g[8], b[8];
+          *reinterpret_cast<float4*>(&g[0]) = *reinterpret_cast<const float4*>(&s_gamma[col]);
+          *reinterpret_cast<float4*>(&g[4]) = *reinterpret_cast<const float4*>(&s_gamma[col + 4]);
+          *reinterpret_cast<float4*>(&b[0]) = *reinterpret_cast<const float4*>(&s_beta[col]);
+          *reinterpret_cast<float4*>(&b[4]) = *reinterpret_cast<const float4*>(&s_beta[col + 4]);
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const int64_t row = row_base + warp + r * kLnTmaConsumers;
+            if (row < M) {
+              const T* h = reinterpret_cast<const T*>(&raw[r][it]);
+              Vec8<T> o;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) o.v[j] = ln_value(to_f(h[j]), rstd[r], shift[r], g[j], b[j]);
+              o.store(out + row * N + col);
+              if (EXTRA) {
+                if (out_f32) {
+                  Vec8<float> w;
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) w.v[j] = o.v[j];
+                  w.store(out_f32 + row * N + col);
+                }
+                if (out_lo) {
+                  Vec8<T> l;
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) l.v[j] = o.v[j] - to_f(from_f<T>(o.v[j]));
+                  l.store(out_lo + row * N + col);
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(status, (int)TTB_ERR_DEVICE_WAIT);
 }
 
 // Any N: one warp per row, three passes over the row (the re-reads hit L1/L2).
@@ -261,15 +439,43 @@ int launch_layernorm(ttb_ctx* ctx, const TIn* x, const TIn* residual, const TOut
                                          (ADD ? (reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(bias)) : 0)) %
                                             16 == 0);
   if constexpr (!ADD && std::is_same<TIn, TOut>::value && sizeof(TIn) == 2) {
-    if (aligned && N <= 1024) {
-      const int grid16 = grid_for((M + kLn16Rows - 1) / kLn16Rows, kLnWarps, ctx->sm_count);
+    const int64_t chunks = (M + kLnTmaRows - 1) / kLnTmaRows;
+    static const bool tma_off = [] { const char* e = getenv("TTB_LN_TMA"); return e && e[0] == '0'; }();
+    if (!tma_off && aligned && N <= kLn16MaxN && chunks >= 2 * (int64_t)ctx->sm_count && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+      const size_t stage_bytes = (size_t)kLnTmaRows * N * sizeof(TOut);
+      const size_t fixed = (size_t)2 * N * sizeof(float) + 2 * kLnTmaMaxStages * 8 + 16;
+      const int stages = (int)std::min<size_t>(kLnTmaMaxStages, (kLnTmaSmem - fixed) / stage_bytes);
+      const size_t smem = (size_t)stages * stage_bytes + fixed;
+      const int grid = (int)std::min<int64_t>(chunks, (int64_t)ctx->sm_count * kLnTmaCtasPerSm);
+#define LNT_CASE(IT)                                                                                                                   \
+  do {                                                                                                                                 \
+    auto kern = extra ? layernorm16_tma_kernel<TOut, IT, true> : layernorm16_tma_kernel<TOut, IT, false>;                              \
+    static bool configured[2][64] = {};                                                                                                \
+    if (ctx->device < 64 && !configured[extra ? 1 : 0][ctx->device]) {                                                                 \
+      TTB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLnTmaSmem));                            \
+      configured[extra ? 1 : 0][ctx->device] = true;                                                                                   \
+    }                                                                                                                                  \
+    launch_pdl(kern, dim3(grid), dim3((kLnTmaConsumers + 1) * 32), smem, ctx->stream, x, gamma, beta, out, out_lo, out_f32, M, (int)N, \
+               eps, stages, ctx->d_status);                                                                                            \
+  } while (0)
+      if (N <= 256) LNT_CASE(1);
+      else if (N <= 512) LNT_CASE(2);
+      else if (N <= 768) LNT_CASE(3);
+      else LNT_CASE(4);
+#undef LNT_CASE
+      return launched(ctx, "layernorm");
+    }
+    if (aligned && N <= kLn16MaxN) {
+      // two CTAs per SM are resident; fewer CTAs when the rows do not fill them
+      const int64_t batches = (M + kLn16Rows - 1) / kLn16Rows;
+      const int grid16 = (int)std::min<int64_t>((batches + kLnWarps - 1) / kLnWarps, (int64_t)ctx->sm_count * 2);
 #define LN16_CASE(IT)                                                                                                                  \
   do {                                                                                                                                 \
     if (extra)                                                                                                                         \
-      launch_pdl(layernorm16_rows_kernel<TOut, IT, true>, dim3(grid16), dim3(block), 0, ctx->stream, x, gamma, beta, out, out_lo, out_f32, M, \
+      launch_pdl(layernorm16_stream_kernel<TOut, IT, true>, dim3(grid16), dim3(block), 0, ctx->stream, x, gamma, beta, out, out_lo, out_f32, M, \
                  (int)N, eps);                                                                                                         \
     else                                                                                                                               \
-      launch_pdl(layernorm16_rows_kernel<TOut, IT, false>, dim3(grid16), dim3(block), 0, ctx->stream, x, gamma, beta, out, out_lo, out_f32, M, \
+      launch_pdl(layernorm16_stream_kernel<TOut, IT, false>, dim3(grid16), dim3(block), 0, ctx->stream, x, gamma, beta, out, out_lo, out_f32, M, \
                  (int)N, eps);                                                                                                         \
   } while (0)
       if (N <= 256) LN16_CASE(1);
@@ -715,9 +921,9 @@ layernorm16_quant_kernel(const T* x, const T* __restrict__ gamma, const T* __res
       rstd[r] = sq;
     }
 #pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-      mean[r] = warp_sum(mean[r]) / (float)N;
-      rstd[r] = rsqrtf(fmaxf(warp_sum(rstd[r]) / (float)N - mean[r] * mean[r], 0.f) + eps);
+    for (int r = 0; r < ROWS; ++r) {  // from here on mean[] holds the shift -mean * rstd
+      const float sum = warp_sum(mean[r]), sq = warp_sum(rstd[r]);
+      ln_row_params(sum, sq, 1.0f / (float)N, eps, rstd[r], mean[r]);
     }
     // normalise in place: the packed registers now hold the rounded 16-bit output, which is also what gets quantised
     float amax[ROWS] = {0.f, 0.f};
@@ -733,7 +939,7 @@ layernorm16_quant_kernel(const T* x, const T* __restrict__ gamma, const T* __res
           T* h = reinterpret_cast<T*>(&raw[r][it]);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            h[j] = from_f<T>(to_f(b[j]) + to_f(g[j]) * rstd[r] * (to_f(h[j]) - mean[r]));
+            h[j] = from_f<T>(ln_value(to_f(h[j]), rstd[r], mean[r], to_f(g[j]), to_f(b[j])));
             amax[r] = fmaxf(amax[r], fabsf(to_f(h[j])));
           }
           if (row0 + r < M) *reinterpret_cast<uint4*>(out + (row0 + r) * N + col) = raw[r][it];

@@ -111,6 +111,7 @@ def main():
     ap.add_argument("--graph", action="store_true", help="with --burst: replay the launches from a CUDA graph (no host time in the number)")
     ap.add_argument("--b-trans", action="store_true", help="matmul: B is stored [N, K]")
     ap.add_argument("--yardstick", action="store_true", help="matmul: also time torch.matmul (cuBLAS SGEMM, TF32 off) on the same operands")
+    ap.add_argument("--plain", action="store_true", help="layernorm: the in-place LayerNorm the encoder layers run (no residual / bias add)")
     ap.add_argument("--pad-rows", action="store_true", help="linear: output rows padded to a multiple of 8 elements, padding declared scratch")
     a = ap.parse_args()
     ctx = _capi.Context(0)
@@ -203,7 +204,10 @@ def main():
         r = torch.randn(M, N, device="cuda", dtype=tdt)
         g = torch.ones(N, device="cuda", dtype=tdt)
         z = torch.zeros(N, device="cuda", dtype=tdt)
-        if a.op == "layernorm":
+        if a.op == "layernorm" and a.plain:
+            fn = lambda: ctx.call("layernorm", code, x, x, g, z, M, N, 1e-12)
+            nbytes = 2.0 * M * N * x.element_size()
+        elif a.op == "layernorm":
             fn = lambda: ctx.call("add_bias_layernorm", code, x, r, z, g, z, M, N, 1e-12)
             nbytes = 3.0 * M * N * x.element_size()
         else:
