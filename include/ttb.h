@@ -239,6 +239,12 @@ int ttb_split_tf32(ttb_ctx* ctx, const float* x, int64_t n, float* hi, float* lo
 int ttb_linear_int8(ttb_ctx* ctx, int out_dtype, const int8_t* Aq, const float* row_scale, const int8_t* Wq,
                     const float* w_scale, const void* bias, const void* residual, int64_t ldr, int64_t M,
                     int64_t N, int64_t K, int epilogue, void* out, int64_t ldo);
+/* ttb_linear_int8 that also gathers, in its epilogue, what a per-row int8 quantiser of `out` needs: row_absmax[m] (fp32,
+ * [M], overwritten) = max |out[m, :]| of the values as stored in out_dtype. With ttb_quantize_rows_int8_given_max the
+ * output of one int8 Linear (the FFN's bias + GELU) becomes the int8 input of the next in one read of it instead of two. */
+int ttb_linear_int8_rowmax(ttb_ctx* ctx, int out_dtype, const int8_t* Aq, const float* row_scale, const int8_t* Wq,
+                           const float* w_scale, const void* bias, const void* residual, int64_t ldr, int64_t M,
+                           int64_t N, int64_t K, int epilogue, void* out, int64_t ldo, float* row_absmax);
 /* The reference's own int8 recipe, python/turbo_transformers/layers/qmodeling_bert.py:13-45: torch dynamic quantisation
  * (torch.quantization.quantize_dynamic, qint8) of a Linear. Weights: per-tensor symmetric, scale = max|W| / 127.5,
  * q = clamp(rint(W / scale), -128, 127), plus their per-output-row sums. Activations: per-tensor affine over the whole
@@ -274,6 +280,11 @@ int ttb_linear_int8_dynamic_noalloc(ttb_ctx* ctx, int dtype, const void* x, cons
  * with the reciprocal rounded to fp32. */
 int ttb_quantize_rows_int8(ttb_ctx* ctx, int dtype, const void* x, int64_t M, int64_t K, int8_t* xq,
                            float* row_scale);
+
+/* ttb_quantize_rows_int8 for rows whose maxima are known (row_absmax[m] = max|x[m,:]|): one streaming pass, results
+ * identical to ttb_quantize_rows_int8. x F16/BF16, K % 8 == 0, 16-byte aligned x and xq. */
+int ttb_quantize_rows_int8_given_max(ttb_ctx* ctx, int dtype, const void* x, int64_t M, int64_t K, const float* row_absmax,
+                                     int8_t* xq, float* row_scale);
 
 /* ttb_layernorm followed by ttb_quantize_rows_int8 of its output, in one pass: out (16-bit, may be `in`) is the layer
  * norm, xq / row_scale its per-row int8 form. For int8 models, whose Linears take the normalised activations as int8 and

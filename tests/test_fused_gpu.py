@@ -366,3 +366,34 @@ def test_layernorm_with_int8_output_equals_the_two_kernels_in_sequence(ctx, dt, 
     # and the quantiser against the numpy statement of the scheme
     xq, xs = restate.q_quantize_rows(host(want))
     assert (want_q.cpu().numpy() == xq).all() and maxdiff(host(want_s), xs.reshape(-1)) == 0.0
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("M,N,K", [(300, 3072, 768), (8192, 3072, 768), (128, 3072, 768), (77, 768, 3072), (1000, 200, 64), (2100, 4096, 1024)])
+@pytest.mark.parametrize("epi", ["bias_gelu", "bias_residual", "none"])
+def test_int8_linear_gathers_row_maxima_for_the_next_quantiser(ctx, dt, M, N, K, epi):
+    """ttb_linear_int8_rowmax + ttb_quantize_rows_int8_given_max == ttb_linear_int8 + ttb_quantize_rows_int8, bit for bit
+    (every tile shape the dispatcher picks: CTA pairs, single CTAs, narrow tiles, split-K clusters)."""
+    r = rng(M + N + K)
+    xq = torch.from_numpy(r.integers(-127, 128, (M, K)).astype(np.int8)).cuda()
+    xs = torch.from_numpy((r.random(M).astype(np.float32) + 0.5) * 0.02).cuda()
+    wq = torch.from_numpy(r.integers(-127, 128, (N, K)).astype(np.int8)).cuda()
+    ws = torch.tensor([0.004], dtype=torch.float32, device="cuda")
+    bias = dev(r.standard_normal(N).astype(np.float32), dt)
+    res = dev(r.standard_normal((M, N)).astype(np.float32), dt)
+    e = {"none": 0, "bias_gelu": 2, "bias_residual": 3}[epi]
+    want = torch.empty((M, N), dtype=TORCH_DT[dt], device="cuda")
+    ctx.call("linear_int8", code(dt), xq, xs, wq, ws, bias, res, N, M, N, K, e, want, N)
+    want_q = torch.empty((M, N), dtype=torch.int8, device="cuda")
+    want_s = torch.empty(M, dtype=torch.float32, device="cuda")
+    ctx.call("quantize_rows_int8", code(dt), want, M, N, want_q, want_s)
+    out = torch.empty_like(want)
+    amax = torch.full((M,), 1e30, dtype=torch.float32, device="cuda")   # the call overwrites it
+    ctx.call("linear_int8_rowmax", code(dt), xq, xs, wq, ws, bias, res, N, M, N, K, e, out, N, amax)
+    q = torch.full((M, N), 99, dtype=torch.int8, device="cuda")
+    s = torch.full((M,), -1.0, dtype=torch.float32, device="cuda")
+    ctx.call("quantize_rows_int8_given_max", code(dt), out, M, N, amax, q, s)
+    assert ctx.device_status() == _capi.OK
+    assert torch.equal(out, want)
+    assert torch.equal(amax, want.float().abs().amax(dim=1))
+    assert torch.equal(s, want_s) and torch.equal(q, want_q)

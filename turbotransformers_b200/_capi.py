@@ -82,6 +82,8 @@ SIGNATURES = {
     "ttb_linear_int8": (i32, [p, i32, p, p, p, p, p, p, i64, i64, i64, i64, i32, p, i64]),
     "ttb_linear_int8_dynamic_noalloc": (i32, [p, i32, p, p, p, p, p, i64, i64, i64, i64, i32, p, i64]),
     "ttb_quantize_rows_int8": (i32, [p, i32, p, i64, i64, p, p]),
+    "ttb_linear_int8_rowmax": (i32, [p, i32, p, p, p, p, p, p, i64, i64, i64, i64, i32, p, i64, p]),
+    "ttb_quantize_rows_int8_given_max": (i32, [p, i32, p, i64, i64, p, p, p]),
     "ttb_layernorm_quant_int8": (i32, [p, i32, p, p, p, p, p, p, i64, i64, f32]),
     "ttb_attention_fwd": (i32, [p, i32, p, i64, p, i64, i64, i64, i64, p, i64, i64, i32, f32, p]),
     "ttb_embedding_ln": (i32, [p, i32, p, p, p, p, i64, i64, i64, p, p, p, p, p, i64, i64, i64, i64, f32, p]),

@@ -156,7 +156,7 @@ void PackedLinear::Int8(bool is_trans, const int8_t** wq, const float** scale, c
 }
 
 void PackedLinear::Forward(const Tensor& x, int64_t M, int epilogue, const void* residual, void* out, bool is_trans,
-                           const char* name, int64_t ldo, void* out_lo, bool f32_out) const {
+                           const char* name, int64_t ldo, void* out_lo, bool f32_out, Tensor* q8_of_out) const {
   const int dt = FloatType(x, name);
   SameTypeDevice(x, weight_, name);
   const int64_t K = in_dim(is_trans), N = out_dim(is_trans);
@@ -214,16 +214,32 @@ void PackedLinear::Forward(const Tensor& x, int64_t M, int epilogue, const void*
     const int8_t* wq;
     const float* ws;
     Int8(is_trans, &wq, &ws);
+    // The product; when the caller wants the int8 form of the output too (the next Linear is an int8 one), the epilogue
+    // gathers the row maxima and one streaming pass quantises, instead of a quantiser that reads the output twice.
+    auto product = [&](const int8_t* aq, const float* as) {
+      static const bool fused_off = [] { const char* e = getenv("TTB_INT8_ROWMAX"); return e && e[0] == '0'; }();  // measurement switch
+      // (below about a thousand rows the extra launches cost more than the second read they save)
+      if (!q8_of_out || fused_off || N % 8 != 0 || N > 4096 || M < 1024) {
+        Check(ttb_linear_int8(c, dt, aq, as, wq, ws, bias, residual, N, M, N, K, epilogue, out, N), c, name);
+        return;
+      }
+      Tensor maxima(nullptr);
+      float* am = maxima.Reshape<float>({M}, kDLCUDA, x.device_id(), "linear/int8_row_maxima");
+      Check(ttb_linear_int8_rowmax(c, dt, aq, as, wq, ws, bias, residual, N, M, N, K, epilogue, out, N, am), c, name);
+      core::TensorExtras& ex = q8_of_out->NewExtras();
+      int8_t* q = static_cast<int8_t*>(ex.q8.Reshape(core::kInt8, {M, N}, kDLCUDA, x.device_id(), "linear/int8_activations"));
+      float* qs = ex.q8_scale.Reshape<float>({M}, kDLCUDA, x.device_id(), "linear/int8_row_scales");
+      Check(ttb_quantize_rows_int8_given_max(c, dt, out, M, N, am, q, qs), c, name);
+    };
     if (x.q8() && x.q8_scale() && x.q8()->numel() == M * K) {  // the producer already quantised this activation
-      Check(ttb_linear_int8(c, dt, x.q8()->data<int8_t>(), x.q8_scale()->data<float>(), wq, ws, bias, residual, N, M, N, K, epilogue, out, N), c,
-            name);
+      product(x.q8()->data<int8_t>(), x.q8_scale()->data<float>());
       return;
     }
     Tensor xq(nullptr), xs(nullptr);
     xq.Reshape(core::kInt8, {M, K}, kDLCUDA, x.device_id(), "linear/int8_activations");
     xs.Reshape(core::kFloat32, {M}, kDLCUDA, x.device_id(), "linear/int8_row_scales");
     Check(ttb_quantize_rows_int8(c, dt, x.raw(), M, K, xq.mutableData<int8_t>(), xs.mutableData<float>()), c, name);
-    Check(ttb_linear_int8(c, dt, xq.data<int8_t>(), xs.data<float>(), wq, ws, bias, residual, N, M, N, K, epilogue, out, N), c, name);
+    product(xq.data<int8_t>(), xs.data<float>());
     return;
   }
   if (ldo != N) epilogue |= TTB_EPI_FLAG_ROW_PADDING_IS_SCRATCH;  // only Linear's own row-padded scratch gets here
@@ -754,7 +770,9 @@ void BertIntermediate::operator()(const Tensor& input_tensor, Tensor* output_ten
   void* lo = nullptr;
   if (PreciseMode(dt) && input_tensor.lo() && !dense_.use_int8())  // the activation leaves as two planes, like it came
     lo = output_tensor->NewExtras().lo.Reshape(input_tensor.dtype(), shape, kDLCUDA, input_tensor.device_id(), "precise/lo_plane");
-  dense_.Forward(input_tensor, input_tensor.rows(), TTB_EPI_BIAS_GELU, nullptr, out, false, "BertIntermediate", 0, lo);
+  // int8 (per-row scheme): BertOutput's Linear takes this activation as int8, so it leaves with its int8 form attached
+  Tensor* q8 = dense_.int8_mode() == PackedLinear::kInt8PerRow ? output_tensor : nullptr;
+  dense_.Forward(input_tensor, input_tensor.rows(), TTB_EPI_BIAS_GELU, nullptr, out, false, "BertIntermediate", 0, lo, false, q8);
 }
 
 void BertOutput::EnforceShapeAndType() const {

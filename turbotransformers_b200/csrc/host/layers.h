@@ -51,8 +51,9 @@ class PackedLinear {
   // `ldo` (elements between output rows) defaults to N. A bf16 x that carries a lo plane is used at full precision
   // (two passes). out_lo (bf16 only) receives the second plane of the output. f32_out: `out` and `residual` are fp32
   // (the residual stream of a bf16 model in its precise mode).
+  // q8_of_out (per-row int8 mode): the tensor that owns `out`; it gets the int8 form of the output attached (q8(), q8_scale()).
   void Forward(const core::Tensor& x, int64_t M, int epilogue, const void* residual, void* out, bool is_trans,
-               const char* name, int64_t ldo = 0, void* out_lo = nullptr, bool f32_out = false) const;
+               const char* name, int64_t ldo = 0, void* out_lo = nullptr, bool f32_out = false, core::Tensor* q8_of_out = nullptr) const;
 
  private:
   core::Tensor weight_, bias_;

@@ -891,6 +891,45 @@ quantize_rows16_wide_kernel(const T* __restrict__ x, int64_t M, int K, int8_t* _
   }
 }
 
+// Rows whose maxima are known (gathered by the epilogue of the GEMM that wrote them): one streaming pass, a warp per row
+// with all of the row's 16-byte loads issued before the first use. ITERS * 256 >= K.
+template <typename T, int ITERS>
+__global__ void __launch_bounds__(kLnWarps * 32)
+quantize_rows16_given_max_kernel(const T* __restrict__ x, int64_t M, int K, const float* __restrict__ row_absmax, int8_t* __restrict__ xq,
+                                 float* __restrict__ scale) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_total = (int64_t)gridDim.x * kLnWarps;
+  for (int64_t row = (int64_t)blockIdx.x * kLnWarps + (threadIdx.x >> 5); row < M; row += warps_total) {
+    const T* xr = x + row * K;
+    uint4 raw[ITERS];
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int col = (it * 32 + lane) * 8;
+      raw[it] = col < K ? *reinterpret_cast<const uint4*>(xr + col) : make_uint4(0, 0, 0, 0);
+    }
+    const float amax = row_absmax[row];
+    const float sc = amax > 0.f ? amax / 127.0f : 1.0f;
+    const float inv = __frcp_rn(sc);
+    if (lane == 0) scale[row] = sc;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int col = (it * 32 + lane) * 8;
+      if (col < K) {
+        const T* h = reinterpret_cast<const T*>(&raw[it]);
+        uint32_t w[2] = {0u, 0u};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float v = fminf(fmaxf(rintf(__fmul_rn(to_f(h[j]), inv)), -127.f), 127.f);
+          w[j >> 2] |= ((uint32_t)(int)v & 0xffu) << ((j & 3) * 8);
+        }
+        *reinterpret_cast<uint2*>(xq + row * K + col) = make_uint2(w[0], w[1]);
+      }
+    }
+  }
+}
+
 // LayerNorm of 16-bit rows that also leaves the int8 form of its output (per-row symmetric, the quantiser above applied
 // to the rounded 16-bit values, so the result is the same as running the two kernels one after the other): the input of
 // an int8 Linear is produced where it is computed instead of by another pass over the activations.
@@ -1322,6 +1361,33 @@ extern "C" int ttb_quantize_rows_int8(ttb_ctx* ctx, int dtype, const void* x, in
   TTB_DISPATCH_FLOAT(ctx, dtype, T,
                      (quantize_rows_kernel<T><<<grid, kRowsPerBlock * 32, 0, ctx->stream>>>((const T*)x, M, (int)K, xq, row_scale)));
   return launched(ctx, "quantize_rows_int8");
+}
+
+extern "C" int ttb_quantize_rows_int8_given_max(ttb_ctx* ctx, int dtype, const void* x, int64_t M, int64_t K, const float* row_absmax,
+                                                int8_t* xq, float* row_scale) {
+  if (!ctx) return TTB_ERR_INVALID;
+  TTB_REQUIRE(ctx, M >= 0 && K > 0, "quantize_rows_int8_given_max: bad shape");
+  if (M == 0) return TTB_OK;
+  TTB_REQUIRE(ctx, x && xq && row_scale && row_absmax, "quantize_rows_int8_given_max: null pointer");
+  TTB_REQUIRE(ctx, dtype == TTB_F16 || dtype == TTB_BF16, "quantize_rows_int8_given_max: F16 or BF16 rows");
+  TTB_REQUIRE(ctx, K % 8 == 0 && K <= 4096 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(xq)) & 15) == 0,
+              "quantize_rows_int8_given_max: K %% 8 == 0, K <= 4096 and 16-byte aligned pointers (K = %lld)", (long long)K);
+  DeviceGuard g(ctx->device);
+  const int grid = grid_for(M, kLnWarps, ctx->sm_count);
+#define QG_CASE(T, IT) \
+  launch_pdl(quantize_rows16_given_max_kernel<T, IT>, dim3(grid), dim3(kLnWarps * 32), 0, ctx->stream, (const T*)x, M, (int)K, row_absmax, xq, row_scale)
+#define QG_PICK(T)                       \
+  do {                                   \
+    if (K <= 1024) QG_CASE(T, 4);        \
+    else if (K <= 2048) QG_CASE(T, 8);   \
+    else if (K <= 3072) QG_CASE(T, 12);  \
+    else QG_CASE(T, 16);                 \
+  } while (0)
+  if (dtype == TTB_F16) QG_PICK(__half);
+  else QG_PICK(__nv_bfloat16);
+#undef QG_PICK
+#undef QG_CASE
+  return launched(ctx, "quantize_rows_int8_given_max");
 }
 
 extern "C" int ttb_quantize_tensor_affine(ttb_ctx* ctx, int dtype, const void* x, int64_t M, int64_t K, int8_t* xq, float* qparams) {

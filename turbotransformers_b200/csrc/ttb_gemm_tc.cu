@@ -72,6 +72,7 @@ struct GemmParams {
   const float* w_scale;    // int8: device scalar, weight scale
   const float* act_qparams;  // int8, affine per tensor: device [scale, zero point]; null selects the symmetric form
   const int* col_sum;        // int8, affine: sum over k of Wq[n, k]
+  float* row_absmax;         // int8 kind, or null: [M], receives max |out[m, :]| as stored (atomic maximum; zero before the launch)
   int epilogue;
   int tma_store;           // 1: the output tile goes through shared memory and TMA stores (needs aligned, 16-byte-multiple rows)
   int split_k;             // CTAs per cluster sharing one tile (SK kernels), else 1
@@ -405,6 +406,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         // ---- one 128-byte-wide chunk of output columns at a time: TMEM -> registers -> (bias, activation, residual) ->
         //      swizzled shared memory tile -> one TMA store per warp. Residual rows are fetched with coalesced 16-byte
         //      loads (8 lanes per 128-byte row) and handed over through the same tile.
+        float row_max = 0.f;  // int8 kind with p.row_absmax: largest |value| this thread produced for its row in this tile
 #pragma unroll 1
         for (int cc = c_beg; cc < c_end; ++cc) {
           const int col0 = n_blk * BN + cc * CH;
@@ -480,6 +482,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                 for (int j = 0; j < P16; ++j) v[g * P16 + j] += q[j];
               }
             }
+            if (KIND == KIND_I8 && p.row_absmax) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) row_max = fmaxf(row_max, fabsf(v[j]));
+            }
 #pragma unroll
             for (int g = 0; g < G16; ++g)
               *reinterpret_cast<uint4*>(buf + lane * 128 + (((hh * G16 + g) ^ (lane & 7)) << 4)) = pack16<OutT>(&v[g * P16]);
@@ -510,10 +516,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             }
           }
         }
+        // rounding to OutT is monotonic, so the maximum of the stored values is the rounded maximum; non-negative floats
+        // order like their bit patterns
+        if (KIND == KIND_I8 && p.row_absmax && row < p.M)
+          atomicMax(reinterpret_cast<int*>(p.row_absmax + row), __float_as_int(to_f(from_f<OutT>(row_max))));
         continue;
       }
       // ---- direct path (narrow tiles or unaligned output): the first warp of each lane quarter walks the tile
       bool gave_up = false;
+      float row_max = 0.f;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -572,6 +583,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] += q[j];
         }
+        if (KIND == KIND_I8 && p.row_absmax) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) row_max = fmaxf(row_max, fabsf(v[j]));
+        }
 #pragma unroll 1
         for (int plane = 0; plane < (two_planes ? 2 : 1); ++plane) {
           OutT* dstp = (plane == 0 ? out : static_cast<OutT*>(p.out_lo)) + (long long)row * p.ldo + col0;
@@ -595,6 +611,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         }
       }
       if (gave_up) break;
+      if (KIND == KIND_I8 && p.row_absmax && row < p.M && !(SK && group > 1 && rank != 0))
+        atomicMax(reinterpret_cast<int*>(p.row_absmax + row), __float_as_int(to_f(from_f<OutT>(row_max))));
       tc_fence_before();
       __syncwarp();
       if (lane == 0) release_accumulator(acc);
@@ -862,9 +880,17 @@ int check_linear(ttb_ctx* ctx, const char* what, const void* A, const void* W, c
   return TTB_OK;
 }
 
+// Zero fill that takes part in programmatic dependent launch: it returns only after the kernel ahead of it has completed,
+// so a kernel that waits for this one is ordered after that one too.
+__global__ void __launch_bounds__(256) zero_floats_kernel(float* dst, int64_t n) {
+  pdl_trigger();
+  pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) dst[i] = 0.f;
+}
+
 int linear_int8_common(ttb_ctx* ctx, const char* what, int out_dtype, const int8_t* Aq, const float* row_scale, const float* act_qparams,
                        const int8_t* Wq, const float* w_scale, const int32_t* col_sum, const void* bias, const void* residual, int64_t ldr,
-                       int64_t M, int64_t N, int64_t K, int epilogue, void* out, int64_t ldo) {
+                       int64_t M, int64_t N, int64_t K, int epilogue, void* out, int64_t ldo, float* row_absmax = nullptr) {
   TTB_REQUIRE(ctx, out_dtype == TTB_F16 || out_dtype == TTB_BF16, "%s: output dtype must be F16 or BF16", what);
   int s = check_linear(ctx, what, Aq, Wq, bias, residual, M, N, K, epilogue, out, ldo, 16);
   if (s || M == 0) return s;
@@ -876,6 +902,11 @@ int linear_int8_common(ttb_ctx* ctx, const char* what, int out_dtype, const int8
   p.out = out; p.ldo = ldo; p.bias = bias; p.residual = residual; p.ldr = ldr;
   p.row_scale = row_scale; p.w_scale = w_scale; p.act_qparams = act_qparams; p.col_sum = col_sum;
   p.epilogue = epilogue; p.split_k = 1; p.status = ctx->d_status;
+  if (row_absmax) {  // zero-filled by a kernel of its own, so that the launches stay one programmatic-dependency chain
+    const int64_t n4 = (M + 3) / 4;
+    launch_pdl(zero_floats_kernel, dim3((unsigned)std::min<int64_t>((n4 + 255) / 256, 1024)), dim3(256), 0, ctx->stream, row_absmax, M);
+    p.row_absmax = row_absmax;
+  }
   const Operands op{Aq, nullptr, K, Wq, nullptr};
   if (act_qparams) {
     if (out_dtype == TTB_F16) return pick_tile<KIND_I8, __half, VAR_AFFINE>(ctx, op, p);
@@ -1046,6 +1077,15 @@ extern "C" int ttb_linear_int8(ttb_ctx* ctx, int out_dtype, const int8_t* Aq, co
   TTB_REQUIRE(ctx, M == 0 || row_scale != nullptr, "linear_int8: null scale pointer");
   return linear_int8_common(ctx, "linear_int8", out_dtype, Aq, row_scale, nullptr, Wq, w_scale, nullptr, bias, residual, ldr, M, N, K, epilogue, out,
                             ldo);
+}
+
+extern "C" int ttb_linear_int8_rowmax(ttb_ctx* ctx, int out_dtype, const int8_t* Aq, const float* row_scale, const int8_t* Wq,
+                                      const float* w_scale, const void* bias, const void* residual, int64_t ldr, int64_t M, int64_t N,
+                                      int64_t K, int epilogue, void* out, int64_t ldo, float* row_absmax) {
+  if (!ctx) return TTB_ERR_INVALID;
+  TTB_REQUIRE(ctx, M == 0 || (row_scale != nullptr && row_absmax != nullptr), "linear_int8_rowmax: null scale or maximum pointer");
+  return linear_int8_common(ctx, "linear_int8_rowmax", out_dtype, Aq, row_scale, nullptr, Wq, w_scale, nullptr, bias, residual, ldr, M, N, K, epilogue,
+                            out, ldo, row_absmax);
 }
 
 extern "C" int ttb_linear_int8_affine(ttb_ctx* ctx, int out_dtype, const int8_t* Aq, const float* act_qparams, const int8_t* Wq,

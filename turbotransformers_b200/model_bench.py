@@ -4,6 +4,8 @@
     python -m turbotransformers_b200.model_bench --config sweep  # BERT-base fp16, batch {1,8,32} x seq {32,128,512}
     python -m turbotransformers_b200.model_bench --config c3     # BERT-base int8, batch {1,16,64}, seq 128
     python -m turbotransformers_b200.model_bench --config c4     # BERT-large fp16, 32 sequences of 512 (one GPU's shard of 256)
+    python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 -m turbotransformers_b200.model_bench --config c4
+                                                                 # the 256 sequences split over N GPUs, max over ranks
     python -m turbotransformers_b200.model_bench --config c5     # GPT-2 small fp16, b8 s1024, logits
     python -m turbotransformers_b200.model_bench --config c5gen  # GPT-2 small fp16 generation: 512-token prompt, then token by token
     python -m turbotransformers_b200.model_bench --config cpp [--devices N]   # the Python-free C++ host on the headline batch
@@ -14,6 +16,7 @@ Weights are seeded synthetic (synthetic.py); ids are uniform.
 """
 import argparse
 import json
+import os
 
 import torch
 
@@ -103,11 +106,36 @@ def main():
             mean, p50 = timeit(lambda: model(ids), a.warmup, a.iters)
             report(name, b, s, enc_flops(12, 768, s), mean, p50)
     elif a.config == "c4":
+        # BERT-large fp16, 256 sequences of 512: the batch is split into contiguous shards, one per GPU, weights replicated,
+        # no collective on the data path. Under torch.distributed.run every rank runs its shard of 256 / world sequences and
+        # the job's rate is all 256 sequences over the slowest rank's device time; a plain single-process run times one
+        # GPU's shard of an 8-GPU job (32 sequences).
+        import torch.distributed as dist
+        from turbotransformers_b200 import sharding
+        world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+        if world > 1:
+            dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+            torch.cuda.set_device(dev)
+            dist.init_process_group("nccl", device_id=dev)
+        shards = sharding.contiguous_shards(256, world if world > 1 else 8)
+        mine = shards[rank if world > 1 else 0]
         hf = synthetic.make_hf_bert("bert-large", 0)
         model = tt.BertModel.from_torch(hf.to(dev).half(), dev)
-        ids = synthetic.random_ids(32, 512, hf.config.vocab_size, 0).to(dev)
+        all_ids = synthetic.random_ids(256, 512, hf.config.vocab_size, 0)
+        ids = all_ids[mine].to(dev)
+        if world > 1:
+            dist.barrier()
         mean, p50 = timeit(lambda: model(ids), a.warmup, a.iters)
-        report("bert-large fp16 (32 of the 256 sequences: one GPU's shard at 8 GPUs)", 32, 512, enc_flops(24, 1024, 512), mean, p50)
+        if world > 1:
+            mean, p50 = sharding.reduce_max_ms(mean, dev), sharding.reduce_max_ms(p50, dev)
+            if rank == 0:
+                report(f"bert-large fp16, 256 sequences over {world} GPUs ({len(mine)} per GPU, max over ranks)", 256, 512,
+                       enc_flops(24, 1024, 512), mean, p50, n_gpus=world)
+            assert tt._cxx_module.device_status(dev.index) == 0
+            dist.barrier()
+            dist.destroy_process_group()
+            return
+        report("bert-large fp16 (32 of the 256 sequences: one GPU's shard at 8 GPUs)", len(mine), 512, enc_flops(24, 1024, 512), mean, p50)
     elif a.config == "c5gen":
         hf = synthetic.make_hf_gpt2("gpt2-small", 0)
         model = tt.GPT2Model.from_torch(hf.to(dev).half(), dev)
