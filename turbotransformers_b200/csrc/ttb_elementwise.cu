@@ -246,6 +246,64 @@ layernorm16_stream_kernel(const T* x, const T* __restrict__ gamma, const T* __re
   }
 }
 
+// Few rows (a single short request): one row per warp, the row and its gamma / beta slices all requested before the first
+// use, no shared memory and no block barrier: the kernel is one memory round trip long.
+template <typename T, int ITERS, bool EXTRA>
+__global__ void __launch_bounds__(kLnWarps * 32)
+layernorm16_small_kernel(const T* x, const T* __restrict__ gamma, const T* __restrict__ beta, T* out, T* __restrict__ out_lo,
+                         float* __restrict__ out_f32, int64_t M, int N, float eps) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kLnWarps + (threadIdx.x >> 5);
+  if (row >= M) return;
+  uint4 raw[ITERS], gq[ITERS], bq[ITERS];
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int col = (it * 32 + lane) * 8;
+    const bool in = col < N;
+    raw[it] = in ? *reinterpret_cast<const uint4*>(x + row * N + col) : make_uint4(0, 0, 0, 0);
+    gq[it] = in ? *reinterpret_cast<const uint4*>(gamma + col) : make_uint4(0, 0, 0, 0);
+    bq[it] = in ? *reinterpret_cast<const uint4*>(beta + col) : make_uint4(0, 0, 0, 0);
+  }
+  float sum = 0.f, sq = 0.f;
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const T* h = reinterpret_cast<const T*>(&raw[it]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { const float f = to_f(h[j]); sum += f; sq = fmaf(f, f, sq); }
+  }
+  float rstd, shift;
+  ln_row_params(warp_sum(sum), warp_sum(sq), 1.0f / (float)N, eps, rstd, shift);
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int col = (it * 32 + lane) * 8;
+    if (col < N) {
+      const T* h = reinterpret_cast<const T*>(&raw[it]);
+      const T* g = reinterpret_cast<const T*>(&gq[it]);
+      const T* b = reinterpret_cast<const T*>(&bq[it]);
+      Vec8<T> o;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o.v[j] = ln_value(to_f(h[j]), rstd, shift, to_f(g[j]), to_f(b[j]));
+      o.store(out + row * N + col);
+      if (EXTRA) {
+        if (out_f32) {
+          Vec8<float> w;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) w.v[j] = o.v[j];
+          w.store(out_f32 + row * N + col);
+        }
+        if (out_lo) {
+          Vec8<T> l;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) l.v[j] = o.v[j] - to_f(from_f<T>(o.v[j]));
+          l.store(out_lo + row * N + col);
+        }
+      }
+    }
+  }
+}
+
 // Large row counts: the same arithmetic fed by bulk copies. One CTA per SM; a producer thread streams chunks of 32 rows
 // (contiguous in memory) into a ring of shared-memory stages with cp.async.bulk, 16 consumer warps take two rows of a
 // chunk each into registers, release the stage and normalise. The depth of the prefetch is the ring (up to 192 KB per SM
@@ -463,6 +521,24 @@ int launch_layernorm(ttb_ctx* ctx, const TIn* x, const TIn* residual, const TOut
       else if (N <= 768) LNT_CASE(3);
       else LNT_CASE(4);
 #undef LNT_CASE
+      return launched(ctx, "layernorm");
+    }
+    if (aligned && N <= kLn16MaxN && M <= 8 * (int64_t)ctx->sm_count) {  // at most one CTA of single-row warps per SM
+      const int grid1 = (int)((M + kLnWarps - 1) / kLnWarps);
+#define LNS_CASE(IT)                                                                                                                   \
+  do {                                                                                                                                 \
+    if (extra)                                                                                                                         \
+      launch_pdl(layernorm16_small_kernel<TOut, IT, true>, dim3(grid1), dim3(block), 0, ctx->stream, x, gamma, beta, out, out_lo, out_f32, M, \
+                 (int)N, eps);                                                                                                         \
+    else                                                                                                                               \
+      launch_pdl(layernorm16_small_kernel<TOut, IT, false>, dim3(grid1), dim3(block), 0, ctx->stream, x, gamma, beta, out, out_lo, out_f32, M, \
+                 (int)N, eps);                                                                                                         \
+  } while (0)
+      if (N <= 256) LNS_CASE(1);
+      else if (N <= 512) LNS_CASE(2);
+      else if (N <= 768) LNS_CASE(3);
+      else LNS_CASE(4);
+#undef LNS_CASE
       return launched(ctx, "layernorm");
     }
     if (aligned && N <= kLn16MaxN) {

@@ -410,7 +410,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
 #pragma unroll 1
         for (int cc = c_beg; cc < c_end; ++cc) {
           const int col0 = n_blk * BN + cc * CH;
-          if (cc != c_beg && p.epilogue == TTB_EPI_BIAS_RESIDUAL) load_residual(res, row_base, col0);
           // the TMA store that last read this warp's staging tile must have finished reading it
           if (lane == 0) bulk_wait_read<0>();
           __syncwarp();
@@ -421,6 +420,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
               *reinterpret_cast<uint4*>(buf + r * 128 + ((ch ^ (r & 7)) << 4)) = res[i];
             }
             __syncwarp();
+            // the next chunk's residual rows travel while this chunk is computed
+            if (cc + 1 < c_end) load_residual(res, row_base, col0 + CH);
           }
           uint4 lo_pack[LO_N];  // two-plane outputs: the chunk's "lo" values, kept until the first store has read the tile
           // 32 columns at a time, to keep the live register set small
