@@ -11,7 +11,7 @@ import pytest
 import torch
 
 from oracle import restate
-from tests.helpers import ATOL, code, dev, host, maxdiff, rng, rounded
+from tests.helpers import ATOL, TORCH_DT, code, dev, host, maxdiff, rng, rounded
 from turbotransformers_b200 import _capi
 
 pytestmark = pytest.mark.gpu
@@ -172,6 +172,25 @@ def test_layernorm_and_add_bias_layernorm(ctx, dt, M, N):
     assert maxdiff(host(Y), want2) < ATOL[dt] * 4
     ctx.call("layernorm", code(dt), X, X, dev(gamma, dt), dev(beta, dt), M, N, 1e-5)  # in place
     assert maxdiff(host(X), want2) < ATOL[dt] * 4
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("M,N", [(1184, 768), (1185, 768), (4735, 768), (4737, 768), (18424, 768), (9999, 1024), (20001, 256), (6000, 520)])
+def test_layernorm_16bit_every_kernel_by_row_count(ctx, dt, M, N):
+    """The 16-bit LayerNorm picks its kernel by row count (one row per warp / register streaming / bulk-copy staged);
+    sizes on both sides of each switch, ragged last chunks, in place and out of place, all against the restatement."""
+    r = rng(M + N)
+    x = rounded(r.standard_normal((M, N)).astype(np.float32) * 1.5 + 0.25, dt)
+    gamma, beta = (rounded(r.standard_normal(N).astype(np.float32), dt) for _ in range(2))
+    want = restate.layer_norm(x, gamma, beta, 1e-12)
+    X = dev(x, dt)
+    Y = torch.full((M + 1, N), float("nan"), dtype=TORCH_DT[dt], device="cuda")   # one guard row behind the output
+    ctx.call("layernorm", code(dt), X, Y, dev(gamma, dt), dev(beta, dt), M, N, 1e-12)
+    assert ctx.device_status() == _capi.OK
+    assert torch.isnan(Y[M]).all()
+    assert maxdiff(host(Y[:M]), want) < ATOL[dt] * 4
+    ctx.call("layernorm", code(dt), X, X, dev(gamma, dt), dev(beta, dt), M, N, 1e-12)
+    assert torch.equal(X, Y[:M])
 
 
 def test_layernorm_honours_eps(ctx):
