@@ -229,6 +229,16 @@ typedef struct ttb_linear_args {
   int64_t ldo;
 } ttb_linear_args;
 int ttb_linear_ex(ttb_ctx* ctx, const ttb_linear_args* args);
+/* out = LayerNorm(A . Wp^T + bias + residual) * gamma + beta over rows of N: the attention output projection and the FFN
+ * output Linear of a post-LN encoder layer together with the AddBiasLayerNorm that follows them
+ * (turbo_transformers/layers/bert_output.cpp:40-56, kernels/layer_norm.cpp:30-75). By default ttb_linear and
+ * ttb_layernorm run in sequence. With TTB_GEMM_LN=1 in the environment, N a multiple of 256 up to 1024, M >= 1024 and
+ * K >= 2048 (TTB_GEMM_LN=2: any K), one kernel does all of it: the CTAs holding a row block's N-tiles exchange row sums
+ * through a workspace the context owns. That form needs its whole grid resident, so use it with one context per device.
+ * The LayerNorm sees the sum rounded to `dtype` either way. F16/BF16, dense output rows, 16-byte aligned pointers. */
+int ttb_linear_layernorm(ttb_ctx* ctx, int dtype, const void* A, int64_t lda, const void* Wp, const void* bias,
+                         const void* residual, int64_t ldr, const void* gamma, const void* beta, float eps, int64_t M,
+                         int64_t N, int64_t K, void* out, int64_t ldo);
 /* hi[i] = x[i] rounded to tf32 (10 mantissa bits), lo[i] = x[i] - hi[i] rounded likewise; x may be hi (in place).
  * The operand planes of the F32 form of ttb_linear_ex. 16-byte aligned pointers. */
 int ttb_split_tf32(ttb_ctx* ctx, const float* x, int64_t n, float* hi, float* lo);

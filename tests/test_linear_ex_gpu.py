@@ -174,3 +174,40 @@ def test_linear_ex_rejects_bad_arguments(ctx):
     with pytest.raises(_capi.TTBError):   # fp32 operands, 16-bit output
         ctx.linear_ex(_capi.F32, _capi.F16, a, a, 8, 8, 16, 0, h)
     assert _capi.lib().ttb_linear_ex(ctx.h, None) == _capi.ERR_INVALID
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("M,N,K", [(1024, 768, 768), (4100, 768, 3072), (18424, 768, 768), (2049, 1024, 1024), (1500, 256, 512), (3000, 512, 64),
+                                   (300, 768, 768), (2048, 640, 768)])
+def test_linear_with_layernorm_epilogue(ctx, dt, M, N, K, monkeypatch):
+    """out = LayerNorm(A . W^T + bias + residual): the one-kernel form (row sums exchanged between the CTAs of a row block,
+    switched on for every K here) against the two kernels in sequence and against the numpy restatement; shapes outside
+    its range take the two-kernel route inside the same call (the last two)."""
+    monkeypatch.setenv("TTB_GEMM_LN", "2")
+    r = rng(M + N + K)
+    a = rounded(r.standard_normal((M, K)).astype(np.float32), dt)
+    w = rounded(r.standard_normal((K, N)).astype(np.float32) * 0.05, dt)
+    bias = rounded(r.standard_normal(N).astype(np.float32), dt)
+    res = rounded(r.standard_normal((M, N)).astype(np.float32) * 2.0, dt)
+    gamma = rounded(1.0 + 0.2 * r.standard_normal(N).astype(np.float32), dt)
+    beta = rounded(0.3 * r.standard_normal(N).astype(np.float32), dt)
+    Wp = prepack(ctx, w, dt)
+    A, B, R, G, Be = dev(a, dt), dev(bias, dt), dev(res, dt), dev(gamma, dt), dev(beta, dt)
+    two = torch.empty((M, N), dtype=TORCH_DT[dt], device="cuda")
+    ctx.call("linear", code(dt), A, K, Wp, B, R, N, M, N, K, EPIS["bias_residual"], two, N)
+    summed = two.clone()
+    ctx.call("layernorm", code(dt), two, two, G, Be, M, N, 1e-12)
+    outs = []
+    for _ in range(2):
+        out = torch.full((M + 1, N), float("nan"), dtype=TORCH_DT[dt], device="cuda")
+        ctx.call("linear_layernorm", code(dt), A, K, Wp, B, R, N, G, Be, 1e-12, M, N, K, out, N)
+        outs.append(out)
+    assert ctx.device_status() == _capi.OK
+    assert torch.isnan(outs[0][M]).all()               # nothing written behind the last row
+    assert torch.equal(outs[0][:M], outs[1][:M])       # deterministic
+    ulp = 2.0 ** -10 if dt == "f16" else 2.0 ** -7
+    scale = max(1.0, float(two.float().abs().max().item()))
+    # same rounded sum, same formula, another summation order of the row statistics: a last-place difference at most
+    assert maxdiff(host(outs[0][:M]), host(two)) <= 2 * ulp * scale
+    want = restate.layer_norm(host(summed), gamma, beta, 1e-12)
+    assert maxdiff(host(outs[0][:M]), want) < 4 * ulp * scale

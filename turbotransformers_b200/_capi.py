@@ -76,6 +76,7 @@ SIGNATURES = {
     "ttb_linear": (i32, [p, i32, p, i64, p, p, p, i64, i64, i64, i64, i32, p, i64]),
     "ttb_linear_ex": (i32, [p, C.POINTER(LinearArgs)]),
     "ttb_split_tf32": (i32, [p, p, i64, p, p]),
+    "ttb_linear_layernorm": (i32, [p, i32, p, i64, p, p, p, i64, p, p, f32, i64, i64, i64, p, i64]),
     "ttb_prepack_weight_int8_affine": (i32, [p, i32, p, i32, i64, i64, p, p, p]),
     "ttb_quantize_tensor_affine": (i32, [p, i32, p, i64, i64, p, p]),
     "ttb_linear_int8_affine": (i32, [p, i32, p, p, p, p, p, p, p, i64, i64, i64, i64, i32, p, i64]),

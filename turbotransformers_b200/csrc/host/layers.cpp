@@ -155,6 +155,22 @@ void PackedLinear::Int8(bool is_trans, const int8_t** wq, const float** scale, c
   *scale = cache_->qscale[i].data<float>();
 }
 
+void PackedLinear::ForwardLayerNorm(const Tensor& x, int64_t M, const void* residual, const Tensor& gamma, const Tensor& beta, float eps,
+                                    void* out, bool is_trans, const char* name) const {
+  const int dt = FloatType(x, name);
+  ttb_ctx* c = DeviceContext(x.device_id());
+  const int64_t K = in_dim(is_trans), N = out_dim(is_trans);
+  const bool two_planes = dt == TTB_BF16 && x.lo() && core::PreciseBF16();
+  if (dt == TTB_F32 || use_int8() || bias_.is_null() || two_planes) {  // not the plain 16-bit product: two kernels
+    Forward(x, M, TTB_EPI_BIAS_RESIDUAL, residual, out, is_trans, name);
+    Check(ttb_layernorm(c, dt, out, out, gamma.raw(), beta.raw(), M, N, eps), c, name);
+    return;
+  }
+  SameTypeDevice(x, weight_, name);
+  TT_ENFORCE_EQ(x.shape(-1), K, "%s: input width %lld does not match the weight's %lld", name, (long long)x.shape(-1), (long long)K);
+  Check(ttb_linear_layernorm(c, dt, x.raw(), K, Packed(is_trans), bias_.raw(), residual, N, gamma.raw(), beta.raw(), eps, M, N, K, out, N), c, name);
+}
+
 void PackedLinear::Forward(const Tensor& x, int64_t M, int epilogue, const void* residual, void* out, bool is_trans,
                            const char* name, int64_t ldo, void* out_lo, bool f32_out, Tensor* q8_of_out) const {
   const int dt = FloatType(x, name);
@@ -617,12 +633,11 @@ void MultiHeadedAttention::Finish(const Tensor& context, const Tensor& x, int64_
                                  layernorm_beta_.raw(), T, H, 1e-12f),
           c, "AddBiasLayerNorm");
   } else {
-    dense_.Forward(context, T, TTB_EPI_BIAS_RESIDUAL, x.raw(), output->raw_mut(), is_trans_weight, "gemm5");
     if (dense_.int8_mode() == PackedLinear::kInt8PerRow) {
+      dense_.Forward(context, T, TTB_EPI_BIAS_RESIDUAL, x.raw(), output->raw_mut(), is_trans_weight, "gemm5");
       LayerNormWithInt8(c, output, layernorm_gamma_, layernorm_beta_, T, H, 1e-12f, "AddBiasLayerNorm");
-    } else {
-      Check(ttb_layernorm(c, dt, output->raw(), output->raw_mut(), layernorm_gamma_.raw(), layernorm_beta_.raw(), T, H, 1e-12f), c,
-            "AddBiasLayerNorm");
+    } else {  // one kernel where the shape allows it: projection + bias + residual + layer norm
+      dense_.ForwardLayerNorm(context, T, x.raw(), layernorm_gamma_, layernorm_beta_, 1e-12f, output->raw_mut(), is_trans_weight, "gemm5");
     }
   }
 }
@@ -801,13 +816,12 @@ void BertOutput::operator()(const Tensor& hidden_states, const Tensor& input_ten
     dense_.Forward(hidden_states, M, TTB_EPI_BIAS_RESIDUAL, input_tensor.f32()->raw(), s, false, "BertOutput/MatMul", 0, nullptr, true);
     LayerNormPlanes(c, true, s, output_tensor, layer_norm_weight_, layer_norm_bias_, M, N, 1e-12f, true, "BertOutput/AddBiasLayerNorm");
   } else {
-    dense_.Forward(hidden_states, M, TTB_EPI_BIAS_RESIDUAL, input_tensor.raw(), output_tensor->raw_mut(), false, "BertOutput/MatMul");
     if (dense_.int8_mode() == PackedLinear::kInt8PerRow) {
+      dense_.Forward(hidden_states, M, TTB_EPI_BIAS_RESIDUAL, input_tensor.raw(), output_tensor->raw_mut(), false, "BertOutput/MatMul");
       LayerNormWithInt8(c, output_tensor, layer_norm_weight_, layer_norm_bias_, M, N, 1e-12f, "BertOutput/AddBiasLayerNorm");
     } else {
-      Check(ttb_layernorm(c, dt, output_tensor->raw(), output_tensor->raw_mut(), layer_norm_weight_.raw(), layer_norm_bias_.raw(), M, N,
-                          1e-12f),
-            c, "BertOutput/AddBiasLayerNorm");
+      dense_.ForwardLayerNorm(hidden_states, M, input_tensor.raw(), layer_norm_weight_, layer_norm_bias_, 1e-12f, output_tensor->raw_mut(), false,
+                              "BertOutput/MatMul");
     }
   }
 }
@@ -831,8 +845,7 @@ void ProjectAddNorm(const PackedLinear& dense, const Tensor& act_in, const Tenso
     dense.Forward(act_in, M, TTB_EPI_BIAS_RESIDUAL, residual.f32()->raw(), s, is_trans, name, 0, nullptr, true);
     LayerNormPlanes(c, true, s, out, gamma, beta, M, N, 1e-12f, true, name);
   } else {
-    dense.Forward(act_in, M, TTB_EPI_BIAS_RESIDUAL, residual.raw(), out->raw_mut(), is_trans, name);
-    Check(ttb_layernorm(c, dt, out->raw(), out->raw_mut(), gamma.raw(), beta.raw(), M, N, 1e-12f), c, name);
+    dense.ForwardLayerNorm(act_in, M, residual.raw(), gamma, beta, 1e-12f, out->raw_mut(), is_trans, name);
   }
 }
 }  // namespace

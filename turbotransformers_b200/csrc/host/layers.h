@@ -51,6 +51,10 @@ class PackedLinear {
   // `ldo` (elements between output rows) defaults to N. A bf16 x that carries a lo plane is used at full precision
   // (two passes). out_lo (bf16 only) receives the second plane of the output. f32_out: `out` and `residual` are fp32
   // (the residual stream of a bf16 model in its precise mode).
+  // out = LayerNorm(x . W + bias + residual) * gamma + beta: one kernel for the plain 16-bit product where the shape allows
+  // it, else Forward with the residual epilogue followed by the layer norm kernel.
+  void ForwardLayerNorm(const core::Tensor& x, int64_t M, const void* residual, const core::Tensor& gamma, const core::Tensor& beta, float eps,
+                        void* out, bool is_trans, const char* name) const;
   // q8_of_out (per-row int8 mode): the tensor that owns `out`; it gets the int8 form of the output attached (q8(), q8_scale()).
   void Forward(const core::Tensor& x, int64_t M, int epilogue, const void* residual, void* out, bool is_trans,
                const char* name, int64_t ldo = 0, void* out_lo = nullptr, bool f32_out = false, core::Tensor* q8_of_out = nullptr) const;

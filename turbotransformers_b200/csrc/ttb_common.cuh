@@ -39,6 +39,10 @@ struct ttb_ctx {
   bool arena_active = false;
   std::vector<std::pair<char*, size_t>> arenas;  // every reserved buffer not yet released (the active one included)
   uint64_t bytes_allocated_total = 0;  // sum of all ttb_alloc sizes so far
+  // workspace of the GEMM kernels whose epilogue is a LayerNorm: per-row partial sums and per-row-block counters. Owned by
+  // the context (not the pool): the counters must be zero between launches, which the kernels themselves see to.
+  void* ln_ws = nullptr;
+  size_t ln_ws_rows = 0;  // rows the workspace is sized for
 };
 
 namespace ttb {

@@ -47,6 +47,7 @@ extern "C" int ttb_ctx_destroy(ttb_ctx* c) {
   for (auto& kv : c->live) cudaFreeAsync(kv.first, c->stream);
   cudaStreamSynchronize(c->stream);
   for (auto& a : c->arenas) cudaFree(a.first);
+  if (c->ln_ws) cudaFree(c->ln_ws);
   if (c->d_status) cudaFree(c->d_status);
   if (c->h_status) cudaFreeHost(c->h_status);
   if (c->owns_pool && c->pool) cudaMemPoolDestroy(c->pool);

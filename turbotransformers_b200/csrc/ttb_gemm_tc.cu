@@ -45,6 +45,7 @@ constexpr int kMaxSplit = 4;     // CTAs of a cluster that may share one tile's 
 // TWO = a pair of CTAs (one cluster of two SMs) computes a 256 x BN tile with cta_group::2 MMAs: each CTA stages its
 // own 128 rows of A and its own half (BN/2 rows) of W, so a k-block costs 32 KB of L2->SM traffic per CTA instead of 48.
 // SK = split-K over a cluster (BN = 32 only): a shorter ring, plus room for the partial tiles of the other CTAs.
+constexpr int kLnMaxTiles = 4;  // kernels with the LayerNorm epilogue: N-tiles of 256 per row, N <= 1024
 template <int BN, bool TWO = false, bool SK = false> struct Cfg {
   static constexpr int A_BYTES = BM * BK_BYTES;
   static constexpr int B_BYTES = (TWO ? BN / 2 : BN) * BK_BYTES;
@@ -73,6 +74,12 @@ struct GemmParams {
   const float* act_qparams;  // int8, affine per tensor: device [scale, zero point]; null selects the symmetric form
   const int* col_sum;        // int8, affine: sum over k of Wq[n, k]
   float* row_absmax;         // int8 kind, or null: [M], receives max |out[m, :]| as stored (atomic maximum; zero before the launch)
+  const void* ln_gamma;      // LN kernels: OutT[N], OutT[N], eps
+  const void* ln_beta;
+  float ln_eps;
+  float2* ln_partials;       // LN kernels: [2 * N / 256 slots][ln_rows] {sum, sum of squares} of a row over 128 columns
+  int* ln_counters;          // LN kernels: per 128-row block {warps that have published, warps that have read}; all zero between launches
+  long long ln_rows;         // rows of the partials array (M rounded up to whole tiles)
   int epilogue;
   int tma_store;           // 1: the output tile goes through shared memory and TMA stores (needs aligned, 16-byte-multiple rows)
   int split_k;             // CTAs per cluster sharing one tile (SK kernels), else 1
@@ -158,13 +165,14 @@ template <typename OutT> __device__ __forceinline__ void load32(const OutT* p, f
 //   VAR_PLAIN, VAR_TWO_PLANES (16-bit output written as hi + lo planes), VAR_AFFINE (int8 with a per-tensor zero point)
 enum { VAR_PLAIN = 0, VAR_TWO_PLANES = 1, VAR_AFFINE = 2 };
 
-template <int BN, int KIND, typename OutT, bool TWO, bool SK, int VAR>
+template <int BN, int KIND, typename OutT, bool TWO, bool SK, int VAR, bool LN = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
                const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmO2, const GemmParams p) {
   using C = Cfg<BN, TWO, SK>;
   static_assert(!SK || (BN == 32 && !TWO), "split-K runs on single-CTA 128 x 32 tiles");
+  static_assert(!LN || (BN == 256 && !SK && VAR == VAR_PLAIN && sizeof(OutT) == 2), "the LayerNorm epilogue: 16-bit 256-column tiles");
   constexpr int IN_BYTES = (KIND == KIND_I8) ? 1 : (KIND == KIND_TF32 ? 4 : 2);
   constexpr int BK_ELEMS = BK_BYTES / IN_BYTES;
   constexpr uint32_t IDESC = make_idesc<KIND, BN, TWO>();
@@ -376,6 +384,142 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
       if (KIND != KIND_I8) return __uint_as_float(word);
       return (float)((int)word - zero_point * colsum) * rs;
     };
+    if constexpr (LN) {
+      // ---- bias + residual + LayerNorm. A warp owns 32 rows x 128 columns of the tile (two staged chunks). Pass 1 builds
+      // the values (accumulator + bias + residual, rounded to OutT as the separate kernels would store them), keeps them
+      // packed in registers, hands the accumulator back and publishes the rows' partial sums; pass 2 normalises with the
+      // sums of the whole row and stores through the staging tile and TMA. The N-tiles of a row block are consecutive
+      // tiles, so the CTAs that hold them work on them at the same time (the grid is persistent and wholly resident);
+      // they meet through global memory: partial sums, then a counter per 128-row block that every warp raises after
+      // publishing and waits on (bounded) before reading. A second counter tells the last reader to reset both.
+      const OutT* gamma = static_cast<const OutT*>(p.ln_gamma);
+      const OutT* beta = static_cast<const OutT*>(p.ln_beta);
+      const int warps_per_block = num_n * 8;
+      const float inv_n = 1.0f / (float)p.N;
+      for (int tile = tile0; tile < num_tiles; tile += tile_step, ++acc_iter) {
+        const int m_blk = tile / num_n, n_blk = tile % num_n;
+        const int acc = acc_iter & 1;
+        const uint32_t acc_phase = (uint32_t)(acc_iter >> 1) & 1u;
+        const int row_block = m_blk * (TILE_M / BM) + (int)(TWO ? rank : 0u);  // which 128 rows of the matrix this CTA holds
+        const int row_base = row_block * BM + quad * 32;
+        const int c_beg = half * 2;
+        uint4 res[8];
+        load_residual(res, row_base, n_blk * BN + c_beg * CH);  // before the wait
+        if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) break;
+        tc_fence_after();
+        prefetch_residual(tile + tile_step);
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
+        uint4 vp[2][2][4];  // [chunk][32-column half][16-byte group]: the values, packed
+        float sum = 0.f, sq = 0.f;
+#pragma unroll
+        for (int ci = 0; ci < 2; ++ci) {
+          const int cc = c_beg + ci;
+          const int col0 = n_blk * BN + cc * CH;
+          if (lane == 0) bulk_wait_read<0>();  // the staging tile may still be read by the previous tile's last store
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = i * 4 + (lane >> 3), ch = lane & 7;
+            *reinterpret_cast<uint4*>(buf + r * 128 + ((ch ^ (r & 7)) << 4)) = res[i];
+          }
+          __syncwarp();
+          if (ci == 0) load_residual(res, row_base, col0 + CH);  // the second chunk's rows travel during the first
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const int colh = col0 + hh * 32;
+            uint4 bq[4];
+#pragma unroll
+            for (int g = 0; g < 4; ++g) bq[g] = __ldg(reinterpret_cast<const uint4*>(bias + colh + g * 8));
+            uint32_t r0[32];
+            tmem_ld32_issue(taddr + (uint32_t)(cc * CH + hh * 32), r0);
+            tmem_ld_wait();
+            if (ci == 1 && hh == 1) {  // this warp's share of the accumulator is in registers: hand it back now
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) release_accumulator(acc);
+            }
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              float bb[8], q[8], v[8];
+              unpack16<OutT>(bq[g], bb);
+              unpack16<OutT>(*reinterpret_cast<const uint4*>(buf + lane * 128 + (((hh * 4 + g) ^ (lane & 7)) << 4)), q);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r0[g * 8 + j]) + bb[j] + q[j];
+              vp[ci][hh][g] = pack16<OutT>(v);
+              unpack16<OutT>(vp[ci][hh][g], v);  // the statistics are those of the rounded values
+#pragma unroll
+              for (int j = 0; j < 8; ++j) { sum += v[j]; sq = fmaf(v[j], v[j], sq); }
+            }
+          }
+          __syncwarp();  // every lane has read its residual row out of the staging tile before it is written again
+        }
+        {
+          const long long prow = (long long)row_base + lane;
+          p.ln_partials[(long long)(n_blk * 2 + half) * p.ln_rows + prow] = make_float2(sum, sq);
+          __syncwarp();
+          int* counters = p.ln_counters + 2 * row_block;
+          bool arrived = true;
+          if (lane == 0) {
+            __threadfence();
+            atomicAdd(counters, 1);
+            const long long t0 = clock64();
+            while (ld_acquire_gpu(counters) < warps_per_block) {
+              if (*abort_flag || clock64() - t0 > kWaitCycles) {
+                *abort_flag = 1;
+                arrived = false;
+                break;
+              }
+              __nanosleep(40);
+            }
+          }
+          if (!__all_sync(0xffffffffu, arrived)) break;
+          float tsum = 0.f, tsq = 0.f;
+          for (int sl = 0; sl < 2 * num_n; ++sl) {
+            const float2 part = __ldcg(p.ln_partials + (long long)sl * p.ln_rows + prow);
+            tsum += part.x;
+            tsq += part.y;
+          }
+          sum = tsum;
+          sq = tsq;
+          __syncwarp();
+          if (lane == 0 && atomicAdd(counters + 1, 1) == warps_per_block - 1) {  // the last reader leaves the block's counters at zero
+            counters[0] = 0;
+            counters[1] = 0;
+          }
+        }
+        const float mean = sum * inv_n;
+        const float rstd = rsqrtf(fmaxf(sq * inv_n - mean * mean, 0.f) + p.ln_eps);
+        const float shift = -mean * rstd;
+#pragma unroll
+        for (int ci = 0; ci < 2; ++ci) {
+          const int col0 = n_blk * BN + (c_beg + ci) * CH;
+          if (lane == 0) bulk_wait_read<0>();
+          __syncwarp();
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int col = col0 + hh * 32 + g * 8;
+              float v[8], gg[8], bb[8];
+              unpack16<OutT>(vp[ci][hh][g], v);
+              unpack16<OutT>(__ldg(reinterpret_cast<const uint4*>(gamma + col)), gg);
+              unpack16<OutT>(__ldg(reinterpret_cast<const uint4*>(beta + col)), bb);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = fmaf(fmaf(v[j], rstd, shift), gg[j], bb[j]);
+              *reinterpret_cast<uint4*>(buf + lane * 128 + (((hh * 4 + g) ^ (lane & 7)) << 4)) = pack16<OutT>(v);
+            }
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmO, smem_u32(buf), col0, row_base);
+            bulk_commit();
+          }
+        }
+      }
+      if (lane == 0) bulk_wait<0>();
+      __syncwarp();
+    } else {
     for (int tile = tile0; tile < num_tiles; tile += tile_step, ++acc_iter) {
       const int m_blk = tile / num_n, n_blk = tile % num_n;
       const int acc = acc_iter & 1;
@@ -621,6 +765,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
     // every TMA store issued by this warp must be complete before its shared memory goes away
     if (use_tma && lane == 0) bulk_wait<0>();
     __syncwarp();
+    }
   }
 
   // ------------------------------------------------------------------ teardown (all roles reach this)
@@ -773,6 +918,105 @@ int launch_tc(ttb_ctx* ctx, const Operands& op, const GemmParams& p) {
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA0, tmA1, tmB0, tmB1, tmO, tmO2, q);
   if (e != cudaSuccess) return fail(ctx, TTB_ERR_CUDA, "cluster launch of gemm_tc failed: %s", cudaGetErrorString(e));
   return launched(ctx, SK ? "gemm_tc_splitk" : "gemm_tc_pair");
+}
+
+// The GEMM whose epilogue is bias + residual + LayerNorm (N a multiple of 256, at most 1024), on the same persistent tile
+// schedule as the plain kernels. Returns TTB_ERR_UNSUPPORTED (nothing launched) when its workspace cannot be had right now
+// (it would have to grow while the stream is being captured); the caller then runs the product and the LayerNorm as two
+// kernels.
+constexpr size_t ln_ws_bytes(size_t rows) { return 2 * kLnMaxTiles * rows * sizeof(float2) + (rows / BM) * 2 * sizeof(int); }
+
+int ensure_ln_workspace(ttb_ctx* ctx, size_t rows) {
+  if (ctx->ln_ws && ctx->ln_ws_rows >= rows) return TTB_OK;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(ctx->stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();
+    return TTB_ERR_UNSUPPORTED;
+  }
+  size_t want = ctx->ln_ws_rows ? ctx->ln_ws_rows : 32768;
+  while (want < rows) want *= 2;
+  TTB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // nothing may still be using the old one
+  if (ctx->ln_ws) cudaFree(ctx->ln_ws);
+  ctx->ln_ws = nullptr;
+  ctx->ln_ws_rows = 0;
+  void* ws = nullptr;
+  TTB_CUDA(ctx, cudaMalloc(&ws, ln_ws_bytes(want)));
+  TTB_CUDA(ctx, cudaMemset(ws, 0, ln_ws_bytes(want)));
+  ctx->ln_ws = ws;
+  ctx->ln_ws_rows = want;
+  return TTB_OK;
+}
+
+template <int KIND, typename OutT, bool TWO>
+int launch_tc_ln(ttb_ctx* ctx, const Operands& op, const GemmParams& p) {
+  using C = Cfg<256, TWO, false>;
+  constexpr int BN = 256;
+  constexpr int TILE_M = TWO ? 2 * BM : BM;
+  const int64_t num_m = (p.M + TILE_M - 1) / TILE_M;
+  const int num_n = p.N / BN;
+  const size_t rows = (size_t)num_m * TILE_M;
+  int s = ensure_ln_workspace(ctx, rows);
+  if (s) return s;
+  CUtensorMap tmA0, tmB0, tmO;
+  if ((s = make_map(ctx, &tmA0, KIND, op.A, p.M, p.K, op.lda, BM))) return s;
+  if ((s = make_map(ctx, &tmB0, KIND, op.W, p.N, p.K, p.K, TWO ? BN / 2 : BN))) return s;
+  if ((s = make_map(ctx, &tmO, out_kind<OutT>(), p.out, p.M, p.N, p.ldo, 32))) return s;
+  GemmParams q = p;
+  q.tma_store = 1;
+  q.ln_partials = static_cast<float2*>(ctx->ln_ws);
+  q.ln_rows = (long long)ctx->ln_ws_rows;
+  q.ln_counters = reinterpret_cast<int*>(static_cast<char*>(ctx->ln_ws) + 2 * kLnMaxTiles * ctx->ln_ws_rows * sizeof(float2));
+  auto kern = gemm_tc_kernel<256, KIND, OutT, TWO, false, VAR_PLAIN, true>;
+  static int resident[64] = {};  // per instantiation and device: CTAs (single) or CTA pairs (TWO) the device holds at once
+  const int dev = ctx->device < 64 ? ctx->device : 63;
+  if (ctx->device >= 64 || resident[dev] == 0) {
+    TTB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    int n = ctx->sm_count;
+    if (TWO) {
+      cudaLaunchConfig_t probe = {};
+      probe.gridDim = dim3(2 * (unsigned)ctx->sm_count);
+      probe.blockDim = dim3(kThreads);
+      probe.dynamicSmemBytes = C::SMEM_BYTES;
+      cudaLaunchAttribute pa[1];
+      pa[0].id = cudaLaunchAttributeClusterDimension;
+      pa[0].val.clusterDim.x = 2;
+      pa[0].val.clusterDim.y = 1;
+      pa[0].val.clusterDim.z = 1;
+      probe.attrs = pa;
+      probe.numAttrs = 1;
+      TTB_CUDA(ctx, cudaOccupancyMaxActiveClusters(&n, kern, &probe));
+    }
+    resident[dev] = n > 0 ? n : 1;
+  }
+  // Every CTA must be resident: the CTAs that hold one row block wait for one another. Whole row blocks per round also keep
+  // the N-tiles of a block in the same round.
+  const int64_t num_tiles = num_m * num_n;
+  int64_t units = num_tiles < resident[dev] ? num_tiles : (resident[dev] / num_n) * num_n;
+  if (units < num_n) return TTB_ERR_UNSUPPORTED;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(units * (TWO ? 2 : 1)));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (TWO) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 2;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  if (pdl_enabled()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA0, tmA0, tmB0, tmB0, tmO, tmO, q);
+  if (e != cudaSuccess) return fail(ctx, TTB_ERR_CUDA, "launch of gemm_tc (LayerNorm epilogue) failed: %s", cudaGetErrorString(e));
+  return launched(ctx, "gemm_tc_layernorm");
 }
 
 // TTB_GEMM_PAIR: 0 disables the two-CTA variant, 2 uses it for every shape with at least half a wave of pair tiles
@@ -1069,6 +1313,59 @@ extern "C" int ttb_linear(ttb_ctx* ctx, int dtype, const void* A, int64_t lda, c
   a.M = M; a.N = N; a.K = K; a.epilogue = epilogue;
   a.out = out; a.ldo = ldo;
   return ttb_linear_ex(ctx, &a);
+}
+
+extern "C" int ttb_layernorm(ttb_ctx* ctx, int dtype, const void* in, void* out, const void* gamma, const void* beta, int64_t M, int64_t N,
+                             float eps);
+
+// TTB_GEMM_LN (read at every call): unset or 0 = the product and the LayerNorm run as two kernels; 1 = one kernel for Linears
+// with a long mainloop (K >= 2048); 2 = one kernel whenever the shape allows. Off by default: the one-kernel form makes the
+// CTAs that hold one row block wait for one another through global memory, which needs the whole grid resident at once.
+// That holds for one context on a device, but two contexts running such kernels on one device at the same time could
+// each hold SMs the other is waiting for (the waits are bounded: the calls would end with TTB_ERR_DEVICE_WAIT), and the
+// measured gain is under one per cent of the benchmark step.
+static int fused_ln_mode() {
+  const char* e = getenv("TTB_GEMM_LN");
+  return (e && e[0] >= '1' && e[0] <= '2') ? e[0] - '0' : 0;
+}
+
+extern "C" int ttb_linear_layernorm(ttb_ctx* ctx, int dtype, const void* A, int64_t lda, const void* Wp, const void* bias,
+                                    const void* residual, int64_t ldr, const void* gamma, const void* beta, float eps, int64_t M, int64_t N,
+                                    int64_t K, void* out, int64_t ldo) {
+  if (!ctx) return TTB_ERR_INVALID;
+  TTB_REQUIRE(ctx, dtype == TTB_F16 || dtype == TTB_BF16, "linear_layernorm: dtype must be F16 or BF16");
+  int s = check_linear(ctx, "linear_layernorm", A, Wp, bias, residual, M, N, K, TTB_EPI_BIAS_RESIDUAL, out, ldo, 8);
+  if (s || M == 0) return s;
+  TTB_REQUIRE(ctx, gamma && beta, "linear_layernorm: null LayerNorm parameters");
+  TTB_REQUIRE(ctx, ldo == N, "linear_layernorm: the output rows must be dense (ldo == N)");
+  TTB_REQUIRE(ctx, lda >= K && lda % 8 == 0, "linear_layernorm: lda must be >= K and a multiple of 8");
+  const bool aligned = ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(Wp) | reinterpret_cast<uintptr_t>(bias) |
+                         reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(gamma) | reinterpret_cast<uintptr_t>(beta) |
+                         reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  // Below about a thousand rows the narrow-tile (and split-K) kernels plus the one-round-trip LayerNorm are faster than
+  // N / 256 CTAs walking the whole K range.
+  // and with a short mainloop (K < 2048) the kernel runs at the speed of its epilogue, which the exchange of row sums
+  // lengthens by more than the separate LayerNorm costs (measured at M = 18424, N = 768: K = 768 40.2 us in one kernel
+  // against 25.6 + 12.5; K = 3072 72.1 against 67.6 + 12.5).
+  const int mode = fused_ln_mode();
+  if (mode && aligned && N % 256 == 0 && N / 256 <= kLnMaxTiles && M >= 1024 && (K >= 2048 || mode == 2) && ldr % 8 == 0 && M < (1ll << 31) &&
+      K < (1ll << 31)) {
+    DeviceGuard g(ctx->device);
+    GemmParams p{};
+    p.M = (int)M; p.N = (int)N; p.K = (int)K; p.npass = 1;
+    p.out = out; p.ldo = ldo; p.bias = bias; p.residual = residual; p.ldr = ldr;
+    p.epilogue = TTB_EPI_BIAS_RESIDUAL; p.split_k = 1; p.status = ctx->d_status;
+    p.ln_gamma = gamma; p.ln_beta = beta; p.ln_eps = eps;
+    const Operands op{A, nullptr, lda, Wp, nullptr};
+    // CTA pairs where the plain kernel would use them too: a long mainloop (see pick_tile)
+    const bool pair = pair_mode() && K * 2 >= 4096 && ((M + 2 * BM - 1) / (2 * BM)) * (N / 256) >= ctx->sm_count / 2;
+    if (dtype == TTB_F16) s = pair ? launch_tc_ln<KIND_F16, __half, true>(ctx, op, p) : launch_tc_ln<KIND_F16, __half, false>(ctx, op, p);
+    else s = pair ? launch_tc_ln<KIND_BF16, __nv_bfloat16, true>(ctx, op, p) : launch_tc_ln<KIND_BF16, __nv_bfloat16, false>(ctx, op, p);
+    if (s != TTB_ERR_UNSUPPORTED) return s;
+  }
+  s = ttb_linear(ctx, dtype, A, lda, Wp, bias, residual, ldr, M, N, K, TTB_EPI_BIAS_RESIDUAL, out, ldo);
+  if (s) return s;
+  return ttb_layernorm(ctx, dtype, out, out, gamma, beta, M, N, eps);
 }
 
 extern "C" int ttb_linear_int8(ttb_ctx* ctx, int out_dtype, const int8_t* Aq, const float* row_scale, const int8_t* Wq,

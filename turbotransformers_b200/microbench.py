@@ -111,6 +111,7 @@ def main():
     ap.add_argument("--graph", action="store_true", help="with --burst: replay the launches from a CUDA graph (no host time in the number)")
     ap.add_argument("--b-trans", action="store_true", help="matmul: B is stored [N, K]")
     ap.add_argument("--yardstick", action="store_true", help="matmul: also time torch.matmul (cuBLAS SGEMM, TF32 off) on the same operands")
+    ap.add_argument("--fuse-ln", action="store_true", help="linear: ttb_linear_layernorm (bias + residual + LayerNorm); one kernel only with TTB_GEMM_LN=1 or 2 in the environment")
     ap.add_argument("--plain", action="store_true", help="layernorm: the in-place LayerNorm the encoder layers run (no residual / bias add)")
     ap.add_argument("--pad-rows", action="store_true", help="linear: output rows padded to a multiple of 8 elements, padding declared scratch")
     a = ap.parse_args()
@@ -137,11 +138,17 @@ def main():
             if a.epilogue != "bias_residual":
                 r = None
             fn = lambda: ctx.call("linear", ocode, x, K, w, b, r, N if r is not None else 0, M, N, K, EPI[a.epilogue] | flag, o, ldo)
+            if a.fuse_ln:
+                gam, bet = torch.ones(N, device="cuda", dtype=odt), torch.zeros(N, device="cuda", dtype=odt)
+                b, r = torch.randn(N, device="cuda", dtype=odt), torch.randn(M, N, device="cuda", dtype=odt)
+                fn = lambda: ctx.call("linear_layernorm", ocode, x, K, w, b, r, N, gam, bet, 1e-12, M, N, K, o, N)
         if a.burst:
             def make():
                 xx, oo = torch.randn_like(x) if a.dtype != "i8" else x.clone(), torch.empty_like(o)
                 if a.dtype == "i8":
                     return lambda: ctx.call("linear_int8", ocode, xx, xs, w, ws, b, r, N, M, N, K, EPI[a.epilogue], oo, N)
+                if a.fuse_ln:
+                    return lambda: ctx.call("linear_layernorm", ocode, xx, K, w, b, r, N, gam, bet, 1e-12, M, N, K, oo, N)
                 return lambda: ctx.call("linear", ocode, xx, K, w, b, r, N if r is not None else 0, M, N, K, EPI[a.epilogue] | flag, oo, ldo)
             fns = [make() for _ in range(a.burst)]
             mean, med, best = timed_graph(ctx, fns, a.warmup, a.iters) if a.graph else timed_burst(fns, a.warmup, a.iters)
