@@ -26,7 +26,10 @@
 //                 (row sum above 2^15), which real score distributions do not reach. The final division by the running
 //                 sum makes the result independent of the reference maximum.
 // TMEM (all 512 columns): S0 | S1 (128 each) | O0 | O1 (64 each) | P0 | P1 (64 each).
-// Items are ordered longest sequence first and dealt round-robin to the streams, so the streams finish together.
+// Items are ordered longest sequence first; a stream's first item is fixed, every further one is the next item nobody has
+// taken (a counter in global memory, fetched one item ahead by the stream's loader), so the streams finish together even
+// when their items differ in length or their SMs in speed (with a fixed round-robin deal the slowest CTA of the ragged
+// benchmark batch finished 10.5 us after the median one, of 77).
 // Every wait is bounded; on expiry the CTA raises a flag, frees its TMEM and the host sees TTB_ERR_DEVICE_WAIT.
 #include <algorithm>
 #include <cstdlib>
@@ -52,7 +55,8 @@ constexpr int SMEM_PREFIX = SMEM_CU + (kMaxB + 1) * 4;     // int[kMaxB + 1] ite
 constexpr int SMEM_ORDER = SMEM_PREFIX + (kMaxB + 1) * 4;  // uint16[kMaxB] sequence at each rank
 constexpr int SMEM_BARS = (SMEM_ORDER + kMaxB * 2 + 63) / 64 * 64;
 constexpr int kBarsPerStream = 16;
-constexpr int SMEM_BYTES = SMEM_BARS + 2 * kBarsPerStream * 8 + 64;
+constexpr int kRing = 8;  // item ids a stream's loader has published and the other roles may still read
+constexpr int SMEM_BYTES = SMEM_BARS + 2 * kBarsPerStream * 8 + 128;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRowSumLimit = 32768.0f;  // a tile row sum below this keeps every probability inside fp16 / bf16 range
@@ -63,6 +67,7 @@ struct Params {
   int batch, heads, causal;
   float scale;
   int* status;
+  int* sched;  // [0] items handed out beyond every stream's first, [1] CTAs that have finished; both zero between launches
 };
 
 struct Item {
@@ -147,6 +152,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
   auto o_done = [&](int s) { return bar(s, 15); };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kBarsPerStream);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // Work distribution: a stream's first item is fixed (2 * blockIdx.x + stream); every further one is the next item nobody
+  // has taken yet, fetched by the stream's loader from a counter in global memory and published here for the stream's
+  // other roles. Items are ranked longest first, so whichever stream is free takes the longest remaining one.
+  volatile int* s_produced = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [2]: items published so far
+  volatile int* s_ring = reinterpret_cast<volatile int*>(tmem_slot + 4);      // [2][kRing]: their ids (n_items = no more work)
   auto smem_q = [&](int s, int b) { return base + (uint32_t)(s * SMEM_STREAM + b * TILE_BYTES); };
   auto smem_k = [&](int s, int st) { return base + (uint32_t)(s * SMEM_STREAM + (2 + st) * TILE_BYTES); };
   auto smem_v = [&](int s, int st) { return base + (uint32_t)(s * SMEM_STREAM + (4 + st) * TILE_BYTES); };
@@ -163,6 +173,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
       mbar_init(o_done(s), 1);
     }
     *abort_flag = 0;
+    s_produced[0] = 0;
+    s_produced[1] = 0;
     mbar_init_fence();
   }
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
@@ -209,7 +221,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const int n_items = s_prefix[p.batch] * p.heads;
-  const int stride = 2 * (int)gridDim.x;  // a stream's items: 2 * blockIdx.x + stream, then every `stride`-th
+  // the id of a stream's nq-th item, once its loader has published it (bounded wait; n_items when giving up)
+  auto item_at = [&](int s, uint32_t nq) -> int {
+    if (s_produced[s] <= (int)nq) {
+      const long long t0 = clock64();
+      while (s_produced[s] <= (int)nq) {
+        if (*abort_flag || clock64() - t0 > kWaitCycles) {
+          *abort_flag = 1;
+          return n_items;
+        }
+      }
+    }
+    return s_ring[s * kRing + (int)(nq & (kRing - 1))];
+  };
   auto tmem_s = [&](int s) { return tmem + (uint32_t)(s * 128); };
   auto tmem_o = [&](int s) { return tmem + (uint32_t)(256 + s * 64); };
   auto tmem_p = [&](int s) { return tmem + (uint32_t)(384 + s * 64); };
@@ -229,6 +253,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
           uint32_t g, nq;
           Item it;
         } kc, vc;
+        int produced = 0, last_id = 0;
+        auto produce = [&]() {  // publishes the id of the stream's next item
+          int id = n_items;
+          if (produced == 0) id = min(2 * (int)blockIdx.x + s, n_items);
+          else if (last_id < n_items) id = min(2 * (int)gridDim.x + atomicAdd(p.sched, 1), n_items);
+          last_id = id;
+          s_ring[s * kRing + (produced & (kRing - 1))] = id;
+          __threadfence_block();
+          s_produced[s] = ++produced;
+        };
+        produce();
+        produce();  // one item ahead of the cursors, so that the counter's round trip is off their path
         kc.i = 2 * (int)blockIdx.x + s;
         kc.j = 0;
         kc.g = 0;
@@ -244,8 +280,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
           ++c.g;
           if (++c.j == c.n) {
             c.j = 0;
-            c.i += stride;
             ++c.nq;
+            if ((int)c.nq + 1 >= produced) produce();  // the key cursor leads: it finds item nq published and publishes nq + 1
+            c.i = s_ring[s * kRing + (int)(c.nq & (kRing - 1))];
             if (c.i < n_items) {
               c.it = decode_item(c.i, p, s_cu, s_prefix, s_order);
               c.n = c.it.n;
@@ -313,8 +350,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
           ++c.g;
           if (++c.j == c.n) {
             c.j = 0;
-            c.i += stride;
             ++c.nq;
+            c.i = item_at(s, c.nq);
             c.n = (c.i < n_items) ? decode_item(c.i, p, s_cu, s_prefix, s_order).n : 0;
           }
         };
@@ -411,7 +448,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
       return true;
     };
 
-    for (int i = 2 * (int)blockIdx.x + s; i < n_items && ok; i += stride, ++nq) {
+    for (int i = 2 * (int)blockIdx.x + s; i < n_items && ok; ++nq, i = item_at(s, nq)) {
       const Item it = decode_item(i, p, s_cu, s_prefix, s_order);
       const int qrow = it.q0 + row;  // row within the sequence
       float m_used = -INFINITY, l_run = 0.f;
@@ -525,6 +562,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
     tmem_dealloc(tmem, TMEM_COLS);
   }
   if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, (int)TTB_ERR_DEVICE_WAIT);
+  if (threadIdx.x == 0) {  // the last CTA to finish leaves the work counters at zero for the next launch
+    __threadfence();
+    if (atomicAdd(p.sched + 1, 1) == (int)gridDim.x - 1) {
+      p.sched[0] = 0;
+      p.sched[1] = 0;
+    }
+  }
 }
 
 }  // namespace
@@ -550,7 +594,7 @@ int attention_tc_launch(ttb_ctx* ctx, int dtype, const void* qkv, int64_t tokens
   CUtensorMap tm;
   if (!encode_tile_map(&tm, qkv, 2, dtype == TTB_BF16, (uint64_t)tokens, (uint64_t)(3 * H), (uint64_t)(3 * H), 128))
     return TTB_ERR_UNSUPPORTED;
-  Params p{out, cu, (int)B, (int)heads, causal ? 1 : 0, scale, ctx->d_status};
+  Params p{out, cu, (int)B, (int)heads, causal ? 1 : 0, scale, ctx->d_status, ctx->d_status + 1};
   // upper bound of the item count from what the host knows; a CTA runs two streams, idle CTAs leave after the tables
   const int64_t tiles_bound = std::min<int64_t>(tokens / QT + B, B * ((max_seqlen + QT - 1) / QT));
   const int64_t items_bound = std::max<int64_t>(1, tiles_bound * heads);

@@ -31,8 +31,9 @@ extern "C" int ttb_ctx_create(int device, void* cuda_stream, ttb_ctx** out) {
   c->owns_pool = true;
   uint64_t keep = UINT64_MAX;  // freed blocks stay cached in the pool: steady state makes no driver calls
   cudaMemPoolSetAttribute(c->pool, cudaMemPoolAttrReleaseThreshold, &keep);
-  if ((e = cudaMalloc(&c->d_status, sizeof(int))) != cudaSuccess) return bail("status word", e);
-  if ((e = cudaMemset(c->d_status, 0, sizeof(int))) != cudaSuccess) return bail("status memset", e);
+  // [0] the status word; [1], [2] the work counters of the attention kernel (zero between launches)
+  if ((e = cudaMalloc(&c->d_status, 4 * sizeof(int))) != cudaSuccess) return bail("status word", e);
+  if ((e = cudaMemset(c->d_status, 0, 4 * sizeof(int))) != cudaSuccess) return bail("status memset", e);
   if ((e = cudaMallocHost(&c->h_status, sizeof(int))) != cudaSuccess) return bail("pinned status", e);
   *c->h_status = 0;
   cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, device);
