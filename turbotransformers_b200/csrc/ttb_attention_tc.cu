@@ -56,7 +56,8 @@ constexpr int SMEM_ORDER = SMEM_PREFIX + (kMaxB + 1) * 4;  // uint16[kMaxB] sequ
 constexpr int SMEM_BARS = (SMEM_ORDER + kMaxB * 2 + 63) / 64 * 64;
 constexpr int kBarsPerStream = 16;
 constexpr int kRing = 8;  // item ids a stream's loader has published and the other roles may still read
-constexpr int SMEM_BYTES = SMEM_BARS + 2 * kBarsPerStream * 8 + 128;
+constexpr int kRingInts = 8;  // per published item: id, tok0, len, q0, head, key tiles
+constexpr int SMEM_BYTES = SMEM_BARS + 2 * kBarsPerStream * 8 + 64 + 2 * kRing * kRingInts * 4;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRowSumLimit = 32768.0f;  // a tile row sum below this keeps every probability inside fp16 / bf16 range
@@ -156,7 +157,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
   // has taken yet, fetched by the stream's loader from a counter in global memory and published here for the stream's
   // other roles. Items are ranked longest first, so whichever stream is free takes the longest remaining one.
   volatile int* s_produced = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [2]: items published so far
-  volatile int* s_ring = reinterpret_cast<volatile int*>(tmem_slot + 4);      // [2][kRing]: their ids (n_items = no more work)
+  volatile int* s_ring = reinterpret_cast<volatile int*>(tmem_slot + 4);      // [2][kRing][kRingInts]: id (n_items = no more work) and decoded form
   auto smem_q = [&](int s, int b) { return base + (uint32_t)(s * SMEM_STREAM + b * TILE_BYTES); };
   auto smem_k = [&](int s, int st) { return base + (uint32_t)(s * SMEM_STREAM + (2 + st) * TILE_BYTES); };
   auto smem_v = [&](int s, int st) { return base + (uint32_t)(s * SMEM_STREAM + (4 + st) * TILE_BYTES); };
@@ -178,6 +179,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
     mbar_init_fence();
   }
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+  if (threadIdx.x == 64) prefetch_tensormap(&tm);  // a kernel parameter: fetching it does not depend on the previous kernel
   pdl_wait();  // everything above ran in the shadow of the previous kernel; global memory is touched from here on
   // ---- schedule tables (every CTA builds the same ones) -----------------------------------------------------------
   for (int i = threadIdx.x; i <= p.batch; i += kThreads) s_cu[i] = p.cu[i];
@@ -232,7 +234,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
         }
       }
     }
-    return s_ring[s * kRing + (int)(nq & (kRing - 1))];
+    return s_ring[(s * kRing + (int)(nq & (kRing - 1))) * kRingInts];
+  };
+  // the decoded form of a published item (decoded once, by the loader)
+  auto item_read = [&](int s, uint32_t nq) -> Item {
+    const volatile int* e = s_ring + (s * kRing + (int)(nq & (kRing - 1))) * kRingInts;
+    Item it;
+    it.tok0 = e[1];
+    it.len = e[2];
+    it.q0 = e[3];
+    it.head = e[4];
+    it.n = e[5];
+    return it;
   };
   auto tmem_s = [&](int s) { return tmem + (uint32_t)(s * 128); };
   auto tmem_o = [&](int s) { return tmem + (uint32_t)(256 + s * 64); };
@@ -259,7 +272,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
           if (produced == 0) id = min(2 * (int)blockIdx.x + s, n_items);
           else if (last_id < n_items) id = min(2 * (int)gridDim.x + atomicAdd(p.sched, 1), n_items);
           last_id = id;
-          s_ring[s * kRing + (produced & (kRing - 1))] = id;
+          volatile int* e = s_ring + (s * kRing + (produced & (kRing - 1))) * kRingInts;
+          e[0] = id;
+          if (id < n_items) {
+            const Item it = decode_item(id, p, s_cu, s_prefix, s_order);
+            e[1] = it.tok0;
+            e[2] = it.len;
+            e[3] = it.q0;
+            e[4] = it.head;
+            e[5] = it.n;
+          }
           __threadfence_block();
           s_produced[s] = ++produced;
         };
@@ -271,7 +293,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
         kc.nq = 0;
         kc.n = 0;
         if (kc.i < n_items) {
-          kc.it = decode_item(kc.i, p, s_cu, s_prefix, s_order);
+          kc.it = item_read(s, 0);
           kc.n = kc.it.n;
         }
         vc = kc;
@@ -282,9 +304,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
             c.j = 0;
             ++c.nq;
             if ((int)c.nq + 1 >= produced) produce();  // the key cursor leads: it finds item nq published and publishes nq + 1
-            c.i = s_ring[s * kRing + (int)(c.nq & (kRing - 1))];
+            c.i = s_ring[(s * kRing + (int)(c.nq & (kRing - 1))) * kRingInts];
             if (c.i < n_items) {
-              c.it = decode_item(c.i, p, s_cu, s_prefix, s_order);
+              c.it = item_read(s, c.nq);
               c.n = c.it.n;
             }
           }
@@ -352,14 +374,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
             c.j = 0;
             ++c.nq;
             c.i = item_at(s, c.nq);
-            c.n = (c.i < n_items) ? decode_item(c.i, p, s_cu, s_prefix, s_order).n : 0;
+            c.n = (c.i < n_items) ? item_read(s, c.nq).n : 0;
           }
         };
-        qc.i = 2 * (int)blockIdx.x + s;
         qc.j = 0;
         qc.g = 0;
         qc.nq = 0;
-        qc.n = (qc.i < n_items) ? decode_item(qc.i, p, s_cu, s_prefix, s_order).n : 0;
+        qc.i = item_at(s, 0);
+        qc.n = (qc.i < n_items) ? item_read(s, 0).n : 0;
         pc = qc;
         // S = Q K_g^T. Q and K_g are in shared memory and S is free when this is called.
         auto qk = [&]() {
@@ -448,8 +470,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
       return true;
     };
 
-    for (int i = 2 * (int)blockIdx.x + s; i < n_items && ok; ++nq, i = item_at(s, nq)) {
-      const Item it = decode_item(i, p, s_cu, s_prefix, s_order);
+    for (int i = item_at(s, 0); i < n_items && ok; ++nq, i = item_at(s, nq)) {
+      const Item it = item_read(s, nq);
       const int qrow = it.q0 + row;  // row within the sequence
       float m_used = -INFINITY, l_run = 0.f;
 
