@@ -69,6 +69,7 @@ struct Params {
   float scale;
   int* status;
   int* sched;  // [0] items handed out beyond every stream's first, [1] CTAs that have finished; both zero between launches
+  int staged;  // measurement switch: 0 = output rows stored straight from registers
 };
 
 struct Item {
@@ -169,6 +170,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s) {
       for (int k = 0; k < 13; ++k) mbar_init(bar(s, k), 1);  // TMA and MMA-commit barriers
+      // a Q buffer is free again once the item's last score MMA has read it and the four softmax warps have used it as
+      // the staging tile of the item's output (see flush_output)
+      mbar_init(q_empty(s, 0), 5);
+      mbar_init(q_empty(s, 1), 5);
       mbar_init(s_free(s), 4);                                // one arrival per softmax warp
       mbar_init(p_ready(s), 4);
       mbar_init(o_done(s), 1);
@@ -443,29 +448,46 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
     bool ok = true;
     // The output pass of an item (O / l to global memory) is deferred into the first tile of the stream's next item, after
     // that tile's scores are in registers: by then the last output MMA has long completed, so nothing is waited for.
-    bool pend = false, pend_store = false;
+    bool pend = false;
     float pend_inv = 0.f;
-    T* pend_op = nullptr;
+    T* pend_base = nullptr;  // first output element of this warp's 32 rows of the pending item
+    int pend_rows = 0;       // how many of those rows exist in the sequence
+    int pend_qb = 0;         // the pending item's Q buffer
+    // Output pass: O / l of the warp's 32 rows goes through shared memory, so that the global stores are whole 128-byte
+    // rows (one lane per row straight from registers costs 32 cache lines per store instruction, and with four warps
+    // flushing at once that was 2000 - 3000 cycles per item). The staging tile is the item's own Q buffer: its last
+    // reader, the item's last score MMA, completed before the scores of that tile were loaded.
     auto flush_output = [&]() {  // whole warp; g = tiles finished so far, the pending item's last tile is g - 1
       if (!__all_sync(0xffffffffu, mbar_wait(o_done(s), (g - 1) & 1u, abort_flag))) return false;
       tc_fence_after();
+      uint8_t* stage = smem + s * SMEM_STREAM + pend_qb * TILE_BYTES + quad * 32 * 128;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
         tmem_ld32_issue(to + (uint32_t)(c * 32), r);
         tmem_ld_wait();
-        if (pend_store) {  // 128 contiguous bytes per row
 #pragma unroll
-          for (int g8 = 0; g8 < 4; ++g8) {
-            uint4 q;
-            q.x = pack2<T>(__uint_as_float(r[g8 * 8 + 0]) * pend_inv, __uint_as_float(r[g8 * 8 + 1]) * pend_inv);
-            q.y = pack2<T>(__uint_as_float(r[g8 * 8 + 2]) * pend_inv, __uint_as_float(r[g8 * 8 + 3]) * pend_inv);
-            q.z = pack2<T>(__uint_as_float(r[g8 * 8 + 4]) * pend_inv, __uint_as_float(r[g8 * 8 + 5]) * pend_inv);
-            q.w = pack2<T>(__uint_as_float(r[g8 * 8 + 6]) * pend_inv, __uint_as_float(r[g8 * 8 + 7]) * pend_inv);
-            *reinterpret_cast<uint4*>(pend_op + c * 32 + g8 * 8) = q;
-          }
+        for (int g8 = 0; g8 < 4; ++g8) {
+          uint4 q;
+          q.x = pack2<T>(__uint_as_float(r[g8 * 8 + 0]) * pend_inv, __uint_as_float(r[g8 * 8 + 1]) * pend_inv);
+          q.y = pack2<T>(__uint_as_float(r[g8 * 8 + 2]) * pend_inv, __uint_as_float(r[g8 * 8 + 3]) * pend_inv);
+          q.z = pack2<T>(__uint_as_float(r[g8 * 8 + 4]) * pend_inv, __uint_as_float(r[g8 * 8 + 5]) * pend_inv);
+          q.w = pack2<T>(__uint_as_float(r[g8 * 8 + 6]) * pend_inv, __uint_as_float(r[g8 * 8 + 7]) * pend_inv);
+          if (p.staged) *reinterpret_cast<uint4*>(stage + lane * 128 + (((c * 4 + g8) ^ (lane & 7)) << 4)) = q;  // swizzled: no bank conflicts either way
+          else if (lane < pend_rows) *reinterpret_cast<uint4*>(pend_base + (long long)lane * H + (c * 4 + g8) * 8) = q;
         }
       }
+      __syncwarp();
+      if (p.staged) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {  // four rows of 128 bytes per instruction
+          const int r = k * 4 + (lane >> 3), j = lane & 7;
+          const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 128 + ((j ^ (r & 7)) << 4));
+          if (r < pend_rows) *reinterpret_cast<uint4*>(pend_base + (long long)r * H + j * 8) = v;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(q_empty(s, pend_qb));
       pend = false;
       return true;
     };
@@ -570,9 +592,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
       }
       if (!ok) break;
       pend = true;
-      pend_store = qrow < it.len;
       pend_inv = 1.0f / l_run;
-      pend_op = static_cast<T*>(p.out) + (long long)(it.tok0 + qrow) * H + it.head * D;
+      pend_rows = it.len - it.q0 - quad * 32;
+      pend_qb = (int)(nq & 1u);
+      pend_base = static_cast<T*>(p.out) + (long long)(it.tok0 + it.q0 + quad * 32) * H + it.head * D;
     }
     if (ok && pend) flush_output();  // the stream's last item
   }
@@ -616,7 +639,8 @@ int attention_tc_launch(ttb_ctx* ctx, int dtype, const void* qkv, int64_t tokens
   CUtensorMap tm;
   if (!encode_tile_map(&tm, qkv, 2, dtype == TTB_BF16, (uint64_t)tokens, (uint64_t)(3 * H), (uint64_t)(3 * H), 128))
     return TTB_ERR_UNSUPPORTED;
-  Params p{out, cu, (int)B, (int)heads, causal ? 1 : 0, scale, ctx->d_status, ctx->d_status + 1};
+  static const int staged = [] { const char* e = getenv("TTB_ATTN_STAGED"); return (e && e[0] == '0') ? 0 : 1; }();
+  Params p{out, cu, (int)B, (int)heads, causal ? 1 : 0, scale, ctx->d_status, ctx->d_status + 1, staged};
   // upper bound of the item count from what the host knows; a CTA runs two streams, idle CTAs leave after the tables
   const int64_t tiles_bound = std::min<int64_t>(tokens / QT + B, B * ((max_seqlen + QT - 1) / QT));
   const int64_t items_bound = std::max<int64_t>(1, tiles_bound * heads);
