@@ -446,8 +446,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
     const float sc = p.scale * kLog2e;
     uint32_t g = 0, nq = 0;
     bool ok = true;
-    // The output pass of an item (O / l to global memory) is deferred into the first tile of the stream's next item, after
-    // that tile's scores are in registers: by then the last output MMA has long completed, so nothing is waited for.
+    // The output pass of an item (O / l to global memory) is deferred to the start of the stream's next item, before that
+    // item's first scores are loaded (so that they do not hold the registers meanwhile): the last output MMA has 200 - 300
+    // cycles left to run at that point, and the next item's first scores are being computed.
     bool pend = false;
     float pend_inv = 0.f;
     T* pend_base = nullptr;  // first output element of this warp's 32 rows of the pending item
@@ -499,6 +500,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
 
       for (int j = 0; j < it.n; ++j, ++g) {
         const int k0 = j * KT;
+        // The previous item's output pass, before this tile's scores occupy the registers. It reads O before this warp's
+        // next p_ready arrival, which is what the next output MMA (the one that overwrites O) waits for; it also proves
+        // PV(g-1) complete, so P may be rewritten.
+        if (pend && !flush_output()) { ok = false; break; }
         if (!__all_sync(0xffffffffu, mbar_wait(s_full(s), g & 1u, abort_flag))) { ok = false; break; }  // warp-uniform
         tc_fence_after();
         uint32_t sr[4][32];
@@ -508,9 +513,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
         tc_fence_before();  // S_g is in registers: the next scores may overwrite it (one phase per tile)
         __syncwarp();
         if (lane == 0) mbar_arrive(s_free(s));
-        // The previous item's output pass. It reads O before this warp's next p_ready arrival, which is what the next
-        // output MMA (the one that overwrites O) waits for; it also proves PV(g-1) complete, so P may be rewritten.
-        if (pend && !flush_output()) { ok = false; break; }
         // keys of this tile that at least one row of this warp can see, in 32-key chunks: the others cost no exponentials
         int lim = it.len - k0;
         if (p.causal) lim = min(lim, it.q0 + quad * 32 + 32 - k0);
