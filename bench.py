@@ -242,7 +242,8 @@ def graph_us(torch, ctx, fns, rounds):
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
-        ctx.set_stream(side.cuda_stream)
+        if ctx is not None:
+            ctx.set_stream(side.cuda_stream)
         for f in fns:
             f()
         side.synchronize()
@@ -251,7 +252,8 @@ def graph_us(torch, ctx, fns, rounds):
             for f in fns:
                 f()
     torch.cuda.current_stream().wait_stream(side)
-    ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+    if ctx is not None:
+        ctx.set_stream(torch.cuda.current_stream().cuda_stream)
     for _ in range(2):
         graph.replay()
     torch.cuda.synchronize()
@@ -286,8 +288,13 @@ def gemm_roofline(torch, lens, peaks):
                  torch.empty(tokens, N, device="cuda", dtype=f16)) for _ in range(sets)]
         us = burst_us(torch, [lambda a=a, r=r, o=o: ctx.call("linear", _capi.F16, a, K, w, b, r, N, tokens, N, K, epi, o, N)
                               for a, r, o in bufs], rounds)
+        # the vendor library on the same operands for orientation (torch.addmm = cuBLAS GEMM + bias, no activation and
+        # no residual), replayed from a CUDA graph to keep torch's host path out of the number
+        wt = w.t()
+        lib_us = graph_us(torch, None, [lambda a=a, o=o: torch.addmm(b, a, wt, out=o) for a, _, o in bufs], rounds)
         fl = 2.0 * tokens * N * K
-        per_shape[name] = {"us": round(us, 1), "tflops": round(fl / us / 1e6, 1), "frac": round(fl / us / 1e6 / peaks["tflops"], 4)}
+        per_shape[name] = {"us": round(us, 1), "tflops": round(fl / us / 1e6, 1), "frac": round(fl / us / 1e6 / peaks["tflops"], 4),
+                           "cublas_bias_only_us": round(lib_us, 1)}
         total_us += us
         total_flops += fl
         del bufs, w, b
