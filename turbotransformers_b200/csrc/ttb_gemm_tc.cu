@@ -1083,7 +1083,8 @@ int pick_tile(ttb_ctx* ctx, const Operands& op, GemmParams& p) {
   // N=3072 K=768 1088 -> 1165, N=768 K=3072 1171 -> 1273, but N=768 K=768 789 -> 756: pairs win unless both the
   // mainloop and the row of tiles are short.
   const int64_t k_bytes = (int64_t)p.K * IN_BYTES * p.npass;
-  const bool pair_pays = k_bytes >= 4096 || p.N >= 1536;
+  // (same box, bias + residual epilogue: N = K = 768 25.7 us single against 26.3 paired; N = K = 1024, M = 16384 37.1 against 35.8)
+  const bool pair_pays = k_bytes >= 4096 || p.N >= 1536 || (k_bytes >= 2048 && p.N >= 1024);
   p.split_k = 1;
   if (pair_mode() && pair_tiles >= ctx->sm_count / 2 && (pair_pays || pair_mode() == 2)) return launch_tc<256, KIND, OutT, true, false, VAR>(ctx, op, p);
   if (tiles(256) >= ctx->sm_count) return launch_tc<256, KIND, OutT, false, false, VAR>(ctx, op, p);
