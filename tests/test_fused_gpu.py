@@ -237,10 +237,38 @@ def test_attention_varlen(ctx, dt, lens, heads, kernel, monkeypatch):
     assert maxdiff(got, want) < (4e-3 if dt == "f16" else 3e-2)
 
 
+@pytest.mark.parametrize("kernel", ["auto", "tensor_memory", "mma_sync"])
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("lens,heads,pitch,causal", [([512, 300, 129, 8, 477, 64, 390, 511, 1, 256, 500, 128], 12, 512, False),
+                                                     ([200, 131, 77], 4, 203, False),     # odd pitch: the scalar mask loads
+                                                     ([384, 250, 512], 4, 512, True),     # padding mask on top of the causal flag
+                                                     ([1100, 640], 2, 1100, False)])
+def test_attention_with_a_per_key_mask(ctx, dt, lens, heads, pitch, causal, kernel, monkeypatch):
+    """The encoder's padding mask ([B, Lk] additive, one row of keys per sequence) on every kernel: 0 / -10000 entries
+    as PrepareBertMasks makes them plus a few graded ones, ragged lengths, key tiles that end inside a tile."""
+    if kernel != "auto":
+        monkeypatch.setenv("TTB_ATTN_TC", "2" if kernel == "tensor_memory" else "0")
+    r = rng(sum(lens) + pitch)
+    H, T, B = heads * 64, sum(lens), len(lens)
+    qkv = rounded(r.standard_normal((T, 3 * H)).astype(np.float32), dt)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32).cuda()
+    mask = np.where(r.random((B, pitch)) < 0.3, -10000.0, 0.0).astype(np.float32)
+    mask += np.where(r.random((B, pitch)) < 0.1, -3.0 * r.random((B, pitch)), 0.0).astype(np.float32)
+    mask[:, 0] = 0   # every query keeps at least one key
+    mask[0, :] = 0   # one sequence without padding
+    out = torch.full((T, H), float("nan"), dtype=TORCH_DT[dt], device="cuda")
+    ctx.call("attention_fwd", code(dt), dev(qkv, dt), T, cu, B, max(lens), heads, 64, dev(mask), pitch, 0, int(causal), 0.125, out)
+    assert ctx.device_status() == _capi.OK
+    got = host(out)
+    assert np.isfinite(got).all()
+    assert maxdiff(got, attention_oracle(qkv, lens, heads, mask, causal=causal)) < (4e-3 if dt == "f16" else 3e-2)
+
+
 @pytest.mark.parametrize("kernel", ["tensor_memory", "mma_sync"])
 @pytest.mark.parametrize("dt", ["f16", "bf16"])
 def test_attention_masks_and_causal(ctx, dt, kernel, monkeypatch):
-    monkeypatch.setenv("TTB_ATTN_TC", "2" if kernel == "tensor_memory" else "0")  # mask tensors always take mma.sync
+    # per-key masks are an operand of both kernels; masks with a row per query always take mma.sync
+    monkeypatch.setenv("TTB_ATTN_TC", "2" if kernel == "tensor_memory" else "0")
     r = rng(21)
     lens, heads = [70, 33, 128], 4
     H, T, B, maxL = heads * 64, sum(lens), len(lens), max(lens)

@@ -294,7 +294,7 @@ attention_fwd_kernel(const AttnParams p) {
 namespace ttb {
 int attention_tc_mode();
 int attention_tc_launch(ttb_ctx* ctx, int dtype, const void* qkv, int64_t tokens, const int32_t* cu, int64_t B, int64_t max_seqlen,
-                        int64_t heads, int causal, float scale, void* out);
+                        int64_t heads, const float* mask, int64_t mask_batch_stride, int causal, float scale, void* out);
 }  // namespace ttb
 
 extern "C" int ttb_attention_fwd(ttb_ctx* ctx, int dtype, const void* qkv, int64_t total_tokens, const int32_t* cu_seqlens,
@@ -313,11 +313,12 @@ extern "C" int ttb_attention_fwd(ttb_ctx* ctx, int dtype, const void* qkv, int64
   DeviceGuard g(ctx->device);
   // The persistent tensor-memory kernel wins once there is enough work to fill its pipeline (measured on B200, whole
   // BERT-base step of 64 sequences U[8,512]: 4.52 ms against 4.75 ms with the mma.sync kernel below); a handful of short
-  // sequences finish sooner on the many small CTAs of the mma.sync kernel, which also serves every call with a mask tensor.
+  // sequences finish sooner on the many small CTAs of the mma.sync kernel, which also serves masks with a row per query
+  // (a mask with one row of keys per sequence, the encoder's padding mask, is an operand of the tensor-memory kernel).
   const bool enough_work = total_tokens >= 4096;
   const int tc_mode = attention_tc_mode();
-  if (!mask && total_tokens > 0 && (tc_mode == 2 || (tc_mode == 1 && enough_work))) {
-    const int s = attention_tc_launch(ctx, dtype, qkv, total_tokens, cu_seqlens, B, max_seqlen, heads, causal, scale, out);
+  if ((!mask || mask_row_stride == 0) && total_tokens > 0 && (tc_mode == 2 || (tc_mode == 1 && enough_work))) {
+    const int s = attention_tc_launch(ctx, dtype, qkv, total_tokens, cu_seqlens, B, max_seqlen, heads, mask, mask_batch_stride, causal, scale, out);
     if (s != TTB_ERR_UNSUPPORTED) return s;
   }
   AttnParams p{qkv, out, cu_seqlens, mask, mask_batch_stride, mask_row_stride, (int)heads, causal ? 1 : 0, scale};

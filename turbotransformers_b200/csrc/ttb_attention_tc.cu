@@ -70,11 +70,15 @@ struct Params {
   int* status;
   int* sched;  // [0] items handed out beyond every stream's first, [1] CTAs that have finished; both zero between launches
   int staged;  // measurement switch: 0 = output rows stored straight from registers
+  const float* mask;      // MASK kernels: additive fp32 mask, one row of keys per sequence: mask[b * mask_bs + key]
+  long long mask_bs;
+  int mask_vec;           // its rows can be read 16 bytes at a time
 };
 
 struct Item {
   int tok0, len, q0, head;
-  int n;  // key tiles this query tile visits
+  int n;    // key tiles this query tile visits
+  int seq;  // which sequence of the batch
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -105,6 +109,7 @@ __device__ __forceinline__ Item decode_item(int i, const Params& p, const int* s
     else hi = mid;
   }
   const int seq = s_order[lo];
+  it.seq = seq;
   it.tok0 = s_cu[seq];
   it.len = s_cu[seq + 1] - it.tok0;
   const int qt = pidx - s_prefix[lo];
@@ -122,7 +127,7 @@ struct Cursor {
   uint32_t nq;  // items before this one in the stream
 };
 
-template <typename T>
+template <typename T, bool MASK>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
   constexpr int FMT = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
@@ -250,6 +255,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
     it.q0 = e[3];
     it.head = e[4];
     it.n = e[5];
+    it.seq = e[6];
     return it;
   };
   auto tmem_s = [&](int s) { return tmem + (uint32_t)(s * 128); };
@@ -286,6 +292,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
             e[3] = it.q0;
             e[4] = it.head;
             e[5] = it.n;
+            e[6] = it.seq;
           }
           __threadfence_block();
           s_produced[s] = ++produced;
@@ -443,7 +450,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
     const int row = quad * 32 + lane;           // row within the tile == TMEM lane
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     const uint32_t ts = tmem_s(s) + lane_addr, to = tmem_o(s) + lane_addr, tp = tmem_p(s) + lane_addr;
-    const float sc = p.scale * kLog2e;
+    // With a mask the scores are moved to the exponent's domain where they are loaded (s * scale * log2 e + mask * log2 e),
+    // so everything after that works with a scale of one.
+    const float sc = MASK ? 1.0f : p.scale * kLog2e;
     uint32_t g = 0, nq = 0;
     bool ok = true;
     // The output pass of an item (O / l to global memory) is deferred to the start of the stream's next item, before that
@@ -513,6 +522,37 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
         tc_fence_before();  // S_g is in registers: the next scores may overwrite it (one phase per tile)
         __syncwarp();
         if (lane == 0) mbar_arrive(s_free(s));
+        if (MASK) {
+          // one mask row per sequence: every thread of the warp reads the same addresses (one transaction per load)
+          const float* mrow = p.mask + (long long)it.seq * p.mask_bs + k0;
+          const float sc_in = p.scale * kLog2e;
+          const int valid = it.len - k0;  // keys of the tile that exist; the others are set to -inf below
+          // the last group of four that holds an existing key; it may reach up to three floats past the sequence's length,
+          // which stays inside the row because the pitch is a multiple of four (mask_vec)
+          const int last4 = ((valid + 3) & ~3) - 4;
+          if (p.mask_vec) {
+            // loads without branches (a group past the end re-reads that last one: its scores become -inf anyway), so
+            // that all of them are in flight together
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+              for (int e = 0; e < 32; e += 4) {
+                float4 mk = __ldg(reinterpret_cast<const float4*>(mrow + min(c * 32 + e, last4)));
+                sr[c][e] = __float_as_uint(fmaf(__uint_as_float(sr[c][e]), sc_in, mk.x * kLog2e));
+                sr[c][e + 1] = __float_as_uint(fmaf(__uint_as_float(sr[c][e + 1]), sc_in, mk.y * kLog2e));
+                sr[c][e + 2] = __float_as_uint(fmaf(__uint_as_float(sr[c][e + 2]), sc_in, mk.z * kLog2e));
+                sr[c][e + 3] = __float_as_uint(fmaf(__uint_as_float(sr[c][e + 3]), sc_in, mk.w * kLog2e));
+              }
+          } else {
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+              for (int e = 0; e < 32; ++e) {
+                const int key = min(c * 32 + e, max(valid - 1, 0));
+                sr[c][e] = __float_as_uint(fmaf(__uint_as_float(sr[c][e]), sc_in, __ldg(mrow + key) * kLog2e));
+              }
+          }
+        }
         // keys of this tile that at least one row of this warp can see, in 32-key chunks: the others cost no exponentials
         int lim = it.len - k0;
         if (p.causal) lim = min(lim, it.q0 + quad * 32 + 32 - k0);
@@ -635,14 +675,15 @@ int attention_tc_mode() {
 // the mma.sync kernel). Returns TTB_ERR_UNSUPPORTED when the batch does not fit the schedule tables or the tensor map
 // cannot be encoded, so the caller can fall back.
 int attention_tc_launch(ttb_ctx* ctx, int dtype, const void* qkv, int64_t tokens, const int32_t* cu, int64_t B, int64_t max_seqlen,
-                        int64_t heads, int causal, float scale, void* out) {
+                        int64_t heads, const float* mask, int64_t mask_batch_stride, int causal, float scale, void* out) {
   if (B > kMaxB || B < 1 || heads < 1) return TTB_ERR_UNSUPPORTED;
   const int64_t H = heads * D;
   CUtensorMap tm;
   if (!encode_tile_map(&tm, qkv, 2, dtype == TTB_BF16, (uint64_t)tokens, (uint64_t)(3 * H), (uint64_t)(3 * H), 128))
     return TTB_ERR_UNSUPPORTED;
   static const int staged = [] { const char* e = getenv("TTB_ATTN_STAGED"); return (e && e[0] == '0') ? 0 : 1; }();
-  Params p{out, cu, (int)B, (int)heads, causal ? 1 : 0, scale, ctx->d_status, ctx->d_status + 1, staged};
+  const int mask_vec = (mask && (reinterpret_cast<uintptr_t>(mask) % 16 == 0) && mask_batch_stride % 4 == 0) ? 1 : 0;
+  Params p{out, cu, (int)B, (int)heads, causal ? 1 : 0, scale, ctx->d_status, ctx->d_status + 1, staged, mask, (long long)mask_batch_stride, mask_vec};
   // upper bound of the item count from what the host knows; a CTA runs two streams, idle CTAs leave after the tables
   const int64_t tiles_bound = std::min<int64_t>(tokens / QT + B, B * ((max_seqlen + QT - 1) / QT));
   const int64_t items_bound = std::max<int64_t>(1, tiles_bound * heads);
@@ -650,13 +691,20 @@ int attention_tc_launch(ttb_ctx* ctx, int dtype, const void* qkv, int64_t tokens
   static bool configured[64] = {};
   const int dev = ctx->device < 64 ? ctx->device : 63;
   if (!configured[dev]) {
-    TTB_CUDA(ctx, cudaFuncSetAttribute(attention_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    TTB_CUDA(ctx, cudaFuncSetAttribute(attention_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    TTB_CUDA(ctx, cudaFuncSetAttribute(attention_tc_kernel<__half, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    TTB_CUDA(ctx, cudaFuncSetAttribute(attention_tc_kernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    TTB_CUDA(ctx, cudaFuncSetAttribute(attention_tc_kernel<__half, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    TTB_CUDA(ctx, cudaFuncSetAttribute(attention_tc_kernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     configured[dev] = true;
   }
-  if (dtype == TTB_F16) launch_pdl(attention_tc_kernel<__half>, grid, dim3(kThreads), SMEM_BYTES, ctx->stream, tm, p);
-  else launch_pdl(attention_tc_kernel<__nv_bfloat16>, grid, dim3(kThreads), SMEM_BYTES, ctx->stream, tm, p);
-  return launched(ctx, "attention_tc");
+  if (mask) {
+    if (dtype == TTB_F16) launch_pdl(attention_tc_kernel<__half, true>, grid, dim3(kThreads), SMEM_BYTES, ctx->stream, tm, p);
+    else launch_pdl(attention_tc_kernel<__nv_bfloat16, true>, grid, dim3(kThreads), SMEM_BYTES, ctx->stream, tm, p);
+  } else {
+    if (dtype == TTB_F16) launch_pdl(attention_tc_kernel<__half, false>, grid, dim3(kThreads), SMEM_BYTES, ctx->stream, tm, p);
+    else launch_pdl(attention_tc_kernel<__nv_bfloat16, false>, grid, dim3(kThreads), SMEM_BYTES, ctx->stream, tm, p);
+  }
+  return launched(ctx, mask ? "attention_tc_mask" : "attention_tc");
 }
 
 }  // namespace ttb

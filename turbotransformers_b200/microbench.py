@@ -104,6 +104,7 @@ def main():
     ap.add_argument("--seq", type=int, default=512)
     ap.add_argument("--heads", type=int, default=12)
     ap.add_argument("--causal", action="store_true")
+    ap.add_argument("--key-mask", action="store_true", help="attention: pass a per-key additive mask [B, max_len] (a quarter of the keys masked)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--no-flush", action="store_true")
@@ -179,11 +180,16 @@ def main():
         qkv = torch.randn(T, 3 * H, device="cuda", dtype=tdt)
         cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device="cuda")
         o = torch.empty(T, H, device="cuda", dtype=tdt)
-        fn = lambda: ctx.call("attention_fwd", code, qkv, T, cu, len(lens), max(lens), a.heads, 64, None, 0, 0, int(a.causal), 0.125, o)
+        mask, pitch = None, 0
+        if a.key_mask:
+            pitch = max(lens)
+            mask = torch.where(torch.rand(len(lens), pitch, device="cuda") < 0.25, -10000.0, 0.0).float()
+            mask[:, 0] = 0
+        fn = lambda: ctx.call("attention_fwd", code, qkv, T, cu, len(lens), max(lens), a.heads, 64, mask, pitch, 0, int(a.causal), 0.125, o)
         if a.burst:
             def make():
                 qq, oo = torch.randn_like(qkv), torch.empty_like(o)
-                return lambda: ctx.call("attention_fwd", code, qq, T, cu, len(lens), max(lens), a.heads, 64, None, 0, 0, int(a.causal), 0.125, oo)
+                return lambda: ctx.call("attention_fwd", code, qq, T, cu, len(lens), max(lens), a.heads, 64, mask, pitch, 0, int(a.causal), 0.125, oo)
             fns = [make() for _ in range(a.burst)]
             mean, med, best = timed_graph(ctx, fns, a.warmup, a.iters) if a.graph else timed_burst(fns, a.warmup, a.iters)
         else:
