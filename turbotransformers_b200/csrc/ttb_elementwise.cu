@@ -689,6 +689,90 @@ embedding_ln_kernel(const int64_t* __restrict__ ids, const int64_t* __restrict__
   }
 }
 
+// The same for 16-bit tables with hidden % 8 == 0 and hidden <= 256 * ITERS: 16-byte loads of the three rows, the sum held
+// in registers for the two passes of the statistics and the output.
+template <typename T, int ITERS>
+__global__ void __launch_bounds__(kRowsPerBlock * 32)
+embedding_ln16_kernel(const int64_t* __restrict__ ids, const int64_t* __restrict__ pos_ids, const int64_t* __restrict__ type_ids,
+                      const int32_t* __restrict__ cu, int B, int seq_len, int64_t n_tokens, const T* __restrict__ word,
+                      const T* __restrict__ position, const T* __restrict__ token_type, const T* __restrict__ gamma,
+                      const T* __restrict__ beta, int hidden, int64_t vocab, int64_t n_pos, int64_t n_types, float eps, T* __restrict__ out,
+                      T* __restrict__ out_lo, float* __restrict__ out_f32, int* status) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int warps_total = gridDim.x * kRowsPerBlock;
+  for (int64_t t = (int64_t)blockIdx.x * kRowsPerBlock + (threadIdx.x >> 5); t < n_tokens; t += warps_total) {
+    int64_t id = ids[t];
+    int64_t pos = pos_ids ? pos_ids[t] : (cu ? (int64_t)t - cu[find_sequence(cu, B, (int)t)] : (t % seq_len));
+    int64_t tt = type_ids ? type_ids[t] : 0;
+    const bool bad = id < 0 || id >= vocab || pos < 0 || pos >= n_pos || tt < 0 || tt >= n_types;
+    if (bad) {
+      if (lane == 0) atomicExch(status, (int)TTB_ERR_BAD_INDEX);
+      id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+      pos = pos < 0 ? 0 : (pos >= n_pos ? n_pos - 1 : pos);
+      tt = tt < 0 ? 0 : (tt >= n_types ? n_types - 1 : tt);
+    }
+    const T* w = word + id * hidden;
+    const T* p = position + pos * hidden;
+    const T* y = token_type + tt * hidden;
+    float v[ITERS][8];
+    float sum = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int col = (it * 32 + lane) * 8;
+      if (col < hidden) {
+        Vec8<T> a, b, c;
+        a.load(w + col);
+        b.load(y + col);
+        c.load(p + col);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {  // same accumulation order as the reference: word, then token type, then position
+          v[it][j] = (a.v[j] + b.v[j]) + c.v[j];
+          sum += v[it][j];
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[it][j] = 0.f;
+      }
+    }
+    const float mean = warp_sum(sum) / (float)hidden;
+    float sq = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      if ((it * 32 + lane) * 8 < hidden) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { const float d = v[it][j] - mean; sq += d * d; }
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(sq) / (float)hidden + eps);
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int col = (it * 32 + lane) * 8;
+      if (col < hidden) {
+        Vec8<T> g, b, o;
+        g.load(gamma + col);
+        b.load(beta + col);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o.v[j] = b.v[j] + g.v[j] * rstd * (v[it][j] - mean);
+        o.store(out + t * hidden + col);
+        if (out_f32) {
+          Vec8<float> f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f.v[j] = o.v[j];
+          f.store(out_f32 + t * hidden + col);
+        }
+        if (out_lo) {
+          Vec8<T> l;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) l.v[j] = o.v[j] - to_f(from_f<T>(o.v[j]));
+          l.store(out_lo + t * hidden + col);
+        }
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // Pooling over the sequence axis.
 // ------------------------------------------------------------------------------------------------
@@ -1275,6 +1359,27 @@ extern "C" int ttb_embedding_ln_planes(ttb_ctx* ctx, int dtype, const int64_t* i
   TTB_REQUIRE(ctx, !cu_seqlens || B > 0, "embedding_ln: cu_seqlens needs B > 0");
   DeviceGuard g(ctx->device);
   const int grid = grid_for(n_tokens, kRowsPerBlock, ctx->sm_count);
+  const bool all16 = ((reinterpret_cast<uintptr_t>(word) | reinterpret_cast<uintptr_t>(position) | reinterpret_cast<uintptr_t>(token_type) |
+                       reinterpret_cast<uintptr_t>(gamma) | reinterpret_cast<uintptr_t>(beta) | reinterpret_cast<uintptr_t>(out) |
+                       reinterpret_cast<uintptr_t>(out_lo) | reinterpret_cast<uintptr_t>(out_f32)) & 15) == 0;
+  if ((dtype == TTB_F16 || dtype == TTB_BF16) && hidden % 8 == 0 && hidden <= 1024 && all16) {
+#define EMB16(T, IT)                                                                                                                         \
+  launch_pdl(embedding_ln16_kernel<T, IT>, dim3(grid), dim3(kRowsPerBlock * 32), 0, ctx->stream, ids, position_ids, token_type_ids, cu_seqlens,  \
+             (int)B, (int)(seq_len > 0 ? seq_len : 1), n_tokens, (const T*)word, (const T*)position, (const T*)token_type, (const T*)gamma,       \
+             (const T*)beta, (int)hidden, vocab, n_positions, n_types, eps, (T*)out, (T*)out_lo, out_f32, ctx->d_status)
+#define EMB16_PICK(T)                    \
+  do {                                   \
+    if (hidden <= 256) EMB16(T, 1);      \
+    else if (hidden <= 512) EMB16(T, 2); \
+    else if (hidden <= 768) EMB16(T, 3); \
+    else EMB16(T, 4);                    \
+  } while (0)
+    if (dtype == TTB_F16) EMB16_PICK(__half);
+    else EMB16_PICK(__nv_bfloat16);
+#undef EMB16_PICK
+#undef EMB16
+    return launched(ctx, "embedding_ln");
+  }
   TTB_DISPATCH_FLOAT(ctx, dtype, T,
                      (embedding_ln_kernel<T><<<grid, kRowsPerBlock * 32, 0, ctx->stream>>>(
                          ids, position_ids, token_type_ids, cu_seqlens, (int)B, (int)(seq_len > 0 ? seq_len : 1), n_tokens,
