@@ -57,7 +57,9 @@ constexpr int SMEM_BARS = (SMEM_ORDER + kMaxB * 2 + 63) / 64 * 64;
 constexpr int kBarsPerStream = 16;
 constexpr int kRing = 8;  // item ids a stream's loader has published and the other roles may still read
 constexpr int kRingInts = 8;  // per published item: id, tok0, len, q0, head, key tiles
-constexpr int SMEM_BYTES = SMEM_BARS + 2 * kBarsPerStream * 8 + 64 + 2 * kRing * kRingInts * 4;
+constexpr int SMEM_MISC = 2 * kBarsPerStream * 8 + 64 + 2 * kRing * kRingInts * 4;  // barriers, TMEM slot, flags, item rings
+constexpr int SMEM_MASKROW = (SMEM_BARS + SMEM_MISC + 15) / 16 * 16;                // float[8 softmax warps][128]: a tile's mask entries
+constexpr int SMEM_BYTES = SMEM_MASKROW + 8 * 128 * 4;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRowSumLimit = 32768.0f;  // a tile row sum below this keeps every probability inside fp16 / bf16 range
@@ -72,7 +74,6 @@ struct Params {
   int staged;  // measurement switch: 0 = output rows stored straight from registers
   const float* mask;      // MASK kernels: additive fp32 mask, one row of keys per sequence: mask[b * mask_bs + key]
   long long mask_bs;
-  int mask_vec;           // its rows can be read 16 bytes at a time
 };
 
 struct Item {
@@ -450,9 +451,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
     const int row = quad * 32 + lane;           // row within the tile == TMEM lane
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     const uint32_t ts = tmem_s(s) + lane_addr, to = tmem_o(s) + lane_addr, tp = tmem_p(s) + lane_addr;
-    // With a mask the scores are moved to the exponent's domain where they are loaded (s * scale * log2 e + mask * log2 e),
-    // so everything after that works with a scale of one.
-    const float sc = MASK ? 1.0f : p.scale * kLog2e;
+    // With a mask, the scores of a tile whose mask entries are not all zero are moved to the exponent's domain where they are
+    // loaded (s * scale * log2 e + mask * log2 e), and everything after that works with a scale of one for that tile.
+    const float sc_plain = p.scale * kLog2e;
     uint32_t g = 0, nq = 0;
     bool ok = true;
     // The output pass of an item (O / l to global memory) is deferred to the start of the stream's next item, before that
@@ -522,34 +523,33 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
         tc_fence_before();  // S_g is in registers: the next scores may overwrite it (one phase per tile)
         __syncwarp();
         if (lane == 0) mbar_arrive(s_free(s));
+        float sc = sc_plain;
         if (MASK) {
-          // one mask row per sequence: every thread of the warp reads the same addresses (one transaction per load)
           const float* mrow = p.mask + (long long)it.seq * p.mask_bs + k0;
-          const float sc_in = p.scale * kLog2e;
+          const float sc_in = sc_plain;
           const int valid = it.len - k0;  // keys of the tile that exist; the others are set to -inf below
-          // the last group of four that holds an existing key; it may reach up to three floats past the sequence's length,
-          // which stays inside the row because the pitch is a multiple of four (mask_vec)
-          const int last4 = ((valid + 3) & ~3) - 4;
-          if (p.mask_vec) {
-            // loads without branches (a group past the end re-reads that last one: its scores become -inf anyway), so
-            // that all of them are in flight together
+          // The warp fetches the tile's 128 entries once, four per lane, coalesced (any row pitch and alignment). A padding
+          // mask is zero over most tiles: when none of the entries is set the scores are left alone. Otherwise the entries go
+          // through a 512-byte row of shared memory, from which every thread reads all of them 16 bytes at a time.
+          float mine[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) mine[u] = (u * 32 + lane < valid) ? __ldg(mrow + u * 32 + lane) : 0.f;
+          if (__any_sync(0xffffffffu, mine[0] != 0.f || mine[1] != 0.f || mine[2] != 0.f || mine[3] != 0.f)) {
+            sc = 1.0f;
+            float* mtile = reinterpret_cast<float*>(smem + SMEM_MASKROW) + (warp - 4) * 128;
+            __syncwarp();  // the previous tile's reads of the row are done
+#pragma unroll
+            for (int u = 0; u < 4; ++u) mtile[u * 32 + lane] = mine[u] * kLog2e;
+            __syncwarp();
 #pragma unroll
             for (int c = 0; c < 4; ++c)
 #pragma unroll
               for (int e = 0; e < 32; e += 4) {
-                float4 mk = __ldg(reinterpret_cast<const float4*>(mrow + min(c * 32 + e, last4)));
-                sr[c][e] = __float_as_uint(fmaf(__uint_as_float(sr[c][e]), sc_in, mk.x * kLog2e));
-                sr[c][e + 1] = __float_as_uint(fmaf(__uint_as_float(sr[c][e + 1]), sc_in, mk.y * kLog2e));
-                sr[c][e + 2] = __float_as_uint(fmaf(__uint_as_float(sr[c][e + 2]), sc_in, mk.z * kLog2e));
-                sr[c][e + 3] = __float_as_uint(fmaf(__uint_as_float(sr[c][e + 3]), sc_in, mk.w * kLog2e));
-              }
-          } else {
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-#pragma unroll
-              for (int e = 0; e < 32; ++e) {
-                const int key = min(c * 32 + e, max(valid - 1, 0));
-                sr[c][e] = __float_as_uint(fmaf(__uint_as_float(sr[c][e]), sc_in, __ldg(mrow + key) * kLog2e));
+                const float4 mk = *reinterpret_cast<const float4*>(mtile + c * 32 + e);
+                sr[c][e] = __float_as_uint(fmaf(__uint_as_float(sr[c][e]), sc_in, mk.x));
+                sr[c][e + 1] = __float_as_uint(fmaf(__uint_as_float(sr[c][e + 1]), sc_in, mk.y));
+                sr[c][e + 2] = __float_as_uint(fmaf(__uint_as_float(sr[c][e + 2]), sc_in, mk.z));
+                sr[c][e + 3] = __float_as_uint(fmaf(__uint_as_float(sr[c][e + 3]), sc_in, mk.w));
               }
           }
         }
@@ -682,8 +682,7 @@ int attention_tc_launch(ttb_ctx* ctx, int dtype, const void* qkv, int64_t tokens
   if (!encode_tile_map(&tm, qkv, 2, dtype == TTB_BF16, (uint64_t)tokens, (uint64_t)(3 * H), (uint64_t)(3 * H), 128))
     return TTB_ERR_UNSUPPORTED;
   static const int staged = [] { const char* e = getenv("TTB_ATTN_STAGED"); return (e && e[0] == '0') ? 0 : 1; }();
-  const int mask_vec = (mask && (reinterpret_cast<uintptr_t>(mask) % 16 == 0) && mask_batch_stride % 4 == 0) ? 1 : 0;
-  Params p{out, cu, (int)B, (int)heads, causal ? 1 : 0, scale, ctx->d_status, ctx->d_status + 1, staged, mask, (long long)mask_batch_stride, mask_vec};
+  Params p{out, cu, (int)B, (int)heads, causal ? 1 : 0, scale, ctx->d_status, ctx->d_status + 1, staged, mask, (long long)mask_batch_stride};
   // upper bound of the item count from what the host knows; a CTA runs two streams, idle CTAs leave after the tables
   const int64_t tiles_bound = std::min<int64_t>(tokens / QT + B, B * ((max_seqlen + QT - 1) / QT));
   const int64_t items_bound = std::max<int64_t>(1, tiles_bound * heads);

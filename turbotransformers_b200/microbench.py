@@ -104,7 +104,8 @@ def main():
     ap.add_argument("--seq", type=int, default=512)
     ap.add_argument("--heads", type=int, default=12)
     ap.add_argument("--causal", action="store_true")
-    ap.add_argument("--key-mask", action="store_true", help="attention: pass a per-key additive mask [B, max_len] (a quarter of the keys masked)")
+    ap.add_argument("--key-mask", default=None, choices=["padding", "scattered"],
+                    help="attention: pass a per-key additive mask [B, max_len]: a padding mask (a suffix of every sequence at -10000) or a quarter of the keys at random")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--no-flush", action="store_true")
@@ -183,8 +184,12 @@ def main():
         mask, pitch = None, 0
         if a.key_mask:
             pitch = max(lens)
-            mask = torch.where(torch.rand(len(lens), pitch, device="cuda") < 0.25, -10000.0, 0.0).float()
-            mask[:, 0] = 0
+            if a.key_mask == "scattered":
+                mask = torch.where(torch.rand(len(lens), pitch, device="cuda") < 0.25, -10000.0, 0.0).float()
+                mask[:, 0] = 0
+            else:  # padding: each sequence keeps a prefix of between half and all of its keys
+                keep = torch.tensor([int(n * (0.5 + 0.5 * ((i * 37) % 100) / 100.0)) for i, n in enumerate(lens)], device="cuda").clamp_min(1)
+                mask = torch.where(torch.arange(pitch, device="cuda")[None, :] < keep[:, None], 0.0, -10000.0).float()
         fn = lambda: ctx.call("attention_fwd", code, qkv, T, cu, len(lens), max(lens), a.heads, 64, mask, pitch, 0, int(a.causal), 0.125, o)
         if a.burst:
             def make():
