@@ -311,11 +311,14 @@ extern "C" int ttb_attention_fwd(ttb_ctx* ctx, int dtype, const void* qkv, int64
               "attention_fwd: qkv and out must be 16-byte aligned");
   TTB_REQUIRE(ctx, total_tokens >= 0, "attention_fwd: negative token count");
   DeviceGuard g(ctx->device);
-  // The persistent tensor-memory kernel wins once there is enough work to fill its pipeline (measured on B200, whole
-  // BERT-base step of 64 sequences U[8,512]: 4.52 ms against 4.75 ms with the mma.sync kernel below); a handful of short
-  // sequences finish sooner on the many small CTAs of the mma.sync kernel, which also serves masks with a row per query
-  // (a mask with one row of keys per sequence, the encoder's padding mask, is an operand of the tensor-memory kernel).
-  const bool enough_work = total_tokens >= 4096;
+  // The persistent tensor-memory kernel wins once its 128 x 128 tiles are mostly full and there is enough work to fill its
+  // pipeline; short sequences (one key tile per item, query tiles half empty) and small batches finish sooner on the many
+  // small CTAs of the mma.sync kernel, which also serves masks with a row per query (a mask with one row of keys per
+  // sequence, the encoder's padding mask, is an operand of the tensor-memory kernel). Measured on B200, graph replay, us,
+  // tensor-memory / mma.sync: 4 x 512 16.0 / 20.7, 3 x 1024 24.7 / 38.9, 2 x 512 14.8 / 12.5, 16 x 256 18.4 / 17.7,
+  // 64 x 128 20.3 / 18.4, 128 x 64 36.7 / 13.9; the ragged benchmark batch (64 sequences of 8..512) 80 / 96.
+  // With a padding mask the tensor-memory kernel is ahead much earlier (16 x 256 20.0 / 30.5, 8 x 512 28.6 / 56.1).
+  const bool enough_work = mask ? total_tokens * max_seqlen >= (1ll << 19) : (max_seqlen >= 384 && total_tokens * max_seqlen >= (1ll << 20));
   const int tc_mode = attention_tc_mode();
   if ((!mask || mask_row_stride == 0) && total_tokens > 0 && (tc_mode == 2 || (tc_mode == 1 && enough_work))) {
     const int s = attention_tc_launch(ctx, dtype, qkv, total_tokens, cu_seqlens, B, max_seqlen, heads, mask, mask_batch_stride, causal, scale, out);
