@@ -1093,13 +1093,12 @@ quantize_rows16_given_max_kernel(const T* __restrict__ x, int64_t M, int K, cons
 // LayerNorm of 16-bit rows that also leaves the int8 form of its output (per-row symmetric, the quantiser above applied
 // to the rounded 16-bit values, so the result is the same as running the two kernels one after the other): the input of
 // an int8 Linear is produced where it is computed instead of by another pass over the activations.
-template <typename T, int ITERS>
+template <typename T, int ITERS, int ROWS>
 __global__ void __launch_bounds__(kLnWarps * 32)
 layernorm16_quant_kernel(const T* x, const T* __restrict__ gamma, const T* __restrict__ beta, T* out, int8_t* __restrict__ xq,
                          float* __restrict__ scale, int64_t M, int N, float eps) {
   pdl_trigger();
   pdl_wait();
-  constexpr int ROWS = 2;
   const int lane = threadIdx.x & 31;
   const int64_t warps_total = (int64_t)gridDim.x * kLnWarps;
   for (int64_t row0 = ((int64_t)blockIdx.x * kLnWarps + (threadIdx.x >> 5)) * ROWS; row0 < M; row0 += warps_total * ROWS) {
@@ -1125,7 +1124,9 @@ layernorm16_quant_kernel(const T* x, const T* __restrict__ gamma, const T* __res
       ln_row_params(sum, sq, 1.0f / (float)N, eps, rstd[r], mean[r]);
     }
     // normalise in place: the packed registers now hold the rounded 16-bit output, which is also what gets quantised
-    float amax[ROWS] = {0.f, 0.f};
+    float amax[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) amax[r] = 0.f;
 #pragma unroll
     for (int it = 0; it < ITERS; ++it) {
       const int col = (it * 32 + lane) * 8;
@@ -1628,10 +1629,18 @@ extern "C" int ttb_layernorm_quant_int8(ttb_ctx* ctx, int dtype, const void* in,
     return ttb_quantize_rows_int8(ctx, dtype, out, M, N, xq, row_scale);
   }
   DeviceGuard g(ctx->device);
-  const int grid = grid_for((M + 1) / 2, kLnWarps, ctx->sm_count);
+  // few rows (a single short request): one row per warp, so that the kernel is spread over more SMs
+  const bool few = M <= 8 * (int64_t)ctx->sm_count;
+  const int grid = grid_for(few ? M : (M + 1) / 2, kLnWarps, ctx->sm_count);
 #define LNQ_CASE(T, IT)                                                                                                                 \
-  launch_pdl(layernorm16_quant_kernel<T, IT>, dim3(grid), dim3(kLnWarps * 32), 0, ctx->stream, (const T*)in, (const T*)gamma, (const T*)beta, \
-             (T*)out, xq, row_scale, M, (int)N, eps)
+  do {                                                                                                                                  \
+    if (few)                                                                                                                            \
+      launch_pdl(layernorm16_quant_kernel<T, IT, 1>, dim3(grid), dim3(kLnWarps * 32), 0, ctx->stream, (const T*)in, (const T*)gamma,    \
+                 (const T*)beta, (T*)out, xq, row_scale, M, (int)N, eps);                                                               \
+    else                                                                                                                                \
+      launch_pdl(layernorm16_quant_kernel<T, IT, 2>, dim3(grid), dim3(kLnWarps * 32), 0, ctx->stream, (const T*)in, (const T*)gamma,    \
+                 (const T*)beta, (T*)out, xq, row_scale, M, (int)N, eps);                                                               \
+  } while (0)
 #define LNQ_PICK(T)                     \
   do {                                  \
     if (N <= 256) LNQ_CASE(T, 1);       \
