@@ -671,9 +671,9 @@ int attention_tc_mode() {
   return 1;
 }
 
-// Launches the tcgen05 attention kernel. qkv is [tokens, 3*heads*64] in fp16/bf16; no mask tensor (callers with one use
-// the mma.sync kernel). Returns TTB_ERR_UNSUPPORTED when the batch does not fit the schedule tables or the tensor map
-// cannot be encoded, so the caller can fall back.
+// Launches the tcgen05 attention kernel. qkv is [tokens, 3*heads*64] in fp16/bf16; mask is null or an additive fp32 mask
+// with one row of keys per sequence (masks with a row per query use the mma.sync kernel). Returns TTB_ERR_UNSUPPORTED when
+// the batch does not fit the schedule tables or the tensor map cannot be encoded, so the caller can fall back.
 int attention_tc_launch(ttb_ctx* ctx, int dtype, const void* qkv, int64_t tokens, const int32_t* cu, int64_t B, int64_t max_seqlen,
                         int64_t heads, const float* mask, int64_t mask_batch_stride, int causal, float scale, void* out) {
   if (B > kMaxB || B < 1 || heads < 1) return TTB_ERR_UNSUPPORTED;
