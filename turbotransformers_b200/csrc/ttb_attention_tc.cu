@@ -1,8 +1,8 @@
 // Self-attention over packed variable-length batches on the 5th-generation tensor cores.
 //
 // Persistent kernel, one CTA per SM, two independent streams per CTA. A work item is one 128-row query tile of one
-// (sequence, head); a stream takes every other item of its CTA and walks the key/value tiles (128 rows) of one item
-// after the other as one flat sequence of tiles g = 0, 1, 2, ...
+// (sequence, head); a stream walks the key/value tiles (128 rows) of one item after the other as one flat sequence of
+// tiles g = 0, 1, 2, ...
 //   warps 0, 2  : TMA loaders of stream 0 / 1 - the item's Q tile (double-buffered) and K_g / V_g into 2-stage rings, by
 //                 two independent cursors (Q + K tiles, V tiles) that each issue as soon as their slot is free, so the next
 //                 item's Q and first K tile are in flight a whole tile before they are needed.
@@ -14,17 +14,19 @@
 //                 wait in an issuing thread only returns once the MMAs that thread has issued have drained, so each
 //                 stream has its own issuer. It waits for the softmax warps' go-ahead first (which lets its earlier MMAs
 //                 drain) and then for the operand tiles of the group (a barrier poll each): the softmax warps never wait
-//                 on a load. Measured with per-phase cycle stamps on 32 x 512: a stream's tile period is the softmax
-//                 warps' serial chain (score load 350-600 cycles, 128 exponentials per thread 2000-2900 while the other
-//                 stream's warp shares the scheduler, P store 150-400, two satisfied barrier waits 200-350 each) plus about
-//                 one tile's worth per item for the row maximum, the output pass and the item bookkeeping.
+//                 on a load. Measured with per-phase cycle stamps on 37 x 512: a stream's tile period is the softmax
+//                 warps' serial chain (score load 160-200 cycles, 128 exponentials per thread with their sums and packing
+//                 2650-2900 while the other stream's warp shares the scheduler, P store 115-160, two satisfied barrier
+//                 waits 110-260 each), plus per item the output pass and 600-1300 cycles of bookkeeping.
 //   warps 4..7  : softmax of stream 0, warps 8..11: of stream 1 (registers are moved from the first
 //                 warpgroup to the softmax ones with setmaxnreg) - one query row per thread: scores from TMEM, running
 //                 max / sum in fp32, exp2 with the scale folded in, P written back to TMEM as packed 16-bit pairs.
 //                 O accumulates in TMEM across key tiles. The row maximum is taken on an item's first tile only; later
 //                 tiles reuse it and fall back to a rescale of O only if a probability would leave the 16-bit range
 //                 (row sum above 2^15), which real score distributions do not reach. The final division by the running
-//                 sum makes the result independent of the reference maximum.
+//                 sum makes the result independent of the reference maximum. With a mask operand (one row of keys per
+//                 sequence) a warp fetches the tile's 128 entries once and, if any is set, adds them where the scores
+//                 leave TMEM. An item's output (O / l) leaves through the item's own Q buffer as whole 128-byte rows.
 // TMEM (all 512 columns): S0 | S1 (128 each) | O0 | O1 (64 each) | P0 | P1 (64 each).
 // Items are ordered longest sequence first; a stream's first item is fixed, every further one is the next item nobody has
 // taken (a counter in global memory, fetched one item ahead by the stream's loader), so the streams finish together even
