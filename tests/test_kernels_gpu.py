@@ -318,6 +318,41 @@ def test_embedding_ln_fixed_and_varlen(ctx, dt):
     assert ctx.device_status() == _capi.OK
 
 
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("H", [256, 512, 1024, 264, 100])
+def test_embedding_ln_16bit_widths_and_explicit_ids(ctx, dt, H):
+    """Every width the 16-byte-vector kernel is instantiated for (and two it is not: 264 > 256 takes the next size up, 100
+    is not a multiple of 8), with caller-supplied position and token-type ids and one id out of range (clamped, flagged)."""
+    r = rng(H)
+    vocab, npos, ntype = 300, 40, 3
+    w = {"word": rounded(r.standard_normal((vocab, H)).astype(np.float32) * 0.05, dt),
+         "position": rounded(r.standard_normal((npos, H)).astype(np.float32) * 0.05, dt),
+         "token_type": rounded(r.standard_normal((ntype, H)).astype(np.float32) * 0.05, dt),
+         "ln_gamma": rounded(1 + 0.1 * r.standard_normal(H).astype(np.float32), dt),
+         "ln_beta": rounded(0.1 * r.standard_normal(H).astype(np.float32), dt)}
+    D = {k: dev(v, dt) for k, v in w.items()}
+    B, L = 5, 33
+    ids = r.integers(0, vocab, (B, L)).astype(np.int64)
+    pos = r.integers(0, npos, (B, L)).astype(np.int64)
+    tt = r.integers(0, ntype, (B, L)).astype(np.int64)
+    want = restate.bert_embedding(ids, pos, tt, w)
+    out = torch.full((B * L + 1, H), float("nan"), dtype=TORCH_DT[dt], device="cuda")
+    ctx.call("embedding_ln", code(dt), dev(ids), dev(pos), dev(tt), None, B, L, B * L, D["word"], D["position"], D["token_type"],
+             D["ln_gamma"], D["ln_beta"], H, vocab, npos, ntype, 1e-12, out)
+    assert ctx.device_status() == _capi.OK
+    assert torch.isnan(out[B * L]).all()
+    assert maxdiff(host(out[:B * L]).reshape(B, L, H), want) < ATOL[dt] * 4
+    bad = ids.copy()
+    bad[2, 7] = vocab + 5
+    ctx.call("embedding_ln", code(dt), dev(bad), dev(pos), dev(tt), None, B, L, B * L, D["word"], D["position"], D["token_type"],
+             D["ln_gamma"], D["ln_beta"], H, vocab, npos, ntype, 1e-12, out)
+    assert ctx.device_status() == _capi.ERR_BAD_INDEX      # reading the status also clears it
+    clamped = ids.copy()
+    clamped[2, 7] = vocab - 1
+    assert maxdiff(host(out[:B * L]).reshape(B, L, H), restate.bert_embedding(clamped, pos, tt, w)) < ATOL[dt] * 4
+    assert ctx.device_status() == _capi.OK
+
+
 def test_invalid_arguments_return_status_without_launching(ctx):
     lib = _capi.lib()
     before = ctx.launches()
