@@ -367,7 +367,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
               *abort_flag = 1;
               break;
             }
-            __nanosleep(64);
+            __nanosleep(400);
           }
         }
         if (*abort_flag) {  // let copies in flight land before shared memory is released
