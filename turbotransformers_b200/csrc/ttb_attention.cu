@@ -190,7 +190,17 @@ attention_fwd_kernel(const AttnParams p) {
     const int k0 = t * KT;
     // Per-element masking only where a tile needs it (warp-uniform): a mask tensor, keys past the end of the
     // sequence, or the causal diagonal. Interior tiles keep the raw scores and fold the scale into the exp2 FMA.
-    const bool edge = (p.mask != nullptr) || (k0 + KT > len) || (p.causal && k0 + KT - 1 > q0 + warp * 16);
+    // A mask with one row of keys per sequence (the encoder's padding mask) is zero over most tiles: the warp looks at the
+    // tile's entries once and treats the tile as unmasked when none of them is set.
+    bool mask_set = p.mask != nullptr;
+    if (p.mask && p.mask_rs == 0) {
+      const float* mr = p.mask + (long long)b * p.mask_bs + k0;
+      bool mine = false;
+#pragma unroll
+      for (int u = 0; u < KT; u += 32) mine = mine || (k0 + u + lane < len && mr[u + lane] != 0.f);
+      mask_set = __any_sync(0xffffffffu, mine);
+    }
+    const bool edge = mask_set || (k0 + KT > len) || (p.causal && k0 + KT - 1 > q0 + warp * 16);
     float sce = sc;
     if (edge) {
       sce = 1.0f;
@@ -202,7 +212,7 @@ attention_fwd_kernel(const AttnParams p) {
           const int key = k0 + j * 8 + t4 * 2 + (e & 1);
           float v = s[j][e] * sc;
           const bool dead = key >= len || (p.causal && key > qrow[r]);
-          if (p.mask && !dead && qrow[r] < len) v += mrow[r][key] * kLog2e;
+          if (mask_set && !dead && qrow[r] < len) v += mrow[r][key] * kLog2e;
           s[j][e] = dead ? -INFINITY : v;
         }
       }
