@@ -342,3 +342,16 @@ def test_concurrent_host_threads_share_one_model():
     assert not errs
     for o in outs:
         assert torch.equal(o, base)
+
+
+def test_gpt2_logits_in_padded_rows_equal_the_contiguous_ones():
+    """contiguous_logits=False returns a strided view of rows padded to a multiple of 8 entries: same values, no copy."""
+    hf32 = synthetic.make_hf_gpt2("gpt2-mini", 0)
+    assert hf32.config.vocab_size % 8 != 0
+    ids = synthetic.random_ids(2, 40, hf32.config.vocab_size, 0).to(DEV)
+    model = tt.GPT2Model.from_torch(hf32.to(DEV).half(), DEV)
+    hidden, logits = model(ids)
+    hidden2, view = model(ids, contiguous_logits=False)
+    assert tuple(view.shape) == tuple(logits.shape) and not view.is_contiguous()
+    assert view.stride(-2) % 8 == 0 and view.stride(-2) >= logits.shape[-1]
+    assert torch.equal(hidden, hidden2) and torch.equal(view, logits)

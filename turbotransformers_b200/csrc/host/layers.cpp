@@ -1066,5 +1066,17 @@ void Linear::operator()(const Tensor& input, Tensor* output) const {
   dense_.Forward(input, M, TTB_EPI_BIAS, nullptr, output->raw_mut(), is_trans_, "Linear");
 }
 
+void Linear::Padded(const Tensor& input, Tensor* output) const {
+  FloatType(input, "Linear input");
+  const int dt = core::ToTTBDtype(input.dtype());
+  const int64_t N = Width(), Np = PaddedWidth(), M = input.rows();
+  if (dt == TTB_F32 || Np == N) {  // nothing to gain: the plain path already stores whole rows
+    (*this)(input, output);
+    return;
+  }
+  output->Reshape(input.dtype(), WithLast(input, Np), kDLCUDA, input.device_id(), "Linear/Reshape");
+  dense_.Forward(input, M, TTB_EPI_BIAS, nullptr, output->raw_mut(), is_trans_, "Linear", Np);
+}
+
 }  // namespace layers
 }  // namespace turbo_transformers

@@ -338,6 +338,13 @@ class Linear {
   Linear(core::Tensor weight, core::Tensor bias, bool is_trans_weight)
       : dense_(std::move(weight), std::move(bias)), is_trans_(is_trans_weight) {}
   void operator()(const core::Tensor& input, core::Tensor* output) const;
+  // The same product with the output's last dimension rounded up to a multiple of 8 elements (rows that start on 16-byte
+  // boundaries, which the tensor-core epilogue stores at full speed): output is [..., PaddedWidth()], of which the first
+  // out-features columns are the result and the rest is undefined. For widths like a 50257-entry vocabulary, where
+  // operator() pays a second pass over the output to compact the rows.
+  void Padded(const core::Tensor& input, core::Tensor* output) const;
+  int64_t Width() const { return dense_.out_dim(is_trans_); }
+  int64_t PaddedWidth() const { return (Width() + 7) / 8 * 8; }
 
  private:
   PackedLinear dense_;

@@ -294,5 +294,9 @@ PYBIND11_MODULE(turbo_transformers_cxx, m) {
 
   py::class_<layers::Linear>(m, "Linear")
       .def(py::init([](Tensor& w, Tensor& b, bool is_trans_weight) { return new layers::Linear(std::move(w), std::move(b), is_trans_weight); }))
-      .def("__call__", &layers::Linear::operator());
+      .def("__call__", &layers::Linear::operator())
+      .def("padded", &layers::Linear::Padded,
+           "The product with the output's last dimension rounded up to a multiple of 8 (columns beyond width() are undefined).")
+      .def("width", &layers::Linear::Width)
+      .def("padded_width", &layers::Linear::PaddedWidth);
 }

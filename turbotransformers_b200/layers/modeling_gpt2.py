@@ -42,9 +42,13 @@ class GPT2Model:
         k = past[0]["self_keys"]
         return 0 if k.is_null() else k.shape(0)
 
-    def __call__(self, input_ids: AnyTensor, return_logits: bool = True, return_type: Optional[ReturnType] = None, past=None):
+    def __call__(self, input_ids: AnyTensor, return_logits: bool = True, return_type: Optional[ReturnType] = None, past=None,
+                 contiguous_logits: bool = True):
         """input_ids int64 [B, L] on the GPU -> (last_hidden_state [B,L,H], logits [B,L,vocab] or None).
-        With `past` (from new_cache()), input_ids are the tokens that follow what the cache already holds."""
+        With `past` (from new_cache()), input_ids are the tokens that follow what the cache already holds.
+        contiguous_logits=False returns the logits as a view of rows padded to a multiple of 8 entries (torch tensors only):
+        a 50257-entry row does not start on a 16-byte boundary, and making the rows contiguous costs a second pass over
+        the largest tensor of the model."""
         if isinstance(input_ids, torch.Tensor):
             use_current_stream(input_ids)
         ids = try_convert(input_ids)
@@ -67,7 +71,11 @@ class GPT2Model:
         h = _empty()
         self.final_norm(x, h)
         logits = None
-        if return_logits:
+        if return_logits and not contiguous_logits and return_type in (None, ReturnType.TORCH):
+            padded = _empty()
+            self.lm_head.padded(h, padded)
+            logits = convert_returns_as_type(padded, ReturnType.TORCH)[..., :self.lm_head.width()]
+        elif return_logits:
             logits = _empty()
             self.lm_head(h, logits)
             logits = convert_returns_as_type(logits, return_type)

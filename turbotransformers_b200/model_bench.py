@@ -173,6 +173,8 @@ def main():
         mean, p50 = timeit(lambda: model(ids), a.warmup, a.iters)
         fl = enc_flops(12, 768, 1024, causal=True) + 2.0 * 1024 * 768 * hf.config.vocab_size
         report("gpt2-small fp16, full-sequence forward with tied-embedding logits", 8, 1024, fl, mean, p50)
+        mean, p50 = timeit(lambda: model(ids, contiguous_logits=False), a.warmup, a.iters)
+        report("gpt2-small fp16, logits left in rows padded to a multiple of 8 entries (a strided view)", 8, 1024, fl, mean, p50)
         mean, p50 = timeit(lambda: model(ids, return_logits=False), a.warmup, a.iters)
         report("gpt2-small fp16, hidden states only", 8, 1024, enc_flops(12, 768, 1024, causal=True), mean, p50)
     assert tt._cxx_module.device_status(0) == 0
