@@ -264,6 +264,32 @@ def test_attention_with_a_per_key_mask(ctx, dt, lens, heads, pitch, causal, kern
     assert maxdiff(got, attention_oracle(qkv, lens, heads, mask, causal=causal)) < (4e-3 if dt == "f16" else 3e-2)
 
 
+@pytest.mark.parametrize("kernel", ["auto", "tensor_memory", "mma_sync"])
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("value", [-10000.0, -3.0e38])
+def test_attention_with_a_padding_mask(ctx, dt, kernel, value, monkeypatch):
+    """A padded batch the way HuggingFace callers pass it: every sequence has the full length and a suffix of its keys
+    masked out (whole key tiles among them, which the kernels skip), kept lengths from one key to all of them."""
+    if kernel != "auto":
+        monkeypatch.setenv("TTB_ATTN_TC", "2" if kernel == "tensor_memory" else "0")
+    r = rng(77)
+    B, L, heads = 9, 512, 4
+    keep = [512, 1, 127, 128, 129, 300, 384, 385, 64]
+    H, T = heads * 64, B * L
+    qkv = rounded(r.standard_normal((T, 3 * H)).astype(np.float32), dt)
+    cu = torch.tensor(np.arange(B + 1) * L, dtype=torch.int32).cuda()
+    mask = np.zeros((B, L), np.float32)
+    for b, n in enumerate(keep):
+        mask[b, n:] = value
+    out = torch.full((T, H), float("nan"), dtype=TORCH_DT[dt], device="cuda")
+    ctx.call("attention_fwd", code(dt), dev(qkv, dt), T, cu, B, L, heads, 64, dev(mask), L, 0, 0, 0.125, out)
+    assert ctx.device_status() == _capi.OK
+    got = host(out)
+    assert np.isfinite(got).all()
+    oracle_mask = np.maximum(mask, -1.0e9)   # the same softmax without overflowing the float32 restatement
+    assert maxdiff(got, attention_oracle(qkv, [L] * B, heads, oracle_mask)) < (4e-3 if dt == "f16" else 3e-2)
+
+
 @pytest.mark.parametrize("kernel", ["tensor_memory", "mma_sync"])
 @pytest.mark.parametrize("dt", ["f16", "bf16"])
 def test_attention_masks_and_causal(ctx, dt, kernel, monkeypatch):

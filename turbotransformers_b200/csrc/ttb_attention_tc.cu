@@ -526,6 +526,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
         __syncwarp();
         if (lane == 0) mbar_arrive(s_free(s));
         float sc = sc_plain;
+        bool tile_dead = false;  // MASK: every key of the tile is masked out for every row of this warp
         if (MASK) {
           const float* mrow = p.mask + (long long)it.seq * p.mask_bs + k0;
           const float sc_in = sc_plain;
@@ -536,7 +537,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
           float mine[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u) mine[u] = (u * 32 + lane < valid) ? __ldg(mrow + u * 32 + lane) : 0.f;
-          if (__any_sync(0xffffffffu, mine[0] != 0.f || mine[1] != 0.f || mine[2] != 0.f || mine[3] != 0.f)) {
+          // A tile whose entries are all at a padding mask's -10000 contributes exact zeros once the row has seen a key
+          // that is not masked (its maximum is then thousands of octaves above anything in this tile): no arithmetic.
+          const bool all_off = __all_sync(0xffffffffu, (lane >= valid || mine[0] <= -5000.f) && (32 + lane >= valid || mine[1] <= -5000.f) &&
+                                                           (64 + lane >= valid || mine[2] <= -5000.f) && (96 + lane >= valid || mine[3] <= -5000.f));
+          tile_dead = all_off && j > 0 && __all_sync(0xffffffffu, m_used > -2000.f);
+          if (!tile_dead && __any_sync(0xffffffffu, mine[0] != 0.f || mine[1] != 0.f || mine[2] != 0.f || mine[3] != 0.f)) {
             sc = 1.0f;
             float* mtile = reinterpret_cast<float*>(smem + SMEM_MASKROW) + (warp - 4) * 128;
             __syncwarp();  // the previous tile's reads of the row are done
@@ -558,7 +564,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm, const Params p) {
         // keys of this tile that at least one row of this warp can see, in 32-key chunks: the others cost no exponentials
         int lim = it.len - k0;
         if (p.causal) lim = min(lim, it.q0 + quad * 32 + 32 - k0);
-        const int live = (min(lim, KT) + 31) >> 5;
+        const int live = tile_dead ? 0 : (min(lim, KT) + 31) >> 5;
         if ((k0 + KT > it.len) || (p.causal && k0 + KT - 1 > it.q0 + quad * 32)) {  // edge tile: keys past the end / above the diagonal
 #pragma unroll
           for (int c = 0; c < 4; ++c)
